@@ -1,0 +1,148 @@
+/* sepal_b200: the trunk projection GEMMs of Sepal-Runner's GPU engine, written for NVIDIA B200 (sm_100a).
+ *
+ * This is the whole boundary of the library: a C ABI with plain pointers and sizes. It follows the conventions of the engine's own
+ * C ABI (runner/include/sepal/c_api.h:1-9,29-60): every function returns 0 on success and non-zero on failure, the message of the
+ * last failure on the calling thread is at sepal_b200_last_error() (cleared by the next successful call), no exception crosses
+ * the boundary, and the caller owns every buffer it passes.
+ *
+ * Two layers:
+ *   - launchers on DEVICE pointers, one for each kernel launcher of the reference's engine that this library replaces. They enqueue
+ *     on the given CUDA stream (a cudaStream_t passed as void*, NULL = the default stream) and return without waiting.
+ *   - a provider on HOST pointers, the face the reference gives its cuBLAS provider (sepal::cuda::CudaGemm,
+ *     runner/cuda/include/sepal/cuda/cuda_gemm.hpp:112-160): weights uploaded once, then Y = beta Y + X W^T with X uploaded and Y
+ *     downloaded inside the call.
+ *
+ * Matrices are row-major; a matrix argument is a pointer and a row stride in elements (runner/cuda/src/device.hpp:14-16).
+ *   Y[t, n] = epilogue( sum over k of X[t, k] * W[n, k] ),   X [T, K], W [N, K] (one output feature per row, K contiguous).
+ *
+ * There is no CPU path and no library GEMM behind these functions: on a device that is not sm_100 sepal_b200_open fails.
+ */
+#ifndef SEPAL_B200_H
+#define SEPAL_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define SEPAL_B200_API __declspec(dllexport)
+#else
+#define SEPAL_B200_API __attribute__((visibility("default")))
+#endif
+
+typedef struct sepal_b200_ctx sepal_b200_ctx;
+typedef struct sepal_b200_provider sepal_b200_provider;
+
+/* Epilogues: the reference's SimtEpilogue (runner/cuda/src/gemm_simt_kernels.hpp:19-25). */
+#define SEPAL_B200_STORE 0  /* Y = acc */
+#define SEPAL_B200_ADD 1    /* Y = Y + acc (the residual stream updated in place; one float32 addition) */
+#define SEPAL_B200_SWIGLU 2 /* W rows are [gate; up] interleaved in blocks of 64; N is the packed width 2 I, Y has I columns */
+
+/* Element types of host matrices given to the provider (the codes of sepal::DType's float types). */
+#define SEPAL_B200_F32 0
+#define SEPAL_B200_F16 1
+
+/* ---- library ------------------------------------------------------------------------------------------------------------ */
+
+/* Version of this ABI (1). Counterpart of sepal_api_version, runner/include/sepal/c_api.h:31. */
+SEPAL_B200_API int32_t sepal_b200_api_version(void);
+
+/* Message of the calling thread's last failed call, "" after a successful one. Counterpart of sepal_last_error, c_api.h:34. */
+SEPAL_B200_API const char* sepal_b200_last_error(void);
+
+/* Creates the per-device state every launcher needs: device properties, the scratch memory of the split-k schedule
+ * (`workspace_bytes`, 0 = two 128 x 256 float32 tiles per SM, about 39 MB on a B200) and the device status word. All device
+ * memory the launchers ever use is allocated here, as the engine allocates its call buffers once (runner/cuda/src/cuda_engine.cpp:714-743).
+ * One context serves one stream at a time: launches that overlap on the device must use different contexts.
+ * On failure *out is NULL. Counterpart of the engine creation behind sepal_open, c_api.h:39. */
+SEPAL_B200_API int32_t sepal_b200_open(int32_t device, uint64_t workspace_bytes, sepal_b200_ctx** out);
+
+/* Frees a context (NULL is allowed). Counterpart of sepal_close, c_api.h:41. */
+SEPAL_B200_API void sepal_b200_close(sepal_b200_ctx* ctx);
+
+/* A JSON description of the context (device, SM count, scratch bytes, kernel names). Size-query protocol of sepal_info,
+ * c_api.h:43-46: with capacity too small nothing is written, *needed gets the size including the terminator, the call fails. */
+SEPAL_B200_API int32_t sepal_b200_info(sepal_b200_ctx* ctx, char* buffer, uint64_t capacity, uint64_t* needed);
+
+/* Waits for `stream`, then reads and clears the device status word: *status_out = 0 when no kernel reported a problem, otherwise
+ * the code of the first bounded wait that ran out (low byte: which wait; higher bits: the CTA). A non-zero status means the
+ * outputs of the launches since the last call are not to be trusted. The reference reports device faults through
+ * cudaStreamSynchronize in CudaEngine::run (runner/cuda/src/cuda_engine.cpp:1969); this is the same place in the flow. */
+SEPAL_B200_API int32_t sepal_b200_status(sepal_b200_ctx* ctx, void* stream, int32_t* status_out);
+
+/* Kernels of this library the calling thread has launched since the previous call of this function. */
+SEPAL_B200_API uint64_t sepal_b200_take_launch_count(void);
+
+/* ---- launchers on device pointers ------------------------------------------------------------------------------------------ */
+
+/* binary16 x binary16 -> float32 accumulation on the tensor cores (tcgen05.mma), result binary16 (y_half != 0) or float32.
+ * Replaces launch_gemm_nt (runner/cuda/src/gemm_kernels.hpp:22-31) and the cublasGemmEx call of CudaEngine::Impl::gemm
+ * (runner/cuda/src/cuda_engine.cpp:1093-1154); the epilogues replace launch_swiglu / launch_add after it (cuda_engine.cpp:1919-1945).
+ * Requires K, ld_x, ld_w multiples of 8, N and ld_y even, x and w 16-byte aligned (gemm_nt_supports, gemm_kernels.hpp:34-36);
+ * SWIGLU needs N a multiple of 128. config: -1 picks a schedule; 0..3 force one (tests). t == 0 is a no-op. */
+SEPAL_B200_API int32_t sepal_b200_gemm_f16(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const void* w, uint64_t ld_w, void* y, uint64_t ld_y,
+                                           int32_t y_half, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t config, void* stream);
+
+/* binary16 activations x int8 weights with one scale per output row and group of 128 values of k (the gpu-w8g layout). Replaces
+ * launch_gemm_simt with SimtWeight::Int8Group (runner/cuda/src/gemm_simt_kernels.hpp:42-56) and launch_gemm_w8a16
+ * (runner/cuda/src/gemm_s8_kernels.hpp:51-57). q is int8 [N, ld_q]; scales_t / descale come from sepal_b200_prepare_w8g_scales.
+ * Requires K a multiple of 128, ld_x a multiple of 8, ld_q a multiple of 16, ld_st >= N. */
+SEPAL_B200_API int32_t sepal_b200_gemm_w8g(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const int8_t* q, uint64_t ld_q, const void* scales_t,
+                                           uint64_t ld_st, const float* descale, void* y, uint64_t ld_y, int32_t y_half, uint64_t t, uint64_t n,
+                                           uint64_t k, int32_t epilogue, int32_t config, void* stream);
+
+/* The group quantiser, bit for bit launch_quantize_group_s8 (runner/cuda/src/gemm_simt_kernels.hpp:64-65): src float32 [rows, K],
+ * q int8 [rows, ld_q], s float32 [rows, ld_s] with one scale per group of 128. */
+SEPAL_B200_API int32_t sepal_b200_quantize_group_s8(const float* src, uint64_t ld_src, int8_t* q, uint64_t ld_q, float* s, uint64_t ld_s,
+                                                    uint64_t rows, uint64_t k, void* stream);
+
+/* s float32 [N, ld_s] (the quantiser's layout) -> scales_t binary16 [groups, ld_st] and *descale (device float), the form the
+ * tensor-core multiply reads: group-major, times the power of two that puts the largest scale in [128, 256). max_bits: 4 bytes of
+ * device scratch. Part of weight placement, where the reference's put_simt quantises (runner/cuda/src/cuda_engine.cpp:580-627). */
+SEPAL_B200_API int32_t sepal_b200_prepare_w8g_scales(const float* s, uint64_t ld_s, uint64_t n, uint64_t groups, void* scales_t, uint64_t ld_st,
+                                                     float* descale, uint32_t* max_bits, void* stream);
+
+/* dst row p = src row pack_gate_up_source(p, inter) for the 2 * inter rows of a stacked [gate; up] matrix
+ * (runner/cuda/src/gemm_simt_kernels.hpp:72-77; the engine's interleave at cuda_engine.cpp:597-611). Strides and row length in bytes. */
+SEPAL_B200_API int32_t sepal_b200_pack_gate_up(const void* src, uint64_t src_stride_bytes, void* dst, uint64_t dst_stride_bytes, uint64_t inter,
+                                               uint64_t row_bytes, void* stream);
+
+/* float32 <-> binary16 on the device, round to nearest even (runner/cuda/src/convert_kernels.hpp). */
+SEPAL_B200_API int32_t sepal_b200_float_to_half(const float* src, void* dst, uint64_t count, void* stream);
+SEPAL_B200_API int32_t sepal_b200_half_to_float(const void* src, float* dst, uint64_t count, void* stream);
+
+/* ---- provider on host pointers ------------------------------------------------------------------------------------------------ */
+
+/* A provider owns a context, a stream and one device allocation (`arena_bytes`, 0 = 1 GiB) from which weights (bottom, for the
+ * provider's life) and per-call temporaries (top, released when the call returns) are carved; nothing else is allocated afterwards.
+ * Counterpart of CudaGemm's constructor (cuda_gemm.hpp:112-115, memory model :7-10). */
+SEPAL_B200_API int32_t sepal_b200_provider_open(int32_t device, uint64_t arena_bytes, sepal_b200_provider** out);
+SEPAL_B200_API void sepal_b200_provider_close(sepal_b200_provider* provider);
+
+/* Copies W [N, K] (host, SEPAL_B200_F32 or _F16) to the device once, rounded to binary16, and returns its id.
+ * Counterpart of CudaGemm::upload_weights (cuda_gemm.hpp:128-129). */
+SEPAL_B200_API int32_t sepal_b200_provider_upload_weights(sepal_b200_provider* provider, const void* w, int32_t dtype, uint64_t n, uint64_t k,
+                                                          uint32_t* id_out);
+
+/* The same for int8-group storage: W float32 [N, K] (host) is quantised on the device (K a multiple of 128) and kept as int8 +
+ * prepared scales, as the gpu-w8g profile stores its matrices (runner/cuda/src/cuda_engine.cpp:580-627). */
+SEPAL_B200_API int32_t sepal_b200_provider_upload_weights_w8g(sepal_b200_provider* provider, const float* w, uint64_t n, uint64_t k, uint32_t* id_out);
+
+/* Y[t, n] = beta Y[t, n] + sum_k X[t, k] W[n, k]: X [T, K] host (F32 or F16; rounded to binary16 on the device), Y [T, N] host
+ * float32. X is uploaded, Y downloaded, and the call returns when Y is complete. With beta == 0 Y is written without being read.
+ * Counterpart of CudaGemm::gemm_f(MatRef, WeightId, MatView, float) (cuda_gemm.hpp:136-137). Pinned host buffers
+ * (sepal_b200_host_alloc) make the copies asynchronous and fast; pageable ones work too. */
+SEPAL_B200_API int32_t sepal_b200_provider_gemm_f(sepal_b200_provider* provider, const void* x, int32_t x_dtype, uint64_t t, uint32_t weight_id,
+                                                  float* y, float beta);
+
+/* Pinned host memory for the provider's callers. */
+SEPAL_B200_API int32_t sepal_b200_host_alloc(uint64_t bytes, void** out);
+SEPAL_B200_API void sepal_b200_host_free(void* ptr);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SEPAL_B200_H */

@@ -1,0 +1,249 @@
+"""ctypes loaders for the two checkers. TEST INFRASTRUCTURE, not product code.
+
+`Oracle`  -> oracle/libsepal_oracle.so, the C restatement (sepal_oracle.c).
+`Ref`     -> oracle/_ref/libsepal_ref.so, the reference's own CPU GEMM compiled from its sources (ref_shim.cpp, Makefile).
+
+Only tests/, the smoke check and the benchmark's CPU-baseline leg import this module.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "libsepal_oracle.so")
+REF_SO = os.path.join(HERE, "_ref", "libsepal_ref.so")
+REFERENCE_ROOT = "/root/reference"
+
+_f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+_f64p = np.ctypeslib.ndpointer(dtype=np.float64, flags="C_CONTIGUOUS")
+_i8p = np.ctypeslib.ndpointer(dtype=np.int8, flags="C_CONTIGUOUS")
+_u32p = np.ctypeslib.ndpointer(dtype=np.uint32, flags="C_CONTIGUOUS")
+_sz = C.c_size_t
+
+
+def build(want_ref: bool = True) -> None:
+    """Compile the checkers (make in oracle/). The reference library is built only where the reference tree exists."""
+    targets = ["oracle"]
+    if want_ref and os.path.exists(os.path.join(REFERENCE_ROOT, "runner", "src", "cpu", "gemm.cpp")):
+        targets.append("ref")
+    subprocess.run(["make", "-s", "-C", HERE, f"REF={REFERENCE_ROOT}", *targets], check=True)
+
+
+def f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+class Oracle:
+    """The C restatement. Every method takes and returns float32 / int8 numpy arrays (16-bit operands widened exactly)."""
+
+    def __init__(self) -> None:
+        if not os.path.exists(ORACLE_SO):
+            build(want_ref=False)
+        L = self.lib = C.CDLL(ORACLE_SO)
+        L.oracle_f32_to_bf16.restype = C.c_uint16
+        L.oracle_f32_to_bf16.argtypes = [C.c_float]
+        L.oracle_f32_to_f16.restype = C.c_uint16
+        L.oracle_f32_to_f16.argtypes = [C.c_float]
+        L.oracle_f16_to_f32.restype = C.c_float
+        L.oracle_f16_to_f32.argtypes = [C.c_uint16]
+        L.oracle_bf16_to_f32.restype = C.c_float
+        L.oracle_bf16_to_f32.argtypes = [C.c_uint16]
+        L.oracle_gemm_f64acc.argtypes = [_f32p, _sz, _f32p, _sz, _f32p, _sz, _sz, _sz, _sz, C.c_float]
+        L.oracle_gemm_fma_chain.argtypes = [_f32p, _sz, _f32p, _sz, _f32p, _sz, _sz, _sz, _sz]
+        L.oracle_gemm_f64acc_sample.argtypes = [_f32p, _sz, _f32p, _sz, _sz, _u32p, _u32p, _sz, _f64p]
+        L.oracle_quantize_group_s8.restype = C.c_int
+        L.oracle_quantize_group_s8.argtypes = [_f32p, _sz, _i8p, _sz, _f32p, _sz, _sz, _sz]
+        L.oracle_dequant_group_s8.argtypes = [_i8p, _sz, _f32p, _sz, _f32p, _sz, _sz, _sz]
+        L.oracle_swiglu.restype = C.c_float
+        L.oracle_swiglu.argtypes = [C.c_float, C.c_float]
+        L.oracle_pack_gate_up_source.restype = _sz
+        L.oracle_pack_gate_up_source.argtypes = [_sz, _sz]
+        L.oracle_swiglu_packed.argtypes = [_f32p, _sz, _f32p, _sz, _sz, _sz]
+        L.oracle_add.argtypes = [_f32p, _sz, _f32p, _sz, _sz, _sz]
+        L.oracle_rmsnorm.argtypes = [_f32p, _sz, _f32p, _sz, _sz, _sz, _f32p, C.c_double]
+
+    def gemm(self, x, w, y0=None, beta: float = 0.0) -> np.ndarray:
+        """float64-accumulated product x [T,K] . w[N,K]^T (+ beta y0), rounded to float32 once."""
+        x, w = f32(x), f32(w)
+        t, k = x.shape
+        n = w.shape[0]
+        assert w.shape[1] == k
+        y = np.zeros((t, n), np.float32) if y0 is None else f32(y0).copy()
+        self.lib.oracle_gemm_f64acc(x, k, w, k, y, n, t, n, k, beta)
+        return y
+
+    def gemm_fma_chain(self, x, w) -> np.ndarray:
+        x, w = f32(x), f32(w)
+        t, k = x.shape
+        n = w.shape[0]
+        y = np.zeros((t, n), np.float32)
+        self.lib.oracle_gemm_fma_chain(x, k, w, k, y, n, t, n, k)
+        return y
+
+    def gemm_sample(self, x, w, rows, cols) -> np.ndarray:
+        x, w = f32(x), f32(w)
+        rows = np.ascontiguousarray(rows, np.uint32)
+        cols = np.ascontiguousarray(cols, np.uint32)
+        out = np.zeros(rows.shape[0], np.float64)
+        self.lib.oracle_gemm_f64acc_sample(x, x.shape[1], w, w.shape[1], x.shape[1], rows, cols, rows.shape[0], out)
+        return out
+
+    def quantize_group_s8(self, w):
+        w = f32(w)
+        n, k = w.shape
+        q = np.zeros((n, k), np.int8)
+        s = np.zeros((n, k // 128), np.float32)
+        if self.lib.oracle_quantize_group_s8(w, k, q, k, s, k // 128, n, k) != 0:
+            raise ValueError("K must be a multiple of 128")
+        return q, s
+
+    def dequant_group_s8(self, q, s) -> np.ndarray:
+        q = np.ascontiguousarray(q, np.int8)
+        s = f32(s)
+        n, k = q.shape
+        wd = np.zeros((n, k), np.float32)
+        self.lib.oracle_dequant_group_s8(q, k, s, s.shape[1], wd, k, n, k)
+        return wd
+
+    def swiglu_packed(self, acc, inter: int) -> np.ndarray:
+        acc = f32(acc)
+        t = acc.shape[0]
+        out = np.zeros((t, inter), np.float32)
+        self.lib.oracle_swiglu_packed(acc, acc.shape[1], out, inter, t, inter)
+        return out
+
+    def pack_gate_up(self, gate, up) -> np.ndarray:
+        """[gate; up] -> the packed row order of the fused SwiGLU multiply (blocks of 64 gate rows, 64 up rows)."""
+        gate, up = np.asarray(gate), np.asarray(up)
+        inter = gate.shape[0]
+        stacked = np.concatenate([gate, up], axis=0)
+        src = np.array([self.lib.oracle_pack_gate_up_source(p, inter) for p in range(2 * inter)], np.int64)
+        return np.ascontiguousarray(stacked[src])
+
+    def add(self, y, acc) -> np.ndarray:
+        y = f32(y).copy()
+        acc = f32(acc)
+        self.lib.oracle_add(y, y.shape[1], acc, acc.shape[1], y.shape[0], y.shape[1])
+        return y
+
+    def rmsnorm(self, x, w, eps: float = 1e-6) -> np.ndarray:
+        x, w = f32(x), f32(w)
+        y = np.zeros_like(x)
+        self.lib.oracle_rmsnorm(x, x.shape[1], y, x.shape[1], x.shape[0], x.shape[1], w, eps)
+        return y
+
+    def to_f16_grid(self, a) -> np.ndarray:
+        """Round float32 values to binary16 and back (numpy's conversion is round-to-nearest-even, as the oracle's scalar one)."""
+        return f32(a).astype(np.float16).astype(np.float32)
+
+    def to_bf16_grid(self, a) -> np.ndarray:
+        bits = f32(a).view(np.uint32).astype(np.uint64)
+        nan = (bits & 0x7FFFFFFF) > 0x7F800000
+        rounded = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16
+        rounded = np.where(nan, ((bits >> 16) | 0x40) << 16, rounded)
+        return rounded.astype(np.uint32).view(np.float32).reshape(np.shape(a))
+
+
+class Ref:
+    """The reference's own CPU GEMM (compiled from its sources). `available()` is False where it was never built."""
+
+    KINDS = {"f32": 0, "bf16": 1, "i8": 2}
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(REF_SO)
+
+    def __init__(self) -> None:
+        if not self.available():
+            raise RuntimeError("oracle/_ref/libsepal_ref.so is not built (needs the reference tree: make -C oracle ref)")
+        L = self.lib = C.CDLL(REF_SO)
+        L.ref_last_error.restype = C.c_char_p
+        L.ref_pool_threads.restype = C.c_uint
+        L.ref_pool_threads.argtypes = [C.c_uint]
+        L.ref_variant_name.restype = C.c_char_p
+        L.ref_variant_name.argtypes = [C.c_int, C.c_char_p]
+        L.ref_cpu_brand.restype = C.c_char_p
+        L.ref_float_to_bf16.restype = C.c_uint16
+        L.ref_float_to_bf16.argtypes = [C.c_float]
+        L.ref_cpu_gemm.restype = C.c_int
+        L.ref_cpu_gemm.argtypes = [C.c_int, C.c_char_p, C.c_uint, _f32p, _sz, _sz, _sz, _f32p, _sz, _sz, _f32p, _sz, C.c_int]
+        L.ref_cpu_gemm_swiglu.restype = C.c_int
+        L.ref_cpu_gemm_swiglu.argtypes = [C.c_int, C.c_char_p, C.c_uint, _f32p, _sz, _sz, _sz, _f32p, _f32p, _sz, _sz, _f32p, _sz]
+        L.ref_pack.restype = C.c_void_p
+        L.ref_pack.argtypes = [C.c_int, C.c_char_p, C.c_uint, _f32p, _sz, _sz, _sz]
+        L.ref_packed_free.argtypes = [C.c_void_p]
+        L.ref_packed_run.restype = C.c_int
+        L.ref_packed_run.argtypes = [C.c_void_p, C.c_uint, _f32p, _sz, _sz, _f32p, _sz, C.c_int, _f64p]
+        L.ref_gemm_f64acc.restype = C.c_int
+        L.ref_gemm_f64acc.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, _sz, _sz, _sz, _f32p, C.c_float]
+        L.ref_rmsnorm_rows.restype = C.c_int
+        L.ref_rmsnorm_rows.argtypes = [C.c_uint, _f32p, _sz, _f32p, _sz, _sz, _sz, _f32p, C.c_double]
+
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise RuntimeError(self.lib.ref_last_error().decode())
+
+    def threads(self, threads: int = 0) -> int:
+        return int(self.lib.ref_pool_threads(threads))
+
+    def variant(self, kind: str = "bf16", isa: str = "") -> str:
+        return self.lib.ref_variant_name(self.KINDS[kind], isa.encode()).decode()
+
+    def brand(self) -> str:
+        return self.lib.ref_cpu_brand().decode()
+
+    def cpu_gemm(self, x, w, kind: str = "bf16", isa: str = "", threads: int = 0, y0=None) -> np.ndarray:
+        x, w = f32(x), f32(w)
+        t, k = x.shape
+        n = w.shape[0]
+        y = np.zeros((t, n), np.float32) if y0 is None else f32(y0).copy()
+        self._check(self.lib.ref_cpu_gemm(self.KINDS[kind], isa.encode(), threads, x, k, t, k, w, k, n, y, n, 0 if y0 is None else 1))
+        return y
+
+    def cpu_gemm_swiglu(self, x, gate, up, kind: str = "bf16", isa: str = "", threads: int = 0) -> np.ndarray:
+        x, gate, up = f32(x), f32(gate), f32(up)
+        t, k = x.shape
+        n = gate.shape[0]
+        y = np.zeros((t, n), np.float32)
+        self._check(self.lib.ref_cpu_gemm_swiglu(self.KINDS[kind], isa.encode(), threads, x, k, t, k, gate, up, k, n, y, n))
+        return y
+
+    def gemm_f64acc(self, x, w, beta: float = 0.0, y0=None) -> np.ndarray:
+        """The reference provider; x and w may be float32 or float16 arrays."""
+        codes = {np.dtype(np.float32): 0, np.dtype(np.float16): 1}
+        x = np.ascontiguousarray(x)
+        w = np.ascontiguousarray(w)
+        t, k = x.shape
+        n = w.shape[0]
+        y = np.zeros((t, n), np.float32) if y0 is None else f32(y0).copy()
+        self._check(self.lib.ref_gemm_f64acc(x.ctypes.data, codes[x.dtype], w.ctypes.data, codes[w.dtype], t, n, k, y, beta))
+        return y
+
+    def rmsnorm_rows(self, x, w1, eps: float = 1e-6, threads: int = 0) -> np.ndarray:
+        x, w1 = f32(x), f32(w1)
+        y = np.zeros_like(x)
+        self._check(self.lib.ref_rmsnorm_rows(threads, x, x.shape[1], y, x.shape[1], x.shape[0], x.shape[1], w1, eps))
+        return y
+
+    def time_gemm(self, x, w, kind: str = "bf16", isa: str = "", threads: int = 0, reps: int = 5):
+        """(pack seconds, product seconds) per repeat, weights packed once, as the reference's own bench times it."""
+        x, w = f32(x), f32(w)
+        t, k = x.shape
+        n = w.shape[0]
+        handle = self.lib.ref_pack(self.KINDS[kind], isa.encode(), threads, w, k, n, k)
+        if not handle:
+            raise RuntimeError(self.lib.ref_last_error().decode())
+        y = np.zeros((t, n), np.float32)
+        out = []
+        sec = np.zeros(2, np.float64)
+        try:
+            for _ in range(reps):
+                self._check(self.lib.ref_packed_run(handle, threads, x, k, t, y, n, 0, sec))
+                out.append((float(sec[0]), float(sec[1])))
+        finally:
+            self.lib.ref_packed_free(handle)
+        return out, y

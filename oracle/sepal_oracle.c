@@ -1,0 +1,277 @@
+/* TEST INFRASTRUCTURE, not product code: the CPU restatement ("oracle") of the arithmetic of Sepal-Runner's trunk
+ * projection GEMMs. Only tests, the smoke check and the benchmark's CPU-baseline leg may load this library; the product
+ * (the CUDA kernels behind include/sepal_b200.h) never calls it and has no CPU fallback.
+ *
+ * Parity pin: every function here is checked (tests/test_oracle.py) against the reference's own code compiled from its
+ * sources (oracle/_ref/libsepal_ref.so: gemm_packed, the float64 reference provider, rmsnorm_rows, float_to_bf16) and
+ * against fixtures that library produced (tests/golden/), plus the bounds and host emulations the reference's tests state.
+ *
+ * Paths are relative to the reference project root. Plain C11, no dependency besides libm and pthreads (threads only
+ * spread independent rows; they change no result).
+ */
+#define _GNU_SOURCE
+#include <math.h>
+#include <pthread.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <string.h>
+#include <unistd.h>
+
+/* ---- rows spread over the host's cores ------------------------------------------------------------------------------- */
+
+typedef void (*row_fn)(void* ctx, size_t begin, size_t end);
+struct row_job {
+    row_fn fn;
+    void* ctx;
+    size_t begin, end;
+};
+static void* row_job_main(void* p) {
+    struct row_job* j = (struct row_job*)p;
+    j->fn(j->ctx, j->begin, j->end);
+    return NULL;
+}
+static void for_rows(size_t rows, row_fn fn, void* ctx) {
+    long cores = sysconf(_SC_NPROCESSORS_ONLN);
+    size_t threads = cores < 1 ? 1 : cores > 64 ? 64 : (size_t)cores;
+    if (threads > rows) threads = rows;
+    if (threads <= 1) {
+        fn(ctx, 0, rows);
+        return;
+    }
+    pthread_t ids[64];
+    struct row_job jobs[64];
+    size_t started = 0;
+    for (size_t i = 0; i < threads; ++i) {
+        jobs[i].fn = fn;
+        jobs[i].ctx = ctx;
+        jobs[i].begin = rows * i / threads;
+        jobs[i].end = rows * (i + 1) / threads;
+    }
+    for (size_t i = 0; i < threads; ++i) {
+        if (pthread_create(&ids[i], NULL, row_job_main, &jobs[i]) != 0) break;
+        ++started;
+    }
+    for (size_t i = started; i < threads; ++i) fn(ctx, jobs[i].begin, jobs[i].end); /* could not start: run here */
+    for (size_t i = 0; i < started; ++i) pthread_join(ids[i], NULL);
+}
+
+/* ---- 16-bit formats ------------------------------------------------------------------------------------------------ */
+
+static uint32_t f32_bits(float x) {
+    uint32_t b;
+    memcpy(&b, &x, 4);
+    return b;
+}
+static float bits_f32(uint32_t b) {
+    float x;
+    memcpy(&x, &b, 4);
+    return x;
+}
+
+/* bfloat16 of a float32, round to nearest even, NaN kept quiet: runner/src/cpu/gemm.cpp:73-78 (the CPU packers) and
+ * runner/cuda/src/gemm_simt_kernels.cu:288-297 (the device converter) use the same rule. */
+uint16_t oracle_f32_to_bf16(float x) {
+    const uint32_t bits = f32_bits(x);
+    if ((bits & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((bits >> 16) | 0x0040u);
+    return (uint16_t)((bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16);
+}
+float oracle_bf16_to_f32(uint16_t b) { return bits_f32((uint32_t)b << 16); }
+
+/* binary16 -> float32, exact (runner/include/sepal/dtype.hpp:33-63 decodes the same way). */
+float oracle_f16_to_f32(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    const uint32_t exp = (h >> 10) & 0x1Fu;
+    const uint32_t man = h & 0x3FFu;
+    if (exp == 0) {
+        if (man == 0) return bits_f32(sign);
+        /* subnormal: man * 2^-24 */
+        const float v = (float)man * 5.9604644775390625e-8f;
+        return sign ? -v : v;
+    }
+    if (exp == 31) return bits_f32(sign | 0x7F800000u | (man << 13));
+    return bits_f32(sign | ((exp + 112u) << 23) | (man << 13));
+}
+
+/* float32 -> binary16, round to nearest even, overflow to infinity: what __float2half_rn does on the device, the rounding
+ * every f16 operand and f16 result of the engine goes through (runner/cuda/src/kernels_elementwise.hpp:12-14). */
+uint16_t oracle_f32_to_f16(float x) {
+    const uint32_t bits = f32_bits(x);
+    const uint16_t sign = (uint16_t)((bits >> 16) & 0x8000u);
+    const uint32_t a = bits & 0x7FFFFFFFu;
+    if (a > 0x7F800000u) return (uint16_t)(sign | 0x7E00u); /* NaN */
+    if (a >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u); /* >= 65520 rounds to infinity */
+    if (a < 0x33000001u) return sign;                        /* <= 2^-25 rounds to zero (ties to even) */
+    const int32_t e = (int32_t)(a >> 23) - 127;
+    uint32_t man = (a & 0x7FFFFFu) | 0x800000u;
+    int shift;
+    uint32_t base;
+    if (e < -14) { /* subnormal result */
+        shift = 13 + (-14 - e);
+        base = 0;
+    } else {
+        shift = 13;
+        base = (uint32_t)(e + 15) << 10;
+        man &= 0x7FFFFFu;
+    }
+    const uint32_t kept = man >> shift;
+    const uint32_t rest = man & ((1u << shift) - 1u);
+    const uint32_t half = 1u << (shift - 1);
+    uint32_t out = base + kept;
+    if (rest > half || (rest == half && (kept & 1u))) out += 1; /* a carry into the exponent is the right answer */
+    return (uint16_t)(sign | out);
+}
+
+/* ---- the product --------------------------------------------------------------------------------------------------- */
+
+/* Y[t, n] = beta Y[t, n] + sum_k X[t, k] W[n, k], accumulated in float64 over k = 0 .. K-1 in that order and rounded to
+ * float32 once: the reference provider, runner/src/provider/gemm_ref.cpp:58-78. X [T, K] stride ldx, W [N, K] stride ldw,
+ * Y [T, N] stride ldy, all float32 (16-bit operands are widened exactly by the caller, as F32Matrix does there). */
+struct gemm_args {
+    const float *x, *w;
+    float* y;
+    size_t ldx, ldw, ldy, n, k;
+    float beta;
+};
+static void gemm_f64acc_rows(void* p, size_t begin, size_t end) {
+    const struct gemm_args* a = (const struct gemm_args*)p;
+    for (size_t r = begin; r < end; ++r) {
+        const float* xr = a->x + r * a->ldx;
+        for (size_t c = 0; c < a->n; ++c) {
+            const float* wr = a->w + c * a->ldw;
+            double acc = 0.0;
+            for (size_t i = 0; i < a->k; ++i) acc += (double)xr[i] * (double)wr[i];
+            float* out = a->y + r * a->ldy + c;
+            if (a->beta != 0.0f) acc += (double)a->beta * (double)*out;
+            *out = (float)acc;
+        }
+    }
+}
+void oracle_gemm_f64acc(const float* x, size_t ldx, const float* w, size_t ldw, float* y, size_t ldy, size_t t, size_t n, size_t k, float beta) {
+    struct gemm_args a = {x, w, y, ldx, ldw, ldy, n, k, beta};
+    for_rows(t, gemm_f64acc_rows, &a);
+}
+
+/* The schedule of the reference's float32 kernels: one chain acc = fma(X[t, k], Wd[n, k], acc) for k = 0 .. K-1 from 0.
+ * The SIMT GPU kernel is tested bit for bit against exactly this (runner/cuda/tests/test_gemm_simt_kernels.cpp:149-153)
+ * and the CPU bf16 AVX2 kernels are modelled by it (runner/tests/test_cpu_gemm.cpp:385-397). */
+static void gemm_fma_chain_rows(void* p, size_t begin, size_t end) {
+    const struct gemm_args* a = (const struct gemm_args*)p;
+    for (size_t r = begin; r < end; ++r) {
+        const float* xr = a->x + r * a->ldx;
+        for (size_t c = 0; c < a->n; ++c) {
+            const float* wr = a->w + c * a->ldw;
+            float acc = 0.0f;
+            for (size_t i = 0; i < a->k; ++i) acc = fmaf(xr[i], wr[i], acc);
+            a->y[r * a->ldy + c] = acc;
+        }
+    }
+}
+void oracle_gemm_fma_chain(const float* x, size_t ldx, const float* w, size_t ldw, float* y, size_t ldy, size_t t, size_t n, size_t k) {
+    struct gemm_args a = {x, w, y, ldx, ldw, ldy, n, k, 0.0f};
+    for_rows(t, gemm_fma_chain_rows, &a);
+}
+
+/* A sample of the float64-accumulated product: out[i] = sum_k X[rows[i], k] W[cols[i], k] (as double), for checking a
+ * full-size result at a few thousand places without computing all of it. */
+struct sample_args {
+    const float *x, *w;
+    size_t ldx, ldw, k;
+    const uint32_t *rows, *cols;
+    double* out;
+};
+static void sample_rows(void* p, size_t begin, size_t end) {
+    const struct sample_args* a = (const struct sample_args*)p;
+    for (size_t i = begin; i < end; ++i) {
+        const float* xr = a->x + (size_t)a->rows[i] * a->ldx;
+        const float* wr = a->w + (size_t)a->cols[i] * a->ldw;
+        double acc = 0.0;
+        for (size_t j = 0; j < a->k; ++j) acc += (double)xr[j] * (double)wr[j];
+        a->out[i] = acc;
+    }
+}
+void oracle_gemm_f64acc_sample(const float* x, size_t ldx, const float* w, size_t ldw, size_t k, const uint32_t* rows, const uint32_t* cols,
+                               size_t count, double* out) {
+    struct sample_args a = {x, w, ldx, ldw, k, rows, cols, out};
+    for_rows(count, sample_rows, &a);
+}
+
+/* ---- int8 weights, one float32 scale per output row and group of 128 values of k ---------------------------------------- */
+
+/* The group quantiser, runner/cuda/src/gemm_simt_kernels.cu:267-286 (host twin: runner/cuda/tests/test_gemm_simt_kernels.cpp:73-90):
+ * scale = max|w| / 127 (IEEE float division), q = clamp(rint(w / scale), -127, 127); an all-zero group gets scale 0, q 0.
+ * src [rows, K] stride ld_src; q [rows, K] stride ld_q bytes; s [rows, K/128] stride ld_s. K a multiple of 128. */
+int oracle_quantize_group_s8(const float* src, size_t ld_src, int8_t* q, size_t ld_q, float* s, size_t ld_s, size_t rows, size_t k) {
+    if (k % 128 != 0) return 1;
+    const size_t groups = k / 128;
+    for (size_t r = 0; r < rows; ++r) {
+        for (size_t g = 0; g < groups; ++g) {
+            const float* v = src + r * ld_src + g * 128;
+            float m = 0.0f;
+            for (int i = 0; i < 128; ++i) m = fmaxf(m, fabsf(v[i]));
+            const float scale = m / 127.0f;
+            s[r * ld_s + g] = scale;
+            for (int i = 0; i < 128; ++i) {
+                int out = 0;
+                if (scale > 0.0f) {
+                    const float rr = nearbyintf(v[i] / scale); /* default rounding mode: to nearest even, as rintf on the device */
+                    out = (int)fminf(fmaxf(rr, -127.0f), 127.0f);
+                }
+                q[r * ld_q + g * 128 + (size_t)i] = (int8_t)out;
+            }
+        }
+    }
+    return 0;
+}
+
+/* Wd[n, k] = float32(q[n, k]) * s[n, k / 128], one float32 multiplication (runner/cuda/src/gemm_simt_kernels.cu:175-177,
+ * runner/cuda/src/gemm_simt_kernels.hpp:9-11): "the reference's dequantised product" multiplies X by this matrix. */
+void oracle_dequant_group_s8(const int8_t* q, size_t ld_q, const float* s, size_t ld_s, float* wd, size_t ld_wd, size_t rows, size_t k) {
+    for (size_t r = 0; r < rows; ++r)
+        for (size_t i = 0; i < k; ++i) wd[r * ld_wd + i] = (float)q[r * ld_q + i] * s[r * ld_s + i / 128];
+}
+
+/* ---- epilogues ----------------------------------------------------------------------------------------------------- */
+
+/* silu(g) * u as the engine's kernels compute it, runner/cuda/src/kernels_elementwise.cu:248-264 and
+ * runner/cuda/src/gemm_simt_kernels.cu:28-29: softplus(x) = max(x, 0) + log1p(exp(-|x|)), silu(x) = x exp(-softplus(-x)),
+ * two float32 multiplications. (The device's expf / log1pf may differ from libm's by an ulp: compare with a tolerance.) */
+float oracle_swiglu(float g, float u) {
+    const float sp = fmaxf(-g, 0.0f) + log1pf(expf(-fabsf(-g)));
+    return (g * expf(-sp)) * u;
+}
+
+/* Row of the stacked [gate; up] matrix (gate rows 0 .. I-1, up rows I .. 2I-1) that packed row p holds when gate and up are
+ * interleaved in blocks of 64 for the fused SwiGLU multiply: runner/cuda/src/gemm_simt_kernels.hpp:72-77. */
+size_t oracle_pack_gate_up_source(size_t p, size_t inter) {
+    const size_t b = p / 128, r = p % 128;
+    return r < 64 ? 64 * b + r : inter + 64 * b + (r - 64);
+}
+
+/* The fused SwiGLU epilogue on a packed product: acc is [T, 2I] (stride ld_acc) in the packed row order above,
+ * out[t, 64 b + r] = swiglu(acc[t, 128 b + r], acc[t, 128 b + 64 + r]) (runner/cuda/src/gemm_simt_kernels.cu:207-214). */
+void oracle_swiglu_packed(const float* acc, size_t ld_acc, float* out, size_t ld_out, size_t t, size_t inter) {
+    for (size_t r = 0; r < t; ++r)
+        for (size_t c = 0; c < inter; ++c) {
+            const size_t b = c / 64, i = c % 64;
+            out[r * ld_out + c] = oracle_swiglu(acc[r * ld_acc + 128 * b + i], acc[r * ld_acc + 128 * b + 64 + i]);
+        }
+}
+
+/* The residual epilogue: Y = Y + acc, one float32 addition per element (runner/cuda/src/gemm_simt_kernels.cu:223-226,
+ * runner/cuda/src/kernels_elementwise.hpp:48-53). */
+void oracle_add(float* y, size_t ld_y, const float* acc, size_t ld_acc, size_t t, size_t n) {
+    for (size_t r = 0; r < t; ++r)
+        for (size_t c = 0; c < n; ++c) y[r * ld_y + c] = y[r * ld_y + c] + acc[r * ld_acc + c];
+}
+
+/* Zero-centred RMSNorm of a row: y = x / sqrt(mean(x^2) + eps) * (1 + w), runner/cuda/src/kernels_elementwise.hpp:41-46
+ * (CPU twin runner/src/cpu/elementwise.cpp:43-59, which takes w1 = 1 + w). The mean is taken in float64 here; the
+ * reference kernels sum in float32 in a fixed order, so compare with a tolerance. */
+void oracle_rmsnorm(const float* x, size_t ldx, float* y, size_t ldy, size_t rows, size_t cols, const float* w, double eps) {
+    for (size_t r = 0; r < rows; ++r) {
+        double ss = 0.0;
+        for (size_t c = 0; c < cols; ++c) ss += (double)x[r * ldx + c] * (double)x[r * ldx + c];
+        const float inv = (float)(1.0 / sqrt(ss / (double)cols + eps));
+        for (size_t c = 0; c < cols; ++c) y[r * ldy + c] = (x[r * ldx + c] * inv) * (1.0f + w[c]);
+    }
+}

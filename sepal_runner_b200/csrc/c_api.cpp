@@ -1,0 +1,196 @@
+// The C ABI (include/sepal_b200.h): argument checks, exception -> error string, nothing else. Modelled on the engine's own
+// boundary file (runner/src/capi/c_api.cpp:28-43: thread-local message, every entry point wrapped).
+#include "../../include/sepal_b200.h"
+
+#include <cstring>
+#include <exception>
+#include <new>
+#include <string>
+
+#include "gemm.hpp"
+#include "provider.hpp"
+
+using namespace sepal::b200;
+
+struct sepal_b200_ctx {
+    Context ctx;
+    sepal_b200_ctx(int device, std::size_t bytes) : ctx(device, bytes) {}
+};
+struct sepal_b200_provider {
+    B200Gemm gemm;
+    sepal_b200_provider(int device, std::size_t bytes) : gemm(device, bytes) {}
+};
+
+namespace {
+
+thread_local std::string g_error;
+
+template <class F>
+int32_t guarded(F&& f) noexcept {
+    try {
+        f();
+        g_error.clear();
+        return 0;
+    } catch (const std::exception& e) {
+        g_error = e.what();
+    } catch (...) {
+        g_error = "unknown error";
+    }
+    return 1;
+}
+
+Epilogue epilogue_of(int32_t e) {
+    if (e < 0 || e > 2) throw std::invalid_argument("epilogue must be 0 (store), 1 (add) or 2 (swiglu)");
+    return static_cast<Epilogue>(e);
+}
+HostType host_type_of(int32_t t) {
+    if (t != SEPAL_B200_F32 && t != SEPAL_B200_F16) throw std::invalid_argument("element type must be 0 (float32) or 1 (binary16)");
+    return static_cast<HostType>(t);
+}
+void require(const void* p, const char* what) {
+    if (p == nullptr) throw std::invalid_argument(std::string(what) + " is null");
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t sepal_b200_api_version(void) { return 1; }
+
+const char* sepal_b200_last_error(void) { return g_error.c_str(); }
+
+int32_t sepal_b200_open(int32_t device, uint64_t workspace_bytes, sepal_b200_ctx** out) {
+    if (out != nullptr) *out = nullptr;
+    return guarded([&] {
+        require(out, "out");
+        *out = new sepal_b200_ctx(device, static_cast<std::size_t>(workspace_bytes));
+    });
+}
+
+void sepal_b200_close(sepal_b200_ctx* ctx) { delete ctx; }
+
+int32_t sepal_b200_info(sepal_b200_ctx* ctx, char* buffer, uint64_t capacity, uint64_t* needed) {
+    return guarded([&] {
+        require(ctx, "ctx");
+        const Context& c = ctx->ctx;
+        const std::string json = std::string("{\"library\":\"sepal_b200\",\"api_version\":1,\"device\":") + std::to_string(c.device) +
+                                 ",\"compute_capability\":\"" + std::to_string(c.compute_major) + "." + std::to_string(c.compute_minor) +
+                                 "\",\"sm_count\":" + std::to_string(c.sm_count) + ",\"workspace_bytes\":" + std::to_string(c.scratch.partial_bytes) +
+                                 ",\"kernels\":[\"gemm_tc_kernel<BN,W8> (tcgen05.mma kind::f16, TMA, TMEM)\",\"quantize_group_s8_kernel\","
+                                 "\"prepare_scales_kernel\",\"pack_gate_up_kernel\"],\"fallback\":\"none\"}";
+        if (needed != nullptr) *needed = json.size() + 1;
+        if (buffer == nullptr || capacity < json.size() + 1) throw std::length_error("buffer too small: " + std::to_string(json.size() + 1) + " bytes needed");
+        std::memcpy(buffer, json.c_str(), json.size() + 1);
+    });
+}
+
+int32_t sepal_b200_status(sepal_b200_ctx* ctx, void* stream, int32_t* status_out) {
+    return guarded([&] {
+        require(ctx, "ctx");
+        require(status_out, "status_out");
+        check(cudaSetDevice(ctx->ctx.device), "cudaSetDevice");
+        *status_out = ctx->ctx.read_status(static_cast<cudaStream_t>(stream));
+    });
+}
+
+uint64_t sepal_b200_take_launch_count(void) { return take_launch_count(); }
+
+int32_t sepal_b200_gemm_f16(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const void* w, uint64_t ld_w, void* y, uint64_t ld_y, int32_t y_half,
+                            uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t config, void* stream) {
+    return guarded([&] {
+        require(ctx, "ctx");
+        launch_gemm_f16(ctx->ctx, x, ld_x, w, ld_w, y, ld_y, y_half != 0, t, n, k, epilogue_of(epilogue), config, static_cast<cudaStream_t>(stream));
+    });
+}
+
+int32_t sepal_b200_gemm_w8g(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const int8_t* q, uint64_t ld_q, const void* scales_t, uint64_t ld_st,
+                            const float* descale, void* y, uint64_t ld_y, int32_t y_half, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue,
+                            int32_t config, void* stream) {
+    return guarded([&] {
+        require(ctx, "ctx");
+        W8gMatrix m;
+        m.q = q;
+        m.ld_q = ld_q;
+        m.scales_t = scales_t;
+        m.ld_st = ld_st;
+        m.descale = descale;
+        launch_gemm_w8g(ctx->ctx, x, ld_x, m, y, ld_y, y_half != 0, t, n, k, epilogue_of(epilogue), config, static_cast<cudaStream_t>(stream));
+    });
+}
+
+int32_t sepal_b200_quantize_group_s8(const float* src, uint64_t ld_src, int8_t* q, uint64_t ld_q, float* s, uint64_t ld_s, uint64_t rows, uint64_t k,
+                                     void* stream) {
+    return guarded([&] { launch_quantize_group_s8(src, ld_src, q, ld_q, s, ld_s, rows, k, static_cast<cudaStream_t>(stream)); });
+}
+
+int32_t sepal_b200_prepare_w8g_scales(const float* s, uint64_t ld_s, uint64_t n, uint64_t groups, void* scales_t, uint64_t ld_st, float* descale,
+                                      uint32_t* max_bits, void* stream) {
+    return guarded([&] { launch_prepare_w8g_scales(s, ld_s, n, groups, scales_t, ld_st, descale, max_bits, static_cast<cudaStream_t>(stream)); });
+}
+
+int32_t sepal_b200_pack_gate_up(const void* src, uint64_t src_stride_bytes, void* dst, uint64_t dst_stride_bytes, uint64_t inter, uint64_t row_bytes,
+                                void* stream) {
+    return guarded([&] { launch_pack_gate_up(src, src_stride_bytes, dst, dst_stride_bytes, inter, row_bytes, static_cast<cudaStream_t>(stream)); });
+}
+
+int32_t sepal_b200_float_to_half(const float* src, void* dst, uint64_t count, void* stream) {
+    return guarded([&] {
+        if (count != 0) {
+            require(src, "src");
+            require(dst, "dst");
+        }
+        launch_float_to_half(src, dst, count, static_cast<cudaStream_t>(stream));
+    });
+}
+int32_t sepal_b200_half_to_float(const void* src, float* dst, uint64_t count, void* stream) {
+    return guarded([&] {
+        if (count != 0) {
+            require(src, "src");
+            require(dst, "dst");
+        }
+        launch_half_to_float(src, dst, count, static_cast<cudaStream_t>(stream));
+    });
+}
+
+int32_t sepal_b200_provider_open(int32_t device, uint64_t arena_bytes, sepal_b200_provider** out) {
+    if (out != nullptr) *out = nullptr;
+    return guarded([&] {
+        require(out, "out");
+        *out = new sepal_b200_provider(device, static_cast<std::size_t>(arena_bytes));
+    });
+}
+void sepal_b200_provider_close(sepal_b200_provider* provider) { delete provider; }
+
+int32_t sepal_b200_provider_upload_weights(sepal_b200_provider* provider, const void* w, int32_t dtype, uint64_t n, uint64_t k, uint32_t* id_out) {
+    return guarded([&] {
+        require(provider, "provider");
+        require(id_out, "id_out");
+        *id_out = provider->gemm.upload_weights(w, host_type_of(dtype), n, k).index;
+    });
+}
+int32_t sepal_b200_provider_upload_weights_w8g(sepal_b200_provider* provider, const float* w, uint64_t n, uint64_t k, uint32_t* id_out) {
+    return guarded([&] {
+        require(provider, "provider");
+        require(id_out, "id_out");
+        *id_out = provider->gemm.upload_weights_w8g(w, n, k).index;
+    });
+}
+int32_t sepal_b200_provider_gemm_f(sepal_b200_provider* provider, const void* x, int32_t x_dtype, uint64_t t, uint32_t weight_id, float* y, float beta) {
+    return guarded([&] {
+        require(provider, "provider");
+        provider->gemm.gemm_f(x, host_type_of(x_dtype), t, WeightId{weight_id}, y, beta);
+    });
+}
+
+int32_t sepal_b200_host_alloc(uint64_t bytes, void** out) {
+    if (out != nullptr) *out = nullptr;
+    return guarded([&] {
+        require(out, "out");
+        check(cudaMallocHost(out, bytes), "cudaMallocHost");
+    });
+}
+void sepal_b200_host_free(void* ptr) {
+    if (ptr != nullptr) (void)cudaFreeHost(ptr);
+}
+
+}  // extern "C"

@@ -1,0 +1,706 @@
+// The trunk projection GEMM for sm_100a: Y = epilogue(X W^T) with binary16 operands on the 5th-generation tensor cores.
+//
+// One persistent CTA per SM, specialised by warp:
+//   warp 0      TMA producer: streams [128 x 64] tiles of X and [BN x 64] tiles of W into a ring of shared-memory stages
+//               (cp.async.bulk.tensor, 128-byte swizzle, completion counted on an mbarrier per stage). No cluster multicast.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M 128, N BN, K 16, kind::f16, float32 accumulator in tensor memory),
+//               four per stage; tcgen05.commit frees the stage and, after the last one of a work unit, hands the accumulator over.
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32 lanes), apply Store / Add / SwiGLU, write Y. Two accumulators
+//               (2 x BN columns of tensor memory) alternate, so the epilogue of one unit overlaps the MMAs of the next.
+//   warps 6..9  (int8 weights only) converters: widen a raw int8 W tile exactly to binary16, multiply by the group's scale and store
+//               it in the swizzled layout the MMA reads (see the W8 notes below).
+//
+// Work is cut into units (tile, k range). With the even split (stream-k) every CTA gets the same number of k iterations; a tile
+// shared by several CTAs is summed by whichever of them finishes last, always in k order, so the result does not depend on timing.
+// No CTA ever waits for another CTA.
+//
+// Every wait on an mbarrier is bounded: when it runs out the CTA raises a flag in shared memory, records a code in the context's
+// status word, lets the copies it has in flight land, frees its tensor memory and returns. The host reads the word with
+// sepal_b200_status.
+#include "gemm.hpp"
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "ptx.cuh"
+
+namespace sepal::b200 {
+
+namespace {
+
+thread_local std::uint64_t g_launches = 0;
+
+constexpr int kBM = 128;  // rows of X per tile = lanes of the accumulator
+constexpr int kBK = 64;   // values of k per stage: 128 bytes of binary16, one swizzle row
+constexpr long long kWaitLimit = 1ll << 30;  // clock cycles (about half a second) before a wait gives up
+
+// Status codes (low byte); the CTA index is in the bits above.
+constexpr int kStatusProducerEmpty = 1, kStatusMmaFull = 2, kStatusMmaAccEmpty = 3, kStatusEpilogueAccFull = 4, kStatusConvFull = 5,
+              kStatusConvEmpty = 6, kStatusMmaConvFull = 7;
+
+struct GemmParams {
+    void* y;
+    unsigned long long ld_y;
+    unsigned m, n, k;                       // rows of X, rows of W (packed width for SwiGLU), depth
+    unsigned m_tiles, n_tiles, k_iters, tiles;
+    unsigned epilogue, y_half, vec_ok;      // vec_ok: Y rows allow 16-byte accesses
+    unsigned stream_k;                      // 0: whole tiles round-robin; 1: all k iterations split evenly over the CTAs
+    float* partials;
+    unsigned* counters;
+    int* status;
+    const __half* scales_t;                 // W8: [K / 128][ld_st] prepared scales (group-major)
+    unsigned long long ld_st;
+    const float* descale;                   // W8: device scalar the sums are multiplied by
+};
+
+template <int BN, bool W8>
+struct Shape {
+    static constexpr int kStages = W8 ? 4 : (BN == 256 ? 4 : 6);
+    static constexpr int kXBytes = kBM * kBK * 2;
+    static constexpr int kWBytes = W8 ? BN * kBK : BN * kBK * 2;  // raw tile as it comes from memory
+    static constexpr int kStageBytes = kXBytes + kWBytes;
+    static constexpr int kConvBytes = W8 ? BN * kBK * 2 : 0;       // one converted W tile
+    static constexpr int kConvBuffers = W8 ? 2 : 0;
+    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kBarriers = 2 * kStages + 4 + 2 * 2;
+    static constexpr int kThreads = W8 ? 320 : 192;
+    static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kConvBuffers * kConvBytes + kBarriers * 8 + 64;
+};
+
+// A CTA's list of work units.
+struct Walker {
+    unsigned cur, end, step, k_iters;
+    bool stream_k;
+    __device__ Walker(const GemmParams& p, unsigned cta, unsigned grid) : k_iters(p.k_iters), stream_k(p.stream_k != 0) {
+        if (stream_k) {
+            const unsigned long long total = static_cast<unsigned long long>(p.tiles) * p.k_iters;
+            cur = static_cast<unsigned>(total * cta / grid);
+            end = static_cast<unsigned>(total * (cta + 1) / grid);
+            step = 0;
+        } else {
+            cur = cta;
+            end = p.tiles;
+            step = grid;
+        }
+    }
+    __device__ bool next(unsigned& tile, unsigned& kb, unsigned& ke) {
+        if (cur >= end) return false;
+        if (stream_k) {
+            tile = cur / k_iters;
+            kb = cur - tile * k_iters;
+            const unsigned len = min(k_iters - kb, end - cur);
+            ke = kb + len;
+            cur += len;
+        } else {
+            tile = cur;
+            kb = 0;
+            ke = k_iters;
+            cur += step;
+        }
+        return true;
+    }
+};
+
+__device__ __forceinline__ unsigned range_lo(unsigned long long total, unsigned cta, unsigned grid) {
+    return static_cast<unsigned>(total * cta / grid);
+}
+
+// Bounded wait. Returns false when the CTA is giving up (this wait ran out, or another role already raised the flag).
+__device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, volatile unsigned* abort_flag, int* status, int code) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    for (;;) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 31u) == 0) {
+            if (*abort_flag != 0) return false;
+            if (clock64() - t0 > kWaitLimit) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code | (static_cast<int>(blockIdx.x) << 8));
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// silu(g) * u as the reference's kernels compute it (runner/cuda/src/kernels_elementwise.cu:248-264): softplus(x) = max(x, 0) +
+// log1p(exp(-|x|)), silu(x) = x exp(-softplus(-x)), every product rounded to nearest.
+__device__ __forceinline__ float swiglu(float g, float u) {
+    const float sp = fmaxf(-g, 0.0f) + log1pf(expf(-fabsf(g)));
+    return __fmul_rn(__fmul_rn(g, expf(-sp)), u);
+}
+
+// Writes 32 consecutive results of one row. `col` is the first output column; columns at or past n_out are dropped.
+__device__ __forceinline__ void store_chunk(const GemmParams& p, unsigned row, unsigned col, unsigned n_out, const float (&v)[32]) {
+    if (row >= p.m || col >= n_out) return;
+    const bool add = p.epilogue == 1;
+    const bool whole = col + 32 <= n_out && p.vec_ok != 0;
+    if (p.y_half != 0) {
+        __half* out = static_cast<__half*>(p.y) + static_cast<size_t>(row) * p.ld_y + col;
+        if (whole) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 packed;
+                __half2 h[4];
+                if (add) {
+                    const uint4 old = *reinterpret_cast<const uint4*>(out + 8 * q);
+                    const __half2* o = reinterpret_cast<const __half2*>(&old);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __half22float2(o[j]);
+                        h[j] = __floats2half2_rn(__fadd_rn(f.x, v[8 * q + 2 * j]), __fadd_rn(f.y, v[8 * q + 2 * j + 1]));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(v[8 * q + 2 * j], v[8 * q + 2 * j + 1]);
+                }
+                packed.x = *reinterpret_cast<unsigned*>(&h[0]);
+                packed.y = *reinterpret_cast<unsigned*>(&h[1]);
+                packed.z = *reinterpret_cast<unsigned*>(&h[2]);
+                packed.w = *reinterpret_cast<unsigned*>(&h[3]);
+                *reinterpret_cast<uint4*>(out + 8 * q) = packed;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (col + j < n_out) out[j] = __float2half_rn(add ? __fadd_rn(__half2float(out[j]), v[j]) : v[j]);
+            }
+        }
+    } else {
+        float* out = static_cast<float*>(p.y) + static_cast<size_t>(row) * p.ld_y + col;
+        if (whole) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                float4 r = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                if (add) {
+                    const float4 old = *reinterpret_cast<const float4*>(out + 4 * q);
+                    r = make_float4(__fadd_rn(old.x, r.x), __fadd_rn(old.y, r.y), __fadd_rn(old.z, r.z), __fadd_rn(old.w, r.w));
+                }
+                *reinterpret_cast<float4*>(out + 4 * q) = r;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (col + j < n_out) out[j] = add ? __fadd_rn(out[j], v[j]) : v[j];
+            }
+        }
+    }
+}
+
+// Accumulator columns [c, c + 32) of this thread's row, from tensor memory.
+__device__ __forceinline__ void load_acc_tmem(uint32_t taddr, unsigned c, float (&v)[32]) {
+    uint32_t r[32];
+    ptx::tmem_ld_32x32(taddr + c, r);
+    ptx::tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+}
+
+// The same columns as the sum, in k order, of the partial tiles the contributing CTAs left in scratch memory.
+// Slot layout: float4 index (chunk * 8 + quad) * 128 + row, so a warp's accesses are contiguous.
+template <int BN>
+__device__ __forceinline__ void load_acc_partials(const GemmParams& p, unsigned long long total, unsigned grid, unsigned tile_start, unsigned c_first,
+                                                  unsigned c_last, unsigned row, unsigned c, float (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+    for (unsigned cta = c_first; cta <= c_last; ++cta) {
+        const unsigned slot = 2 * cta + (range_lo(total, cta, grid) >= tile_start ? 0u : 1u);
+        const float4* src = reinterpret_cast<const float4*>(p.partials) + static_cast<size_t>(slot) * (kBM * BN / 4) + (c / 32) * 8 * kBM + row;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 t = __ldcg(src + q * kBM);
+            v[4 * q] = __fadd_rn(v[4 * q], t.x);
+            v[4 * q + 1] = __fadd_rn(v[4 * q + 1], t.y);
+            v[4 * q + 2] = __fadd_rn(v[4 * q + 2], t.z);
+            v[4 * q + 3] = __fadd_rn(v[4 * q + 3], t.w);
+        }
+    }
+}
+
+// Applies the epilogue to a whole tile row by row; `load(c, v)` yields accumulator columns [c, c + 32) of this thread's row.
+template <int BN, class Load>
+__device__ __forceinline__ void finish_tile(const GemmParams& p, unsigned m_tile, unsigned n_tile, unsigned row_in_tile, float descale, Load&& load) {
+    const unsigned row = m_tile * kBM + row_in_tile;
+    if (p.epilogue == 2) {
+        // Packed columns: blocks of 128 = 64 gate then 64 up. Output column of gate column 128 b + r is 64 b + r.
+        const unsigned n_out = p.n / 2;
+#pragma unroll 1
+        for (unsigned b = 0; b < BN / 128; ++b) {
+#pragma unroll 1
+            for (unsigned h = 0; h < 2; ++h) {
+                float g[32], u[32];
+                load(b * 128 + h * 32, g);
+                load(b * 128 + 64 + h * 32, u);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) g[j] = swiglu(__fmul_rn(g[j], descale), __fmul_rn(u[j], descale));
+                store_chunk(p, row, n_tile * (BN / 2) + b * 64 + h * 32, n_out, g);
+            }
+        }
+    } else {
+#pragma unroll 1
+        for (unsigned c = 0; c < BN; c += 32) {
+            float v[32];
+            load(c, v);
+            if (descale != 1.0f) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], descale);
+            }
+            store_chunk(p, row, n_tile * BN + c, p.n, v);
+        }
+    }
+}
+
+template <int BN, bool W8>
+__global__ void __launch_bounds__(Shape<BN, W8>::kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+    using S = Shape<BN, W8>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_addr(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;  // operand tiles start on 1024-byte boundaries (128-byte swizzle)
+    uint8_t* const smem = smem_raw + (base - raw_addr);
+
+    const uint32_t stages_addr = base;
+    const uint32_t conv_addr = base + S::kStages * S::kStageBytes;
+    uint8_t* const tail = smem + S::kStages * S::kStageBytes + S::kConvBuffers * S::kConvBytes;
+    const uint32_t bars = ptx::smem_addr(tail);
+    const auto full_bar = [&](int s) { return bars + 8u * s; };
+    const auto empty_bar = [&](int s) { return bars + 8u * (S::kStages + s); };
+    const auto acc_full_bar = [&](int a) { return bars + 8u * (2 * S::kStages + a); };
+    const auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * S::kStages + 2 + a); };
+    const auto conv_full_bar = [&](int c) { return bars + 8u * (2 * S::kStages + 4 + c); };
+    const auto conv_empty_bar = [&](int c) { return bars + 8u * (2 * S::kStages + 6 + c); };
+    unsigned* const words = reinterpret_cast<unsigned*>(tail + S::kBarriers * 8);
+    unsigned* const tmem_slot = words;                 // base address of the tensor memory allocation
+    volatile unsigned* const abort_flag = words + 1;   // raised by the first wait that runs out
+    volatile unsigned* const fix = words + 2;          // [0] this CTA reduces the tile, [1] first and [2] last contributing CTA
+
+    const unsigned warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const unsigned grid = gridDim.x, cta = blockIdx.x;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::kStages; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), W8 ? 1 + 4 : 1);  // the MMA's commit (+ one arrival per converter warp)
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(acc_full_bar(a), 1);
+            ptx::mbar_init(acc_empty_bar(a), 128);
+            ptx::mbar_init(conv_full_bar(a), 4);
+            ptx::mbar_init(conv_empty_bar(a), 1);
+        }
+        words[1] = 0;
+        words[2] = 0;
+        ptx::fence_barrier_init();
+        ptx::tma_prefetch_descriptor(&map_x);
+        ptx::tma_prefetch_descriptor(&map_w);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_addr(tmem_slot), S::kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            Walker walk(p, cta, grid);
+            unsigned tile, kb, ke;
+            int stage = 0;
+            unsigned phase = 0;
+            unsigned issued = 0;  // stages filled so far (for the drain below)
+            bool ok = true;
+            while (ok && walk.next(tile, kb, ke)) {
+                const unsigned m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+                for (unsigned kk = kb; kk < ke; ++kk) {
+                    if (!wait_barrier(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kStatusProducerEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t dst = stages_addr + stage * S::kStageBytes;
+                    ptx::mbar_arrive_expect_tx(full_bar(stage), S::kStageBytes);
+                    ptx::tma_load_2d(dst, &map_x, full_bar(stage), static_cast<int>(kk * kBK), static_cast<int>(m_tile * kBM));
+                    ptx::tma_load_2d(dst + S::kXBytes, &map_w, full_bar(stage), static_cast<int>(kk * kBK), static_cast<int>(n_tile * BN));
+                    ++issued;
+                    if (++stage == S::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok) {
+                // Giving up: let the copies still in flight land before the CTA's shared memory is released. The last
+                // min(issued, stages) fills are the ones that may not have been consumed; each has its own full barrier.
+                const unsigned pending = issued < static_cast<unsigned>(S::kStages) ? issued : static_cast<unsigned>(S::kStages);
+                int s = stage;
+                unsigned ph = phase;
+                for (unsigned i = 0; i < pending; ++i) {
+                    if (--s < 0) {
+                        s = S::kStages - 1;
+                        ph ^= 1u;
+                    }
+                    const long long t0 = clock64();
+                    while (!ptx::mbar_try_wait(full_bar(s), ph) && clock64() - t0 < (1ll << 24)) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::instr_desc_f16_f32acc(kBM, BN);
+            Walker walk(p, cta, grid);
+            unsigned tile, kb, ke;
+            int stage = 0;
+            unsigned phase = 0;
+            int acc = 0;
+            unsigned acc_phase = 0;
+            int conv = 0;
+            unsigned conv_phase = 0;
+            bool ok = true;
+            while (ok && walk.next(tile, kb, ke)) {
+                if (!wait_barrier(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kStatusMmaAccEmpty)) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t d = tmem_base + static_cast<uint32_t>(acc * BN);
+                for (unsigned kk = kb; kk < ke; ++kk) {
+                    if (!wait_barrier(full_bar(stage), phase, abort_flag, p.status, kStatusMmaFull)) {
+                        ok = false;
+                        break;
+                    }
+                    uint32_t w_tile = stages_addr + stage * S::kStageBytes + S::kXBytes;
+                    if constexpr (W8) {
+                        if (!wait_barrier(conv_full_bar(conv), conv_phase, abort_flag, p.status, kStatusMmaConvFull)) {
+                            ok = false;
+                            break;
+                        }
+                        w_tile = conv_addr + conv * S::kConvBytes;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint64_t desc_x = ptx::smem_desc_k_major_sw128(stages_addr + stage * S::kStageBytes);
+                    const uint64_t desc_w = ptx::smem_desc_k_major_sw128(w_tile);
+#pragma unroll
+                    for (int j = 0; j < kBK / 16; ++j) {
+                        // 16 values of k = 32 bytes inside the swizzled 128-byte row: +2 in the descriptor's 16-byte address units
+                        ptx::mma_f16_ss(d, desc_x + 2u * j, desc_w + 2u * j, idesc, (kk > kb || j > 0) ? 1u : 0u);
+                    }
+                    ptx::mma_commit(empty_bar(stage));
+                    if constexpr (W8) {
+                        ptx::mma_commit(conv_empty_bar(conv));
+                        if (++conv == 2) {
+                            conv = 0;
+                            conv_phase ^= 1u;
+                        }
+                    }
+                    if (++stage == S::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::mma_commit(acc_full_bar(acc));
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- epilogue
+        const unsigned quarter = warp % 4;  // the lanes of tensor memory this warp may read: 32 * quarter onwards
+        const unsigned row_in_tile = quarter * 32 + lane;
+        const unsigned long long total = static_cast<unsigned long long>(p.tiles) * p.k_iters;
+        float descale = 1.0f;
+        if constexpr (W8) descale = __ldg(p.descale);
+        Walker walk(p, cta, grid);
+        unsigned tile, kb, ke;
+        int acc = 0;
+        unsigned acc_phase = 0;
+        unsigned unit = 0;
+        while (walk.next(tile, kb, ke)) {
+            const bool arrived = wait_barrier(acc_full_bar(acc), acc_phase, abort_flag, p.status, kStatusEpilogueAccFull);
+            // All 128 threads take the same decision: the flag is read after a barrier every one of them reaches.
+            epilogue_barrier();
+            if (!arrived || *abort_flag != 0) break;
+            ptx::tc_fence_after_sync();
+            const unsigned m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + static_cast<uint32_t>(acc * BN);
+            const bool partial = kb != 0 || ke != p.k_iters;
+            if (!partial) {
+                finish_tile<BN>(p, m_tile, n_tile, row_in_tile, descale, [&](unsigned c, float (&v)[32]) { load_acc_tmem(taddr, c, v); });
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(acc_empty_bar(acc));
+            } else {
+                // Leave the partial sums in this CTA's scratch slot (0 for its first unit, 1 otherwise) and hand the accumulator back.
+                const unsigned slot = 2 * cta + (unit == 0 ? 0u : 1u);
+                float4* dst = reinterpret_cast<float4*>(p.partials) + static_cast<size_t>(slot) * (kBM * BN / 4) + row_in_tile;
+#pragma unroll 1
+                for (unsigned c = 0; c < BN; c += 32) {
+                    float v[32];
+                    load_acc_tmem(taddr, c, v);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) __stcg(dst + ((c / 32) * 8 + q) * kBM, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+                }
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(acc_empty_bar(acc));
+                __threadfence();
+                epilogue_barrier();
+                const unsigned tile_start = tile * p.k_iters;
+                if (warp == 2 && lane == 0) {
+                    // The CTAs whose ranges meet this tile: the one holding its first k iteration up to the one holding its last.
+                    unsigned c_first = static_cast<unsigned>(static_cast<unsigned long long>(tile_start) * grid / total);
+                    while (c_first + 1 < grid && range_lo(total, c_first + 1, grid) <= tile_start) ++c_first;
+                    while (c_first > 0 && range_lo(total, c_first, grid) > tile_start) --c_first;
+                    const unsigned tile_last = tile_start + p.k_iters - 1;
+                    unsigned c_last = static_cast<unsigned>(static_cast<unsigned long long>(tile_last) * grid / total);
+                    while (c_last + 1 < grid && range_lo(total, c_last + 1, grid) <= tile_last) ++c_last;
+                    while (c_last > 0 && range_lo(total, c_last, grid) > tile_last) --c_last;
+                    const unsigned contributors = c_last - c_first + 1;
+                    const unsigned before = atomicAdd(p.counters + tile, 1u);
+                    const bool last = before + 1 == contributors;
+                    if (last) p.counters[tile] = 0;  // everyone has arrived: ready for the next launch
+                    fix[0] = last ? 1u : 0u;
+                    fix[1] = c_first;
+                    fix[2] = c_last;
+                }
+                epilogue_barrier();
+                const bool reduce = fix[0] != 0;
+                const unsigned c_first = fix[1], c_last = fix[2];
+                epilogue_barrier();  // the words may be rewritten by the next partial unit
+                if (reduce) {
+                    __threadfence();
+                    finish_tile<BN>(p, m_tile, n_tile, row_in_tile, descale, [&](unsigned c, float (&v)[32]) {
+                        load_acc_partials<BN>(p, total, grid, tile_start, c_first, c_last, row_in_tile, c, v);
+                    });
+                }
+            }
+            ++unit;
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- int8 -> binary16 converters (W8 only)
+        if constexpr (W8) {
+            // The raw tile is [BN rows][64 bytes] unswizzled; thread i of the 128 converters takes 16-byte piece i, i + 128, ... of it,
+            // that is row (piece / 4), k offset 16 * (piece % 4): a warp reads 512 contiguous bytes. Its 16 values become two 16-byte
+            // pieces (2 j, 2 j + 1) of the row's 128-byte binary16 row, stored at piece index XOR (row % 8): the 128-byte swizzle.
+            // int8 -> binary16 exactly: byte ^ 0x80 is b + 128 in [1, 255]; 0x6400 | that is the binary16 number 1024 + 128 + b (spacing
+            // 1 there); minus 1152 gives b. Then one binary16 multiplication by the group's prepared scale.
+            const unsigned ct = threadIdx.x - 192;  // 0 .. 127
+            const unsigned cwarp = ct / 32;
+            Walker walk(p, cta, grid);
+            unsigned tile, kb, ke;
+            int stage = 0;
+            unsigned phase = 0;
+            int conv = 0;
+            unsigned conv_phase = 0;
+            bool ok = true;
+            const __half2 offset = __half2half2(__ushort_as_half(0x6480));  // 1152
+            while (ok && walk.next(tile, kb, ke)) {
+                const unsigned n_tile = tile / p.m_tiles;
+                for (unsigned kk = kb; kk < ke; ++kk) {
+                    // scales of this thread's rows for the group of this k block (rows past N read as zero)
+                    __half2 sc[BN / 32];
+                    const __half* srow = p.scales_t + static_cast<size_t>((kk * kBK) / kGroup) * p.ld_st;
+#pragma unroll
+                    for (int i = 0; i < BN / 32; ++i) {
+                        const unsigned n = n_tile * BN + (ct + 128 * i) / 4;
+                        sc[i] = n < p.n ? __half2half2(srow[n]) : __half2half2(__ushort_as_half(0));
+                    }
+                    bool got = wait_barrier(full_bar(stage), phase, abort_flag, p.status, kStatusConvFull);
+                    got = got && wait_barrier(conv_empty_bar(conv), conv_phase ^ 1u, abort_flag, p.status, kStatusConvEmpty);
+                    if (!__all_sync(0xFFFFFFFFu, got)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint8_t* raw = smem + stage * S::kStageBytes + S::kXBytes;
+                    uint8_t* out = smem + S::kStages * S::kStageBytes + conv * S::kConvBytes;
+#pragma unroll
+                    for (int i = 0; i < BN / 32; ++i) {
+                        const unsigned piece = ct + 128 * i;
+                        const unsigned row = piece / 4, part = piece % 4;
+                        const uint4 q = *reinterpret_cast<const uint4*>(raw + piece * 16);
+                        const unsigned w[4] = {q.x ^ 0x80808080u, q.y ^ 0x80808080u, q.z ^ 0x80808080u, q.w ^ 0x80808080u};
+                        unsigned h[8];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            unsigned lo = __byte_perm(w[j], 0x64646464u, 0x5140);  // bytes 0, 1 -> two binary16 numbers 1024 + byte
+                            unsigned hi = __byte_perm(w[j], 0x64646464u, 0x5342);  // bytes 2, 3
+                            __half2 a = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&lo), offset), sc[i]);
+                            __half2 b = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&hi), offset), sc[i]);
+                            h[2 * j] = *reinterpret_cast<unsigned*>(&a);
+                            h[2 * j + 1] = *reinterpret_cast<unsigned*>(&b);
+                        }
+                        uint8_t* dst_row = out + row * 128;
+                        const unsigned sw = row & 7u;
+                        *reinterpret_cast<uint4*>(dst_row + (((2 * part) ^ sw) * 16)) = make_uint4(h[0], h[1], h[2], h[3]);
+                        *reinterpret_cast<uint4*>(dst_row + (((2 * part + 1) ^ sw) * 16)) = make_uint4(h[4], h[5], h[6], h[7]);
+                    }
+                    ptx::fence_proxy_async_smem();  // the MMA reads these stores through the async proxy
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::mbar_arrive(conv_full_bar(conv));
+                        ptx::mbar_arrive(empty_bar(stage));  // this warp is done with the raw tile
+                    }
+                    (void)cwarp;
+                    if (++conv == 2) {
+                        conv = 0;
+                        conv_phase ^= 1u;
+                    }
+                    if (++stage == S::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    }
+
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, S::kTmemCols);
+    }
+}
+
+template <int BN, bool W8>
+void launch_config(const Context& ctx, const CUtensorMap& map_x, const CUtensorMap& map_w, GemmParams p, bool stream_k, cudaStream_t stream) {
+    using S = Shape<BN, W8>;
+    p.m_tiles = (p.m + kBM - 1) / kBM;
+    p.n_tiles = (p.n + BN - 1) / BN;
+    p.k_iters = (p.k + kBK - 1) / kBK;
+    p.tiles = p.m_tiles * p.n_tiles;
+    p.stream_k = stream_k ? 1u : 0u;
+    if (p.tiles > ctx.scratch.counter_count) throw std::invalid_argument("sepal_b200: more output tiles than the context has counters for");
+    const unsigned long long total = static_cast<unsigned long long>(p.tiles) * p.k_iters;
+    if (total > 0xFFFFFFFFull) throw std::invalid_argument("sepal_b200: the product is too large for one launch");
+    unsigned grid = static_cast<unsigned>(ctx.sm_count);
+    if (stream_k) {
+        // Not more CTAs than there are pieces of at least four k iterations (or whole tiles, when there are enough of them).
+        const unsigned long long pieces = total / 4 > p.tiles ? total / 4 : p.tiles;
+        if (pieces < grid) grid = static_cast<unsigned>(pieces);
+        const std::size_t need = static_cast<std::size_t>(grid) * 2u * kBM * BN * sizeof(float);
+        if (need > ctx.scratch.partial_bytes) {
+            // Fall back to whole tiles rather than write past the scratch the context owns.
+            p.stream_k = 0;
+        }
+    }
+    if (p.stream_k == 0 && p.tiles < grid) grid = p.tiles;
+    static bool configured[64] = {};  // per device; a benign race: every writer sets the same attribute
+    if (ctx.device >= 64 || !configured[ctx.device]) {
+        check(cudaFuncSetAttribute(gemm_tc_kernel<BN, W8>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes), "cudaFuncSetAttribute");
+        if (ctx.device < 64) configured[ctx.device] = true;
+    }
+    gemm_tc_kernel<BN, W8><<<grid, S::kThreads, S::kSmemBytes, stream>>>(map_x, map_w, p);
+    check(cudaGetLastError(), "gemm_tc_kernel launch");
+    ++g_launches;
+}
+
+void require_aligned(const void* ptr, const char* what) {
+    if (reinterpret_cast<std::uintptr_t>(ptr) % 16 != 0) throw std::invalid_argument(std::string("sepal_b200: ") + what + " must be 16-byte aligned");
+}
+
+GemmParams common_params(Context& ctx, void* y, std::size_t ld_y, bool y_half, std::size_t t, std::size_t n, std::size_t k, Epilogue epilogue) {
+    if (t > 0x7FFFFFFFu || n > 0x7FFFFFFFu || k > 0x7FFFFFFFu) throw std::invalid_argument("sepal_b200: dimension beyond 2^31");
+    if (y == nullptr) throw std::invalid_argument("sepal_b200: null output");
+    GemmParams p{};
+    p.y = y;
+    p.ld_y = ld_y;
+    p.m = static_cast<unsigned>(t);
+    p.n = static_cast<unsigned>(n);
+    p.k = static_cast<unsigned>(k);
+    p.epilogue = static_cast<unsigned>(epilogue);
+    p.y_half = y_half ? 1u : 0u;
+    const std::size_t elem = y_half ? 2 : 4;
+    p.vec_ok = (reinterpret_cast<std::uintptr_t>(y) % 16 == 0 && (ld_y * elem) % 16 == 0) ? 1u : 0u;
+    p.partials = ctx.scratch.partials;
+    p.counters = ctx.scratch.tile_counters;
+    p.status = ctx.status;
+    return p;
+}
+
+// -1: the even split unless the whole tiles already fill the CTAs evenly (or there are so many waves that the tail does not matter).
+bool pick_stream_k(const Context& ctx, unsigned tiles) {
+    const unsigned sms = static_cast<unsigned>(ctx.sm_count);
+    if (tiles % sms == 0) return false;
+    return true;
+}
+
+}  // namespace
+
+std::uint64_t take_launch_count() {
+    const std::uint64_t n = g_launches;
+    g_launches = 0;
+    return n;
+}
+void count_launch() { ++g_launches; }
+
+void launch_gemm_f16(Context& ctx, const void* x, std::size_t ld_x, const void* w, std::size_t ld_w, void* y, std::size_t ld_y, bool y_half,
+                     std::size_t t, std::size_t n, std::size_t k, Epilogue epilogue, int config, cudaStream_t stream) {
+    if (!gemm_f16_supports(n, k, ld_x, ld_w, ld_y, epilogue))
+        throw std::invalid_argument("launch_gemm_f16: unsupported shape [" + std::to_string(t) + " x " + std::to_string(k) + "] by [" + std::to_string(n) +
+                                    " x " + std::to_string(k) + "] (K and the strides of X and W multiples of 8, N and the stride of Y even, "
+                                    "SwiGLU needs N a multiple of 128)");
+    if (config < -1 || config >= kConfigs) throw std::invalid_argument("launch_gemm_f16: config must be -1 .. 3");
+    if (t == 0) return;
+    if (x == nullptr || w == nullptr) throw std::invalid_argument("launch_gemm_f16: null operand");
+    require_aligned(x, "X");
+    require_aligned(w, "W");
+    check(cudaSetDevice(ctx.device), "cudaSetDevice");
+    GemmParams p = common_params(ctx, y, ld_y, y_half, t, n, k, epilogue);
+    const bool narrow = config >= 0 ? config >= 2 : (n <= 128);
+    const unsigned bn = narrow ? 128 : 256;
+    const CUtensorMap map_x = make_tensor_map_2d(ctx, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, t, k, ld_x, kBM, kBK, true);
+    const CUtensorMap map_w = make_tensor_map_2d(ctx, w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n, k, ld_w, bn, kBK, true);
+    const unsigned tiles = static_cast<unsigned>(((t + kBM - 1) / kBM) * ((n + bn - 1) / bn));
+    const bool stream_k = config >= 0 ? (config & 1) != 0 : pick_stream_k(ctx, tiles);
+    if (narrow)
+        launch_config<128, false>(ctx, map_x, map_w, p, stream_k, stream);
+    else
+        launch_config<256, false>(ctx, map_x, map_w, p, stream_k, stream);
+}
+
+void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMatrix& wm, void* y, std::size_t ld_y, bool y_half, std::size_t t,
+                     std::size_t n, std::size_t k, Epilogue epilogue, int config, cudaStream_t stream) {
+    const std::int8_t* q = wm.q;
+    const std::size_t ld_q = wm.ld_q, ld_st = wm.ld_st;
+    const void* scales_t = wm.scales_t;
+    const float* descale = wm.descale;
+    if (!gemm_w8g_supports(n, k, ld_x, ld_q, k / kGroup, ld_y, epilogue) || ld_st < n)
+        throw std::invalid_argument("launch_gemm_w8g: unsupported shape [" + std::to_string(t) + " x " + std::to_string(k) + "] by [" + std::to_string(n) +
+                                    " x " + std::to_string(k) + "] (K a multiple of 128, the stride of X a multiple of 8, of q a multiple of 16, "
+                                    "N and the stride of Y even, SwiGLU needs N a multiple of 128)");
+    if (config < -1 || config >= kConfigs) throw std::invalid_argument("launch_gemm_w8g: config must be -1 .. 3");
+    if (t == 0) return;
+    if (x == nullptr || q == nullptr || scales_t == nullptr || descale == nullptr) throw std::invalid_argument("launch_gemm_w8g: null operand");
+    require_aligned(x, "X");
+    require_aligned(q, "q");
+    check(cudaSetDevice(ctx.device), "cudaSetDevice");
+    GemmParams p = common_params(ctx, y, ld_y, y_half, t, n, k, epilogue);
+    p.scales_t = static_cast<const __half*>(scales_t);
+    p.ld_st = ld_st;
+    p.descale = descale;
+    const bool narrow = config >= 0 ? config >= 2 : (n <= 128);
+    const unsigned bn = narrow ? 128 : 256;
+    const CUtensorMap map_x = make_tensor_map_2d(ctx, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, t, k, ld_x, kBM, kBK, true);
+    const CUtensorMap map_w = make_tensor_map_2d(ctx, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k, ld_q, bn, kBK, false);
+    const unsigned tiles = static_cast<unsigned>(((t + kBM - 1) / kBM) * ((n + bn - 1) / bn));
+    const bool stream_k = config >= 0 ? (config & 1) != 0 : pick_stream_k(ctx, tiles);
+    if (narrow)
+        launch_config<128, true>(ctx, map_x, map_w, p, stream_k, stream);
+    else
+        launch_config<256, true>(ctx, map_x, map_w, p, stream_k, stream);
+}
+
+}  // namespace sepal::b200

@@ -1,0 +1,418 @@
+#!/usr/bin/env python3
+"""Benchmark of the trunk projection GEMMs on B200, one JSON line on stdout.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Workloads (BASELINE.json `configs`, zero-based):
+    w8g_down_m900   configs[1]: int8-group down projection, M = 900, K = 9728, N = 2560, fp16 activations, fp16 result   (default)
+    f16_up_m900     configs[0]: fp16 up projection, M = 900, K = 2560, N = 9728
+    f16_up_m4096 / w8g_down_m4096: the same products at the long-log call size
+
+A step is one batch of `calls_per_step` independent products of that shape (as many requests of M tokens), each on the next of a
+ring of operand sets whose total size exceeds the 126 MB L2, so no timed launch finds its operands in cache. `value` is the
+whole-job TFLOP/s with operands resident in HBM; `e2e` is the same metric through the host-pointer provider (pinned host X in,
+float32 Y out, copies inside the timed region). With N > 1 (torchrun, one rank per GPU) every GPU holds its own replica and runs the
+same steps (requests shard whole, no collective on the data path); time is the max over ranks.
+
+`--impl reference` times the reference's own CPU implementation of the same product (its cpu-bf16 packed GEMM compiled from its
+sources into oracle/_ref, on all host cores it takes) on the same metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (kind, M, N, K, config index in BASELINE.json)
+    "w8g_down_m900": ("w8g", 900, 2560, 9728, 1),
+    "f16_up_m900": ("f16", 900, 9728, 2560, 0),
+    "w8g_down_m4096": ("w8g", 4096, 2560, 9728, 1),
+    "f16_up_m4096": ("f16", 4096, 9728, 2560, 0),
+}
+# Every named trunk GEMM (N x K) for the per-shape table: SURVEY's list of projections at hidden 2560, MLP 9728.
+TRUNK_SHAPES = [("gate_up+swiglu", 19456, 2560, "swiglu"), ("down+residual", 2560, 9728, "add"), ("q", 4096, 2560, "store"),
+                ("kv", 2048, 2560, "store"), ("o+residual", 2560, 4096, "add"), ("dn_in", 8192, 2560, "store"),
+                ("dn_out+residual", 2560, 2048, "add")]
+L2_BYTES = 126 * 1024 * 1024
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs (read-only)."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index: int) -> None:
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self.stop_flag = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self) -> None:
+        if not self.ok:
+            return
+        while not self.stop_flag.is_set():
+            try:
+                mhz = int(self.nv.nvmlDeviceGetClockInfo(self.handle, self.nv.NVML_CLOCK_SM))
+                mask = int(self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)) if hasattr(self.nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else int(self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.samples.append(mhz)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def make_operand_sets(ctx, kind, m, n, k, device):
+    """A ring of independent operand sets (seeded synthetic data with BASELINE's distributions) larger than the L2 in total."""
+    import torch
+
+    per_set = m * k * 2 + (n * k if kind == "w8g" else n * k * 2) + m * n * 2
+    sets = max(2, -(-int(1.5 * L2_BYTES) // per_set))
+    gen = torch.Generator(device=device).manual_seed(1001)
+    out = []
+    for _ in range(sets):
+        x = torch.randn((m, k), generator=gen, device=device).bfloat16().half()  # N(0, 1), exact in bf16 and fp16
+        y = torch.empty((m, n), dtype=torch.float16, device=device)
+        if kind == "w8g":
+            q = torch.randint(-127, 128, (n, k), generator=gen, device=device, dtype=torch.int32).to(torch.int8)
+            s = (torch.randn((n, k // 128), generator=gen, device=device) * 0.02).abs() / 127.0
+            w = ctx.prepare_w8g(q, s.float().contiguous())
+        else:
+            w = (torch.randn((n, k), generator=gen, device=device) * 0.02).bfloat16().half()
+        out.append((x, w, y))
+    return out, sets * per_set
+
+
+def algorithmic_bytes(kind, m, n, k):
+    """Bytes one product must move: X once, W once (int8 + scales for w8g), Y once (fp16)."""
+    w = n * k + n * (k // 128) * 2 if kind == "w8g" else n * k * 2
+    return m * k * 2 + w + m * n * 2
+
+
+def run_ours(args):
+    import torch
+
+    import sepal_runner_b200 as sb
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    kind, m, n, k, cfg_index = WORKLOADS[args.workload]
+    ctx = sb.Context(local)
+    sets, ring_bytes = make_operand_sets(ctx, kind, m, n, k, device)
+    calls = args.calls_per_step
+    flops_call = 2.0 * m * n * k
+
+    def call(i):
+        x, w, y = sets[i % len(sets)]
+        if kind == "w8g":
+            ctx.gemm_w8g(x, w, y)
+        else:
+            ctx.gemm_f16(x, w, y)
+
+    def step(s):
+        for c in range(calls):
+            call(s * calls + c)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for s in range(args.warmup):
+        step(s)
+    ctx.check_status()
+    ctx.take_launch_count()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(args.steps):
+        step(args.warmup + s)
+    e1.record()
+    barrier()
+    elapsed_ms = e0.elapsed_time(e1)
+    launches = ctx.take_launch_count()
+    ctx.check_status()
+
+    # ---- end to end through the host-pointer provider: pinned X in, float32 Y out, copies inside the timed region
+    import numpy as np
+
+    prov = sb.Provider(local, 1 << 30)
+    x0, w0, _ = sets[0]
+    if kind == "w8g":
+        wd = (w0.q.float() * w0.scales.repeat_interleave(128, dim=1)).cpu().numpy()
+        wid = prov.upload_weights_w8g(wd)
+    else:
+        wid = prov.upload_weights(w0.cpu().numpy())
+    hx = torch.empty((m, k), dtype=torch.float16).pin_memory()
+    hx.copy_(x0.cpu())
+    hy = torch.empty((m, n), dtype=torch.float32).pin_memory()
+    e2e_steps = max(1, min(args.steps, 20))
+    e2e_calls = min(calls, 8)
+    for _ in range(2):
+        prov.gemm_f_raw(hx.data_ptr(), 1, m, wid, hy.data_ptr(), 0.0)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps * e2e_calls):
+        prov.gemm_f_raw(hx.data_ptr(), 1, m, wid, hy.data_ptr(), 0.0)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    sampler.stop_flag.set()
+    sampler.join(timeout=2)
+
+    times = torch.tensor([elapsed_ms, e2e_s * 1e3], dtype=torch.float64, device=device)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = float(times[0]), float(times[1])
+
+    peaks, peak_kind = measured_peaks()
+    peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    total_calls = args.steps * calls
+    per_call_ms = elapsed_ms / total_calls
+    tflops_gpu = flops_call / (per_call_ms * 1e-3) / 1e12
+    value = tflops_gpu * world
+    e2e_value = flops_call * e2e_steps * e2e_calls / (e2e_ms * 1e-3) / 1e12 * world
+
+    line = {
+        "metric": "GEMM TFLOP/s (f16 tensor cores; w8 group) at M=900",
+        "value": round(value, 2),
+        "unit": "TFLOP/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(elapsed_ms / args.steps, 5),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "f16 x int8-group -> f32 accumulate" if kind == "w8g" else "f16 x f16 -> f32 accumulate",
+        "data": "synthetic",
+        "config": {
+            "workload": f"{args.workload} (BASELINE configs[{cfg_index}]): M={m} K={k} N={n}",
+            "calls_per_step": calls,
+            "l2": f"ring of {len(sets)} operand sets, {ring_bytes >> 20} MiB > 126 MiB L2: every launch reads its operands from HBM",
+            "prefill_tokens_per_s": round(m * total_calls / (elapsed_ms * 1e-3) * world, 1),
+            "parallelism": f"request-sharded x{world}, full replica per GPU, no collective",
+        },
+        "roofline": {
+            "bound": "tensor",
+            "achieved": round(tflops_gpu, 2),
+            "peak": peak_tf,
+            "unit": "TFLOP/s",
+            "frac": round(tflops_gpu / peak_tf, 4),
+            "peak_source": f"bf16_tflops of MEASURED_PEAKS.json ({peak_kind}; burst: the kernel is timed alone)",
+            "traffic": args.traffic,
+            "algorithmic_bytes": algorithmic_bytes(kind, m, n, k),
+            "hbm_gbs_achieved": round(algorithmic_bytes(kind, m, n, k) / (per_call_ms * 1e-3) / 1e9, 1),
+            "us_per_launch": round(per_call_ms * 1e3, 2),
+        },
+        "e2e": {
+            "value": round(e2e_value, 3),
+            "unit": "TFLOP/s",
+            "h2d_bytes_per_step": m * k * 2 * calls,
+            "d2h_bytes_per_step": m * n * 4 * calls,
+            "note": f"sepal_b200_provider_gemm_f, pinned host buffers, {e2e_steps * e2e_calls} calls timed by wall clock around a device sync",
+        },
+        "gpu_launches": int(launches),
+        "clocks": sampler.summary(),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(kind, m, n, k)
+    if rank == 0 and world == 1 and args.shapes:
+        line["shapes"] = shape_table(ctx, device, peak_tf)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    prov.close()
+    ctx.close()
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+def shape_table(ctx, device, peak_tf):
+    """TFLOP/s of every named trunk GEMM at M = 900 and M = 4096, fp16 and int8-group weights, with the fused epilogues."""
+    import torch
+
+    import sepal_runner_b200 as sb
+
+    rows = []
+    gen = torch.Generator(device=device).manual_seed(7)
+    for m in (900, 4096):
+        for name, n, k, ep in TRUNK_SHAPES:
+            epi = {"store": sb.STORE, "add": sb.ADD, "swiglu": sb.SWIGLU}[ep]
+            x = torch.randn((m, k), generator=gen, device=device).half()
+            w = (torch.randn((n, k), generator=gen, device=device) * 0.02).half()
+            n_out = n // 2 if ep == "swiglu" else n
+            y = torch.zeros((m, n_out), dtype=torch.float32 if ep == "add" else torch.float16, device=device)
+            variants = [("f16", lambda: ctx.gemm_f16(x, w, y, epilogue=epi))]
+            if k % 128 == 0:
+                q, s = ctx.quantize_group_s8(w.float())
+                wq = ctx.prepare_w8g(q, s)
+                variants.append(("w8g", lambda: ctx.gemm_w8g(x, wq, y, epilogue=epi)))
+            for vname, fn in variants:
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                best = None
+                for _ in range(3):  # min over 3 batches of back-to-back launches (the reference's probe method, gemm_probe.cpp:69-89)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(10):
+                        fn()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ms = e0.elapsed_time(e1) / 10
+                    best = ms if best is None else min(best, ms)
+                tf = 2.0 * m * n * k / (best * 1e-3) / 1e12
+                rows.append({"gemm": name, "weights": vname, "m": m, "n": n, "k": k, "us": round(best * 1e3, 1), "tflops": round(tf, 1),
+                             "frac_of_peak": round(tf / peak_tf, 3)})
+    ctx.check_status()
+    return rows
+
+
+def cpu_baseline(kind, m, n, k, reps: int = 5):
+    """The reference's cpu-bf16 packed GEMM on this host's cores, on the same product (int8 weights dequantised to float32 first:
+    the reference has no group-128 CPU kernel), weights packed once, best of `reps` (runner/tools/sepal_cpu_gemm_bench.cpp:153-201)."""
+    import numpy as np
+
+    from oracle.oracle import Oracle, Ref
+
+    rng = np.random.default_rng(1001)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    flops = 2.0 * m * n * k
+    if Ref.available():
+        r = Ref()
+        runs, _ = r.time_gemm(x, w, kind="bf16", reps=reps)
+        best = min(p + g for p, g in runs)
+        return {"value": round(flops / best / 1e12, 4), "unit": "TFLOP/s", "cores": r.threads(), "kind": "reference",
+                "sample": f"{reps} full products of M={m} N={n} K={k} by the reference's gemm_packed ({r.variant()}, {r.brand()}), best, activation packing included",
+                "ms": round(best * 1e3, 2)}
+    o = Oracle()
+    rows = min(m, 64)
+    t0 = time.perf_counter()
+    o.gemm(x[:rows], w)
+    dt = time.perf_counter() - t0
+    return {"value": round(2.0 * rows * n * k / dt / 1e12, 5), "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{rows} of {m} rows by the float64 oracle (oracle/_ref was not built)", "ms": round(dt * 1e3, 2)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+
+    from oracle.oracle import Ref
+
+    kind, m, n, k, cfg_index = WORKLOADS[args.workload]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not Ref.available():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libsepal_ref.so was not built (the reference tree was absent at build time)"}))
+        return
+    r = Ref()
+    rng = np.random.default_rng(1001)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    flops = 2.0 * m * n * k
+    steps = max(1, min(args.steps, 50))
+    warm = max(1, min(args.warmup, 5))
+    runs, _ = r.time_gemm(x, w, kind="bf16", reps=warm + steps)
+    timed = runs[warm:]
+    total = sum(p + g for p, g in timed)
+    value = flops * len(timed) / total / 1e12
+    line = {
+        "impl": "reference",
+        "metric": "GEMM TFLOP/s (f16 tensor cores; w8 group) at M=900",
+        "value": round(value, 4),
+        "unit": "TFLOP/s",
+        "n_gpus": world,
+        "steps": len(timed),
+        "warmup": warm,
+        "ms_per_step": round(total / len(timed) * 1e3, 3),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16 weights x f32/bf16 activations -> f32 accumulate (cpu-bf16)",
+        "data": "synthetic",
+        "config": {"workload": f"{args.workload} (BASELINE configs[{cfg_index}]): M={m} K={k} N={n}", "calls_per_step": 1,
+                   "note": "one full product per step by the reference's cpu-bf16 gemm_packed; int8-group weights run dequantised (no group-128 CPU kernel exists)"},
+        "cpu_baseline": {"value": round(value, 4), "unit": "TFLOP/s", "cores": r.threads(), "kind": "reference",
+                         "sample": f"{len(timed)} full products, {r.variant()}, {r.brand()}"},
+        "e2e": {"value": round(value, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="w8g_down_m900", choices=sorted(WORKLOADS))
+    ap.add_argument("--calls-per-step", type=int, default=32)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-shapes", dest="shapes", action="store_false", help="skip the per-shape table")
+    ap.add_argument("--traffic", type=float, default=None, help="DRAM bytes per launch from an ncu capture (reported as roofline.traffic)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

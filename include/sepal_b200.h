@@ -85,6 +85,26 @@ SEPAL_B200_API uint64_t sepal_b200_take_launch_count(void);
 SEPAL_B200_API int32_t sepal_b200_gemm_f16(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const void* w, uint64_t ld_w, void* y, uint64_t ld_y,
                                            int32_t y_half, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t config, void* stream);
 
+/* The same product for callers that cannot allocate device memory. This function has NO counterpart in the reference: its engine
+ * allocates its buffers itself at creation. It exists for hosts that may not call cudaMalloc once they are running - a process
+ * that gave all device memory to its own pool at start-up, a plug-in whose host forbids allocation after initialisation, code
+ * that runs while another component holds the allocator. It takes no context: the scratch of the split-k schedule (partial tiles,
+ * tile counters, the status word) is a fixed array of 20 MiB + 17 KiB inside the library, held by every GPU that loads the library
+ * until the process exits. It calls no cudaMalloc, cudaFree or allocating library routine, on any call.
+ *   - Runs on the CURRENT device, with 128 x 128 tiles and the even split of all k iterations (the schedule that uses the scratch).
+ *   - Limit: ceil(T / 128) * ceil(N / 128) <= 4096 output tiles (for example T = 4096 with N = 16384); a larger product fails with a
+ *     message and nothing is launched. Otherwise the requirements of sepal_b200_gemm_f16.
+ *   - The first call on a device resolves the array's device address and reads the device's properties; make that call before
+ *     any stream capture begins.
+ *   - All calls share the one array. Each call first clears the counters and the status word on `stream` (the array keeps what the
+ *     previous call left); two calls that overlap on the device (different streams, different threads) race on it and give
+ *     wrong results: keep every call of this function on one stream, or order them yourself.
+ *   - status_out == NULL: enqueue and return. Otherwise the call waits for `stream` and stores the kernel status word
+ *     (0 = every wait completed; see sepal_b200_status). */
+SEPAL_B200_API int32_t sepal_b200_gemm_f16_noalloc(const void* x, uint64_t ld_x, const void* w, uint64_t ld_w, void* y, uint64_t ld_y,
+                                                   int32_t y_half, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, void* stream,
+                                                   int32_t* status_out);
+
 /* binary16 activations x int8 weights with one scale per output row and group of 128 values of k (the gpu-w8g layout). Replaces
  * launch_gemm_simt with SimtWeight::Int8Group (runner/cuda/src/gemm_simt_kernels.hpp:42-56) and launch_gemm_w8a16
  * (runner/cuda/src/gemm_s8_kernels.hpp:51-57). q is int8 [N, ld_q]; scales_t / descale come from sepal_b200_prepare_w8g_scales.

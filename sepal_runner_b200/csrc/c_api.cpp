@@ -103,6 +103,16 @@ int32_t sepal_b200_gemm_f16(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, c
     });
 }
 
+int32_t sepal_b200_gemm_f16_noalloc(const void* x, uint64_t ld_x, const void* w, uint64_t ld_w, void* y, uint64_t ld_y, int32_t y_half, uint64_t t,
+                                    uint64_t n, uint64_t k, int32_t epilogue, void* stream, int32_t* status_out) {
+    return guarded([&] {
+        int status = 0;
+        launch_gemm_f16_noalloc(x, ld_x, w, ld_w, y, ld_y, y_half != 0, t, n, k, epilogue_of(epilogue), static_cast<cudaStream_t>(stream),
+                                status_out != nullptr ? &status : nullptr);
+        if (status_out != nullptr) *status_out = status;
+    });
+}
+
 int32_t sepal_b200_gemm_w8g(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const int8_t* q, uint64_t ld_q, const void* scales_t, uint64_t ld_st,
                             const float* descale, void* y, uint64_t ld_y, int32_t y_half, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue,
                             int32_t config, void* stream) {

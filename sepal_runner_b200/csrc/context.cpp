@@ -43,6 +43,29 @@ Context::Context(int device_, std::size_t workspace_bytes) : device(device_) {
     check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
 }
 
+Context::Context(Borrowed, int device_, float* partials, std::size_t partial_bytes, unsigned* counters, std::size_t counter_count, int* status_word)
+    : device(device_) {
+    check(cudaDeviceGetAttribute(&compute_major, cudaDevAttrComputeCapabilityMajor, device), "cudaDeviceGetAttribute");
+    check(cudaDeviceGetAttribute(&compute_minor, cudaDevAttrComputeCapabilityMinor, device), "cudaDeviceGetAttribute");
+    check(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute");
+    int optin = 0;
+    check(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device), "cudaDeviceGetAttribute");
+    smem_optin = static_cast<std::size_t>(optin);
+    if (compute_major != 10)
+        throw std::runtime_error("sepal_b200: the kernels are built for sm_100a only; device " + std::to_string(device) + " is sm_" +
+                                 std::to_string(compute_major) + std::to_string(compute_minor) + " (there is no fallback path)");
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult query{};
+    check(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &query), "cudaGetDriverEntryPoint");
+    if (fn == nullptr || query != cudaDriverEntryPointSuccess) throw std::runtime_error("sepal_b200: the driver has no cuTensorMapEncodeTiled");
+    encode = reinterpret_cast<TensorMapEncodeFn>(fn);
+    scratch.partials = partials;
+    scratch.partial_bytes = partial_bytes;
+    scratch.tile_counters = counters;
+    scratch.counter_count = counter_count;
+    status = status_word;
+}
+
 Context::~Context() {
     (void)cudaSetDevice(device);
     if (scratch.partials != nullptr) cudaFree(scratch.partials);

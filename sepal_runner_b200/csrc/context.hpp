@@ -42,6 +42,10 @@ struct Context {
     TensorMapEncodeFn encode = nullptr;
 
     Context(int device, std::size_t workspace_bytes);
+    /// A context over device memory that somebody else owns: nothing is allocated here, and such a context must never be destroyed
+    /// (the destructor would free what it does not own). For callers that cannot allocate; see gemm_tc.cu.
+    struct Borrowed {};
+    Context(Borrowed, int device, float* partials, std::size_t partial_bytes, unsigned* counters, std::size_t counter_count, int* status_word);
     ~Context();
     Context(const Context&) = delete;
     Context& operator=(const Context&) = delete;

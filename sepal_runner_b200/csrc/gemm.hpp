@@ -68,6 +68,12 @@ constexpr bool gemm_w8g_supports(std::size_t n, std::size_t k, std::size_t ld_x,
 void launch_gemm_f16(Context& ctx, const void* x, std::size_t ld_x, const void* w, std::size_t ld_w, void* y, std::size_t ld_y, bool y_half,
                      std::size_t t, std::size_t n, std::size_t k, Epilogue epilogue, int config, cudaStream_t stream);
 
+/// launch_gemm_f16 for callers that may not allocate device memory (see include/sepal_b200.h, sepal_b200_gemm_f16_noalloc): no
+/// Context; the split-k scratch is a fixed array inside the library. Runs on the current device. With `status_out` the call waits for
+/// the stream and stores the kernel status word there (0 = fine).
+void launch_gemm_f16_noalloc(const void* x, std::size_t ld_x, const void* w, std::size_t ld_w, void* y, std::size_t ld_y, bool y_half, std::size_t t,
+                             std::size_t n, std::size_t k, Epilogue epilogue, cudaStream_t stream, int* status_out);
+
 /// An int8 weight matrix as the tensor-core multiply reads it (the counterpart of the reference's SimtMatrix with
 /// SimtWeight::Int8Group, runner/cuda/src/gemm_simt_kernels.hpp:42-51). q is the reference's layout unchanged. The scales are
 /// "prepared" once at weight placement by launch_prepare_w8g_scales: transposed to group-major order, multiplied by a power of two

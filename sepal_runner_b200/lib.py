@@ -40,6 +40,7 @@ SIGNATURES = {
     "sepal_b200_status": (_i32, [_vp, _vp, C.POINTER(_i32)]),
     "sepal_b200_take_launch_count": (_u64, []),
     "sepal_b200_gemm_f16": (_i32, [_vp, _vp, _u64, _vp, _u64, _vp, _u64, _i32, _u64, _u64, _u64, _i32, _i32, _vp]),
+    "sepal_b200_gemm_f16_noalloc": (_i32, [_vp, _u64, _vp, _u64, _vp, _u64, _i32, _u64, _u64, _u64, _i32, _vp, C.POINTER(_i32)]),
     "sepal_b200_gemm_w8g": (_i32, [_vp, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _vp, _u64, _i32, _u64, _u64, _u64, _i32, _i32, _vp]),
     "sepal_b200_quantize_group_s8": (_i32, [_vp, _u64, _vp, _u64, _vp, _u64, _u64, _u64, _vp]),
     "sepal_b200_prepare_w8g_scales": (_i32, [_vp, _u64, _u64, _u64, _vp, _u64, _vp, _vp, _vp]),
@@ -289,6 +290,22 @@ class Provider:
 
     def gemm_f_raw(self, x_ptr: int, x_dtype: int, t: int, weight_id: int, y_ptr: int, beta: float = 0.0) -> None:
         _check(self._lib.sepal_b200_provider_gemm_f(self._h, x_ptr, x_dtype, t, weight_id, y_ptr, beta))
+
+
+def gemm_f16_noalloc(x, w, y, *, epilogue: int = STORE, stream=None, wait: bool = True) -> int:
+    """sepal_b200_gemm_f16_noalloc on CUDA tensors of the current device: y = epilogue(x @ w.T) without a Context and without any
+    device allocation inside the library. Returns the kernel status word when `wait` (0 = fine), else 0 right after enqueueing."""
+    import torch
+
+    assert x.dtype == torch.float16 and w.dtype == torch.float16 and x.stride(-1) == 1 and w.stride(-1) == 1 and y.stride(-1) == 1
+    t, k = x.shape
+    n = w.shape[0]
+    status = _i32(0)
+    _check(library().sepal_b200_gemm_f16_noalloc(x.data_ptr(), x.stride(0) if t > 1 else max(x.stride(0), k), w.data_ptr(),
+                                                 w.stride(0) if n > 1 else max(w.stride(0), k), y.data_ptr(), y.stride(0) if t > 1 else y.shape[1],
+                                                 1 if y.dtype == torch.float16 else 0, t, n, k, epilogue, _stream_ptr(stream),
+                                                 C.byref(status) if wait else None))
+    return status.value
 
 
 def host_alloc(nbytes: int) -> int:

@@ -7,6 +7,8 @@ Workloads (BASELINE.json `configs`, zero-based):
     w8g_down_m900   configs[1]: int8-group down projection, M = 900, K = 9728, N = 2560, fp16 activations, fp16 result   (default)
     f16_up_m900     configs[0]: fp16 up projection, M = 900, K = 2560, N = 9728
     f16_up_m4096 / w8g_down_m4096: the same products at the long-log call size
+    serve           configs[4]: 64 requests of 600-1200 tokens and 4 of 15,900 through the 36-layer GEMM-chain trunk (configs[3]'s
+                    stack), whole requests dealt longest-first to the GPUs; reports prefill tokens/s and p50 / p95 request latency
 
 A step is one batch of `calls_per_step` independent products of that shape (as many requests of M tokens), each on the next of a
 ring of operand sets whose total size exceeds the 126 MB L2, so no timed launch finds its operands in cache. `value` is the
@@ -39,9 +41,9 @@ WORKLOADS = {
     "f16_up_m4096": ("f16", 4096, 9728, 2560, 0),
 }
 # Every named trunk GEMM (N x K) for the per-shape table: SURVEY's list of projections at hidden 2560, MLP 9728.
-TRUNK_SHAPES = [("gate_up+swiglu", 19456, 2560, "swiglu"), ("down+residual", 2560, 9728, "add"), ("q", 4096, 2560, "store"),
-                ("kv", 2048, 2560, "store"), ("o+residual", 2560, 4096, "add"), ("dn_in", 8192, 2560, "store"),
-                ("dn_out+residual", 2560, 2048, "add")]
+TRUNK_SHAPES = [("gate_up+swiglu", 19456, 2560, "swiglu"), ("up (config 0)", 9728, 2560, "store"), ("down+residual", 2560, 9728, "add"),
+                ("q", 4096, 2560, "store"), ("k or v", 1024, 2560, "store"), ("qkv fused", 6144, 2560, "store"), ("o+residual", 2560, 4096, "add"),
+                ("dn_in", 8192, 2560, "store"), ("dn_out+residual", 2560, 2048, "add")]
 L2_BYTES = 126 * 1024 * 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -270,6 +272,11 @@ def run_ours(args):
         line["cpu_baseline"] = cpu_baseline(kind, m, n, k)
     if rank == 0 and world == 1 and args.shapes:
         line["shapes"] = shape_table(ctx, device, peak_tf)
+    if rank == 0 and world == 1 and args.trunk:
+        prov.close()
+        ctx.close()
+        torch.cuda.empty_cache()
+        line["trunk"] = trunk_numbers(local, float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])))
     if rank == 0:
         print(json.dumps(line), flush=True)
     prov.close()
@@ -319,6 +326,141 @@ def shape_table(ctx, device, peak_tf):
                              "frac_of_peak": round(tf / peak_tf, 3)})
     ctx.check_status()
     return rows
+
+
+def trunk_numbers(local, peak_tf):
+    """Whole passes through the 36-layer GEMM-chain trunk (BASELINE configs[2] and [3]): a 900-token alert and the 15,900-token log in
+    calls of 4096, fp16 weights and int8-group MLP weights. Host token ids in, last hidden state out (copies inside the timed region)."""
+    import numpy as np
+
+    import sepal_runner_b200 as sb
+
+    out = {}
+    rng = np.random.default_rng(4004)
+    for name, int8 in (("f16", 0), ("mlp_int8", 1)):
+        trunk = sb.Trunk(local, sb.TrunkConfig(mlp_int8=int8))
+        flops_tok = trunk.gemm_flops_per_token
+        row = {"weight_gb": round(trunk.weight_bytes / 1e9, 2), "gemm_gflop_per_token": round(flops_tok / 1e9, 3)}
+        for label, n in (("alert_900", 900), ("log_15900", 15900)):
+            tokens = rng.integers(0, 151936, n).astype(np.uint32)
+            trunk.run(tokens)
+            best = None
+            for _ in range(3):
+                t0 = time.perf_counter()
+                _, _, dev_ms = trunk.run(tokens)
+                wall = time.perf_counter() - t0
+                best = (wall, dev_ms) if best is None or wall < best[0] else best
+            row[label] = {"tokens_per_s": round(n / best[0], 1), "ms": round(best[0] * 1e3, 3), "device_ms": round(best[1], 3),
+                          "gemm_tflops": round(flops_tok * n / (best[1] * 1e-3) / 1e12, 1),
+                          "frac_of_peak": round(flops_tok * n / (best[1] * 1e-3) / 1e12 / peak_tf, 3)}
+        out[name] = row
+        trunk.close()
+    return out
+
+
+def run_serve(args):
+    """BASELINE configs[4]: request-sharded serving sweep. Every rank holds a full replica; requests are dealt whole, longest first,
+    each to the GPU with the least work so far; all requests arrive at time zero, so a request's latency is its completion time."""
+    import numpy as np
+    import torch
+
+    import sepal_runner_b200 as sb
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    rng = np.random.default_rng(5005)
+    lengths = [int(v) for v in rng.integers(600, 1201, 64)] + [15900] * 4
+    order = sorted(range(len(lengths)), key=lambda i: -lengths[i])
+    load = [0] * world
+    mine = []
+    for i in order:
+        g = min(range(world), key=lambda r: load[r])
+        load[g] += lengths[i]
+        if g == rank:
+            mine.append(i)
+    trunk = sb.Trunk(local, sb.TrunkConfig(mlp_int8=1 if args.int8 else 0))
+    tok_rng = np.random.default_rng(4004 + rank)
+    requests = {i: tok_rng.integers(0, 151936, lengths[i]).astype(np.uint32) for i in mine}
+    for i in mine[:1]:
+        trunk.run(requests[i][:900])  # warm up: first launches, kernel attributes
+    sampler = ClockSampler(local)
+    sampler.start()
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    passes = []
+    for _ in range(max(1, args.steps if args.steps <= 5 else 3)):
+        barrier()
+        t0 = time.perf_counter()
+        lat = {}
+        dev_ms = 0.0
+        for i in mine:
+            _, _, ms = trunk.run(requests[i])
+            dev_ms += ms
+            lat[i] = time.perf_counter() - t0
+        span = time.perf_counter() - t0
+        barrier()
+        passes.append((span, lat, dev_ms))
+    sampler.stop_flag.set()
+    sampler.join(timeout=2)
+    span, lat, dev_ms = min(passes, key=lambda p: p[0])
+    if world > 1:
+        import torch.distributed as dist
+
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (span, lat, dev_ms, len(mine), sum(lengths[i] for i in mine)))
+    else:
+        gathered = [(span, lat, dev_ms, len(mine), sum(lengths[i] for i in mine))]
+    if rank == 0:
+        makespan = max(g[0] for g in gathered)
+        all_lat = sorted(v for g in gathered for v in g[1].values())
+        total = sum(lengths)
+        peaks, peak_kind = measured_peaks()
+        peak_tf = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+        flops = trunk.gemm_flops_per_token * total
+        line = {
+            "metric": "prefill tokens/s (request-sharded, 36-layer GEMM-chain trunk)",
+            "value": round(total / makespan, 1),
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": len(passes),
+            "warmup": 1,
+            "ms_per_step": round(makespan * 1e3, 3),
+            "higher_is_better": True,
+            "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": "f16 x int8-group MLP" if args.int8 else "f16 x f16 -> f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": "serve (BASELINE configs[4]): 64 requests of 600-1200 tokens + 4 of 15900, whole requests per GPU, longest first",
+                       "total_tokens": total, "p50_latency_s": round(all_lat[len(all_lat) // 2], 4),
+                       "p95_latency_s": round(all_lat[min(len(all_lat) - 1, int(0.95 * len(all_lat)))], 4),
+                       "per_gpu": [{"requests": g[3], "tokens": g[4], "span_s": round(g[0], 4), "device_s": round(g[2] / 1e3, 4)} for g in gathered],
+                       "l2": "weights 7.3 GB per replica: far larger than the L2", "parallelism": f"request-sharded x{world}, full replica per GPU, no collective"},
+            "roofline": {"bound": "tensor", "achieved": round(flops / makespan / 1e12 / world, 1), "peak": peak_tf, "unit": "TFLOP/s",
+                         "frac": round(flops / makespan / 1e12 / world / peak_tf, 4),
+                         "peak_source": f"bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_kind}; the GEMMs run inside a long step)", "traffic": None},
+            "e2e": {"value": round(total / makespan, 1), "unit": "tokens/s", "h2d_bytes_per_step": total * 4, "d2h_bytes_per_step": len(lengths) * 2560 * 4,
+                    "note": "the same number: sepal_b200_trunk_run takes host token ids and returns the last hidden state to the host"},
+            "gpu_launches": int(sb.Context.take_launch_count()),
+            "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    trunk.close()
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
 
 
 def cpu_baseline(kind, m, n, k, reps: int = 5):
@@ -401,7 +543,9 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="w8g_down_m900", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="w8g_down_m900", choices=sorted(WORKLOADS) + ["serve"])
+    ap.add_argument("--int8", action="store_true", help="serve: store the MLP weights as int8 groups")
+    ap.add_argument("--no-trunk", dest="trunk", action="store_false", help="skip the whole-trunk passes")
     ap.add_argument("--calls-per-step", type=int, default=32)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-shapes", dest="shapes", action="store_false", help="skip the per-shape table")
@@ -409,7 +553,11 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
+        if args.workload == "serve":
+            args.workload = "w8g_down_m900"
         run_reference(args)
+    elif args.workload == "serve":
+        run_serve(args)
     else:
         run_ours(args)
 

@@ -81,7 +81,8 @@ SEPAL_B200_API uint64_t sepal_b200_take_launch_count(void);
  * Replaces launch_gemm_nt (runner/cuda/src/gemm_kernels.hpp:22-31) and the cublasGemmEx call of CudaEngine::Impl::gemm
  * (runner/cuda/src/cuda_engine.cpp:1093-1154); the epilogues replace launch_swiglu / launch_add after it (cuda_engine.cpp:1919-1945).
  * Requires K, ld_x, ld_w multiples of 8, N and ld_y even, x and w 16-byte aligned (gemm_nt_supports, gemm_kernels.hpp:34-36);
- * SWIGLU needs N a multiple of 128. config: -1 picks a schedule; 0..3 force one (tests). t == 0 is a no-op. */
+ * SWIGLU needs N a multiple of 128. config: -1 picks the tile width and schedule from the shape; other values force one (tests and
+ * tuning: 0..3, or a tile width that is a multiple of 16 up to 256, plus 1 for the even split of k or 2 for CTA pairs). t == 0 is a no-op. */
 SEPAL_B200_API int32_t sepal_b200_gemm_f16(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const void* w, uint64_t ld_w, void* y, uint64_t ld_y,
                                            int32_t y_half, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t config, void* stream);
 
@@ -108,7 +109,8 @@ SEPAL_B200_API int32_t sepal_b200_gemm_f16_noalloc(const void* x, uint64_t ld_x,
 /* binary16 activations x int8 weights with one scale per output row and group of 128 values of k (the gpu-w8g layout). Replaces
  * launch_gemm_simt with SimtWeight::Int8Group (runner/cuda/src/gemm_simt_kernels.hpp:42-56) and launch_gemm_w8a16
  * (runner/cuda/src/gemm_s8_kernels.hpp:51-57). q is int8 [N, ld_q]; scales_t / descale come from sepal_b200_prepare_w8g_scales.
- * Requires K a multiple of 128, ld_x a multiple of 8, ld_q a multiple of 16, ld_st >= N. */
+ * Requires K a multiple of 128, ld_x a multiple of 8, ld_q a multiple of 16, scales_t 16-byte aligned with ld_st >= N rounded up to
+ * 256 (the padding zero). */
 SEPAL_B200_API int32_t sepal_b200_gemm_w8g(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const int8_t* q, uint64_t ld_q, const void* scales_t,
                                            uint64_t ld_st, const float* descale, void* y, uint64_t ld_y, int32_t y_half, uint64_t t, uint64_t n,
                                            uint64_t k, int32_t epilogue, int32_t config, void* stream);
@@ -119,7 +121,8 @@ SEPAL_B200_API int32_t sepal_b200_quantize_group_s8(const float* src, uint64_t l
                                                     uint64_t rows, uint64_t k, void* stream);
 
 /* s float32 [N, ld_s] (the quantiser's layout) -> scales_t binary16 [groups, ld_st] and *descale (device float), the form the
- * tensor-core multiply reads: group-major, times the power of two that puts the largest scale in [128, 256). max_bits: 4 bytes of
+ * tensor-core multiply reads: group-major (give it rows of ld_st >= N rounded up to 256 binary16 values, zeroed beforehand), times
+ * the power of two that puts the largest scale in [128, 256). max_bits: 4 bytes of
  * device scratch. Part of weight placement, where the reference's put_simt quantises (runner/cuda/src/cuda_engine.cpp:580-627). */
 SEPAL_B200_API int32_t sepal_b200_prepare_w8g_scales(const float* s, uint64_t ld_s, uint64_t n, uint64_t groups, void* scales_t, uint64_t ld_st,
                                                      float* descale, uint32_t* max_bits, void* stream);
@@ -132,6 +135,43 @@ SEPAL_B200_API int32_t sepal_b200_pack_gate_up(const void* src, uint64_t src_str
 /* float32 <-> binary16 on the device, round to nearest even (runner/cuda/src/convert_kernels.hpp). */
 SEPAL_B200_API int32_t sepal_b200_float_to_half(const float* src, void* dst, uint64_t count, void* stream);
 SEPAL_B200_API int32_t sepal_b200_half_to_float(const void* src, float* dst, uint64_t count, void* stream);
+
+/* Token embedding gather and the zero-centred RMSNorm that produce a multiply's binary16 operand from the float32 residual stream
+ * (launch_embed / launch_rms_norm of runner/cuda/src/kernels_elementwise.hpp:41-46,85-95): x[t, :] = table[tokens[t], :] widened;
+ * y = x / sqrt(mean(x^2) + eps) * (1 + w), float32 in, binary16 out. hidden a multiple of 8; cols, ld_x, ld_y multiples of 4. */
+SEPAL_B200_API int32_t sepal_b200_embed(const void* table_half, const uint32_t* tokens, float* x, uint64_t rows, uint64_t hidden, uint64_t vocab,
+                                        void* stream);
+SEPAL_B200_API int32_t sepal_b200_rms_norm_half(const float* x, uint64_t ld_x, const float* w, void* y_half, uint64_t ld_y, uint64_t rows,
+                                                uint64_t cols, float eps, void* stream);
+
+/* ---- a synthetic trunk made of the projection GEMMs ---------------------------------------------------------------------------- */
+
+/* The caller of the hot path for whole-pass measurements: the reference's layer loop (runner/cuda/src/cuda_engine.cpp:1724-1952) with
+ * random N(0, 0.02) weights and the mixer cores wired out (the o projection reads the q band of the fused [q; k; v] product, the
+ * DeltaNet out projection the v band of the fused in-projection), so that a pass is embedding, RMSNorms and the GEMMs with their fused
+ * SwiGLU and residual epilogues. Layer l is an attention layer when l % 4 == 3. Counterpart of creating a CudaEngine from a config and
+ * random weights (runner/cuda/include/sepal/cuda/cuda_engine.hpp:395-403) and of CudaEngine::run. */
+typedef struct sepal_b200_trunk sepal_b200_trunk;
+typedef struct sepal_b200_trunk_config {
+    uint32_t layers, hidden, intermediate, vocab;
+    uint32_t attn_q, attn_kv;             /* q width; k and v width each (one fused [q; k; v] multiply) */
+    uint32_t dn_in, dn_v_offset, dn_v;    /* fused DeltaNet in-projection width; the band its out-projection reads */
+    uint32_t max_call_tokens;             /* rows per call; a longer request is cut into calls (gpu_decision_engine.cpp:233-245) */
+    uint32_t mlp_int8;                    /* 1: gate_up and down stored as int8 groups */
+    float eps;
+    uint64_t seed;
+} sepal_b200_trunk_config;
+SEPAL_B200_API int32_t sepal_b200_trunk_open(int32_t device, const sepal_b200_trunk_config* config, sepal_b200_trunk** out);
+SEPAL_B200_API void sepal_b200_trunk_close(sepal_b200_trunk* trunk);
+/* One request of n host token ids. last_hidden: `hidden` floats (host) for the last token's final hidden state; all_hidden: NULL or
+ * [n, hidden] floats (host). times_ms: NULL or 2 doubles (device time of the request by CUDA events; reserved). Returns when done. */
+SEPAL_B200_API int32_t sepal_b200_trunk_run(sepal_b200_trunk* trunk, const uint32_t* tokens, uint64_t n, float* last_hidden, float* all_hidden,
+                                            double* times_ms);
+/* Copies a stored weight to the host (size-query protocol: host_out NULL only reports *needed). which: 0 embedding, 1 input norm,
+ * 2 mixer in-projection, 3 mixer out-projection, 4 post norm, 5 packed [gate; up], 6 down. */
+SEPAL_B200_API int32_t sepal_b200_trunk_weight(sepal_b200_trunk* trunk, uint32_t layer, int32_t which, void* host_out, uint64_t capacity,
+                                               uint64_t* needed);
+SEPAL_B200_API int32_t sepal_b200_trunk_info(sepal_b200_trunk* trunk, uint64_t* gemm_flops_per_token, uint64_t* weight_bytes);
 
 /* ---- provider on host pointers ------------------------------------------------------------------------------------------------ */
 

@@ -11,6 +11,8 @@ from .lib import (  # noqa: F401
     Context,
     Provider,
     SepalB200Error,
+    Trunk,
+    TrunkConfig,
     W8gWeight,
     library,
     library_path,

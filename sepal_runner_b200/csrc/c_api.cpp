@@ -9,6 +9,7 @@
 
 #include "gemm.hpp"
 #include "provider.hpp"
+#include "trunk.hpp"
 
 using namespace sepal::b200;
 
@@ -19,6 +20,11 @@ struct sepal_b200_ctx {
 struct sepal_b200_provider {
     B200Gemm gemm;
     sepal_b200_provider(int device, std::size_t bytes) : gemm(device, bytes) {}
+};
+
+struct sepal_b200_trunk {
+    Trunk trunk;
+    sepal_b200_trunk(int device, const TrunkConfig& c) : trunk(device, c) {}
 };
 
 namespace {
@@ -159,6 +165,73 @@ int32_t sepal_b200_half_to_float(const void* src, float* dst, uint64_t count, vo
             require(dst, "dst");
         }
         launch_half_to_float(src, dst, count, static_cast<cudaStream_t>(stream));
+    });
+}
+
+int32_t sepal_b200_embed(const void* table_half, const uint32_t* tokens, float* x, uint64_t rows, uint64_t hidden, uint64_t vocab, void* stream) {
+    return guarded([&] {
+        if (rows != 0) {
+            require(table_half, "table");
+            require(tokens, "tokens");
+            require(x, "x");
+        }
+        launch_embed(table_half, tokens, x, rows, hidden, vocab, static_cast<cudaStream_t>(stream));
+    });
+}
+int32_t sepal_b200_rms_norm_half(const float* x, uint64_t ld_x, const float* w, void* y_half, uint64_t ld_y, uint64_t rows, uint64_t cols, float eps,
+                                 void* stream) {
+    return guarded([&] {
+        if (rows != 0) {
+            require(x, "x");
+            require(w, "w");
+            require(y_half, "y");
+        }
+        launch_rms_norm_half(x, ld_x, w, y_half, ld_y, rows, cols, eps, static_cast<cudaStream_t>(stream));
+    });
+}
+
+int32_t sepal_b200_trunk_open(int32_t device, const sepal_b200_trunk_config* config, sepal_b200_trunk** out) {
+    if (out != nullptr) *out = nullptr;
+    return guarded([&] {
+        require(out, "out");
+        require(config, "config");
+        TrunkConfig c;
+        c.layers = config->layers;
+        c.hidden = config->hidden;
+        c.intermediate = config->intermediate;
+        c.vocab = config->vocab;
+        c.attn_q = config->attn_q;
+        c.attn_kv = config->attn_kv;
+        c.dn_in = config->dn_in;
+        c.dn_v_offset = config->dn_v_offset;
+        c.dn_v = config->dn_v;
+        c.max_call_tokens = config->max_call_tokens;
+        c.mlp_int8 = config->mlp_int8;
+        c.eps = config->eps;
+        c.seed = config->seed;
+        *out = new sepal_b200_trunk(device, c);
+    });
+}
+void sepal_b200_trunk_close(sepal_b200_trunk* trunk) { delete trunk; }
+int32_t sepal_b200_trunk_run(sepal_b200_trunk* trunk, const uint32_t* tokens, uint64_t n, float* last_hidden, float* all_hidden, double* times_ms) {
+    return guarded([&] {
+        require(trunk, "trunk");
+        trunk->trunk.run(tokens, n, last_hidden, all_hidden, times_ms);
+    });
+}
+int32_t sepal_b200_trunk_weight(sepal_b200_trunk* trunk, uint32_t layer, int32_t which, void* host_out, uint64_t capacity, uint64_t* needed) {
+    return guarded([&] {
+        require(trunk, "trunk");
+        if (which < 0 || which > 6) throw std::invalid_argument("which must be 0 .. 6");
+        const std::size_t bytes = trunk->trunk.weight(layer, static_cast<TrunkWeight>(which), host_out, capacity);
+        if (needed != nullptr) *needed = bytes;
+    });
+}
+int32_t sepal_b200_trunk_info(sepal_b200_trunk* trunk, uint64_t* gemm_flops_per_token, uint64_t* weight_bytes) {
+    return guarded([&] {
+        require(trunk, "trunk");
+        if (gemm_flops_per_token != nullptr) *gemm_flops_per_token = trunk->trunk.gemm_flops_per_token();
+        if (weight_bytes != nullptr) *weight_bytes = trunk->trunk.weight_bytes();
     });
 }
 

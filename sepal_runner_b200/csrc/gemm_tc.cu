@@ -1,12 +1,14 @@
 // The trunk projection GEMM for sm_100a: Y = epilogue(X W^T) with binary16 operands on the 5th-generation tensor cores.
 //
 // One persistent CTA per SM, specialised by warp:
-//   warp 0      TMA producer: streams [128 x 64] tiles of X and [BN x 64] tiles of W into a ring of shared-memory stages
+//   warp 0      TMA producer: streams [128 x 64] tiles of X and [bn x 64] tiles of W into a ring of shared-memory stages
 //               (cp.async.bulk.tensor, 128-byte swizzle, completion counted on an mbarrier per stage). No cluster multicast.
-//   warp 1      MMA issuer: one thread issues tcgen05.mma (M 128, N BN, K 16, kind::f16, float32 accumulator in tensor memory),
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M 128, N bn, K 16, kind::f16, float32 accumulator in tensor memory),
 //               four per stage; tcgen05.commit frees the stage and, after the last one of a work unit, hands the accumulator over.
 //   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its 32 lanes), apply Store / Add / SwiGLU, write Y. Two accumulators
-//               (2 x BN columns of tensor memory) alternate, so the epilogue of one unit overlaps the MMAs of the next.
+//               (2 x 256 columns of tensor memory) alternate, so the epilogue of one unit overlaps the MMAs of the next.
+//               The tile width bn is a run-time value (a multiple of 16 up to 256) chosen per shape so that the tiles fill whole
+//               waves of the SMs.
 //   warps 6..9  (int8 weights only) converters: widen a raw int8 W tile exactly to binary16, multiply by the group's scale and store
 //               it in the swizzled layout the MMA reads (see the W8 notes below).
 //
@@ -50,6 +52,7 @@ struct GemmParams {
     unsigned long long ld_y;
     unsigned m, n, k;                       // rows of X, rows of W (packed width for SwiGLU), depth
     unsigned m_tiles, n_tiles, k_iters, tiles;
+    unsigned bn, stages, stage_bytes;       // tile width (columns of W per tile), depth of the ring, bytes of one stage
     unsigned epilogue, y_half, vec_ok;      // vec_ok: Y rows allow 16-byte accesses
     unsigned stream_k;                      // 0: whole tiles round-robin; 1: all k iterations split evenly over the CTAs
     float* partials;
@@ -60,18 +63,28 @@ struct GemmParams {
     const float* descale;                   // W8: device scalar the sums are multiplied by
 };
 
-template <int BN, bool W8>
+constexpr int kMaxStages = 8;
+constexpr int kXBytes = kBM * kBK * 2;              // one X tile: 128 rows of 128 bytes
+constexpr int kAccStride = 256;                     // tensor-memory columns between the two accumulators
+constexpr int kTmemCols = 512;
+constexpr int kBarriers = 2 * kMaxStages + 4 + 4;   // full, empty, accumulator full / empty, converted full / empty
+constexpr int kTailBytes = kBarriers * 8 + 64;
+constexpr int kSmemLimit = 232448;                  // 227 KB: the most one CTA may have
+constexpr int kSlotFloats = kBM * 256;              // scratch slot of one partial tile (sized for the widest tile)
+
+template <bool W8>
 struct Shape {
-    static constexpr int kStages = W8 ? 4 : (BN == 256 ? 4 : 6);
-    static constexpr int kXBytes = kBM * kBK * 2;
-    static constexpr int kWBytes = W8 ? BN * kBK : BN * kBK * 2;  // raw tile as it comes from memory
-    static constexpr int kStageBytes = kXBytes + kWBytes;
-    static constexpr int kConvBytes = W8 ? BN * kBK * 2 : 0;       // one converted W tile
-    static constexpr int kConvBuffers = W8 ? 2 : 0;
-    static constexpr int kTmemCols = 2 * BN;
-    static constexpr int kBarriers = 2 * kStages + 4 + 2 * 2;
     static constexpr int kThreads = W8 ? 320 : 192;
-    static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kConvBuffers * kConvBytes + kBarriers * 8 + 64;
+    static constexpr int kConvBuffers = W8 ? 2 : 0;
+    __host__ __device__ static constexpr unsigned w_bytes(unsigned bn) { return W8 ? bn * kBK : bn * kBK * 2; }  // raw W tile
+    __host__ __device__ static constexpr unsigned stage_bytes(unsigned bn) { return kXBytes + w_bytes(bn); }
+    __host__ __device__ static constexpr unsigned conv_bytes(unsigned bn) { return W8 ? bn * kBK * 2 : 0; }        // one converted W tile
+    static unsigned stages_for(unsigned bn) {
+        const unsigned room = kSmemLimit - 1024 - kTailBytes - kConvBuffers * conv_bytes(bn);
+        const unsigned s = room / stage_bytes(bn);
+        return s > kMaxStages ? kMaxStages : s;
+    }
+    static unsigned smem_bytes(unsigned bn, unsigned stages) { return 1024 + stages * stage_bytes(bn) + kConvBuffers * conv_bytes(bn) + kTailBytes; }
 };
 
 // A CTA's list of work units.
@@ -140,6 +153,8 @@ __device__ __forceinline__ float swiglu(float g, float u) {
 }
 
 // Writes 32 consecutive results of one row. `col` is the first output column; columns at or past n_out are dropped.
+// With the residual epilogue all the old values of the piece are loaded before the first store: loads interleaved with stores to
+// the same array would wait for one another, one memory round trip each.
 __device__ __forceinline__ void store_chunk(const GemmParams& p, unsigned row, unsigned col, unsigned n_out, const float (&v)[32]) {
     if (row >= p.m || col >= n_out) return;
     const bool add = p.epilogue == 1;
@@ -147,13 +162,17 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, unsigned row, u
     if (p.y_half != 0) {
         __half* out = static_cast<__half*>(p.y) + static_cast<size_t>(row) * p.ld_y + col;
         if (whole) {
+            uint4 old[4];
+            if (add) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) old[q] = __ldcg(reinterpret_cast<const uint4*>(out + 8 * q));
+            }
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 uint4 packed;
                 __half2 h[4];
                 if (add) {
-                    const uint4 old = *reinterpret_cast<const uint4*>(out + 8 * q);
-                    const __half2* o = reinterpret_cast<const __half2*>(&old);
+                    const __half2* o = reinterpret_cast<const __half2*>(&old[q]);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const float2 f = __half22float2(o[j]);
@@ -178,13 +197,15 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, unsigned row, u
     } else {
         float* out = static_cast<float*>(p.y) + static_cast<size_t>(row) * p.ld_y + col;
         if (whole) {
+            float4 old[8];
+            if (add) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) old[q] = __ldcg(reinterpret_cast<const float4*>(out + 4 * q));
+            }
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 float4 r = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                if (add) {
-                    const float4 old = *reinterpret_cast<const float4*>(out + 4 * q);
-                    r = make_float4(__fadd_rn(old.x, r.x), __fadd_rn(old.y, r.y), __fadd_rn(old.z, r.z), __fadd_rn(old.w, r.w));
-                }
+                if (add) r = make_float4(__fadd_rn(old[q].x, r.x), __fadd_rn(old[q].y, r.y), __fadd_rn(old[q].z, r.z), __fadd_rn(old[q].w, r.w));
                 *reinterpret_cast<float4*>(out + 4 * q) = r;
             }
         } else {
@@ -207,14 +228,13 @@ __device__ __forceinline__ void load_acc_tmem(uint32_t taddr, unsigned c, float 
 
 // The same columns as the sum, in k order, of the partial tiles the contributing CTAs left in scratch memory.
 // Slot layout: float4 index (chunk * 8 + quad) * 128 + row, so a warp's accesses are contiguous.
-template <int BN>
 __device__ __forceinline__ void load_acc_partials(const GemmParams& p, unsigned long long total, unsigned grid, unsigned tile_start, unsigned c_first,
                                                   unsigned c_last, unsigned row, unsigned c, float (&v)[32]) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = 0.0f;
     for (unsigned cta = c_first; cta <= c_last; ++cta) {
         const unsigned slot = 2 * cta + (range_lo(total, cta, grid) >= tile_start ? 0u : 1u);
-        const float4* src = reinterpret_cast<const float4*>(p.partials) + static_cast<size_t>(slot) * (kBM * BN / 4) + (c / 32) * 8 * kBM + row;
+        const float4* src = reinterpret_cast<const float4*>(p.partials) + static_cast<size_t>(slot) * (kSlotFloats / 4) + (c / 32) * 8 * kBM + row;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
             const float4 t = __ldcg(src + q * kBM);
@@ -227,14 +247,15 @@ __device__ __forceinline__ void load_acc_partials(const GemmParams& p, unsigned 
 }
 
 // Applies the epilogue to a whole tile row by row; `load(c, v)` yields accumulator columns [c, c + 32) of this thread's row.
-template <int BN, class Load>
+template <class Load>
 __device__ __forceinline__ void finish_tile(const GemmParams& p, unsigned m_tile, unsigned n_tile, unsigned row_in_tile, float descale, Load&& load) {
     const unsigned row = m_tile * kBM + row_in_tile;
+    const unsigned bn = p.bn;
     if (p.epilogue == 2) {
-        // Packed columns: blocks of 128 = 64 gate then 64 up. Output column of gate column 128 b + r is 64 b + r.
+        // Packed columns: blocks of 128 = 64 gate then 64 up (bn is 128 or 256). Output column of gate column 128 b + r is 64 b + r.
         const unsigned n_out = p.n / 2;
 #pragma unroll 1
-        for (unsigned b = 0; b < BN / 128; ++b) {
+        for (unsigned b = 0; b < bn / 128; ++b) {
 #pragma unroll 1
             for (unsigned h = 0; h < 2; ++h) {
                 float g[32], u[32];
@@ -242,43 +263,49 @@ __device__ __forceinline__ void finish_tile(const GemmParams& p, unsigned m_tile
                 load(b * 128 + 64 + h * 32, u);
 #pragma unroll
                 for (int j = 0; j < 32; ++j) g[j] = swiglu(__fmul_rn(g[j], descale), __fmul_rn(u[j], descale));
-                store_chunk(p, row, n_tile * (BN / 2) + b * 64 + h * 32, n_out, g);
+                store_chunk(p, row, n_tile * (bn / 2) + b * 64 + h * 32, n_out, g);
             }
         }
     } else {
+        // Columns past the tile's own width (the last 32-column piece of a tile whose width is not a multiple of 32) belong to nobody.
+        const unsigned n_end = min(p.n, (n_tile + 1) * bn);
 #pragma unroll 1
-        for (unsigned c = 0; c < BN; c += 32) {
+        for (unsigned c = 0; c < bn; c += 32) {
             float v[32];
             load(c, v);
             if (descale != 1.0f) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], descale);
             }
-            store_chunk(p, row, n_tile * BN + c, p.n, v);
+            store_chunk(p, row, n_tile * bn + c, n_end, v);
         }
     }
 }
 
-template <int BN, bool W8>
-__global__ void __launch_bounds__(Shape<BN, W8>::kThreads, 1)
+template <bool W8>
+__global__ void __launch_bounds__(Shape<W8>::kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
-    using S = Shape<BN, W8>;
+    using S = Shape<W8>;
+    const unsigned bn = p.bn;
+    const int stages = static_cast<int>(p.stages);
+    const unsigned stage_bytes = p.stage_bytes;
+    const unsigned conv_bytes = S::conv_bytes(bn);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_addr(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;  // operand tiles start on 1024-byte boundaries (128-byte swizzle)
     uint8_t* const smem = smem_raw + (base - raw_addr);
 
     const uint32_t stages_addr = base;
-    const uint32_t conv_addr = base + S::kStages * S::kStageBytes;
-    uint8_t* const tail = smem + S::kStages * S::kStageBytes + S::kConvBuffers * S::kConvBytes;
+    const uint32_t conv_addr = base + stages * stage_bytes;
+    uint8_t* const tail = smem + stages * stage_bytes + S::kConvBuffers * conv_bytes;
     const uint32_t bars = ptx::smem_addr(tail);
     const auto full_bar = [&](int s) { return bars + 8u * s; };
-    const auto empty_bar = [&](int s) { return bars + 8u * (S::kStages + s); };
-    const auto acc_full_bar = [&](int a) { return bars + 8u * (2 * S::kStages + a); };
-    const auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * S::kStages + 2 + a); };
-    const auto conv_full_bar = [&](int c) { return bars + 8u * (2 * S::kStages + 4 + c); };
-    const auto conv_empty_bar = [&](int c) { return bars + 8u * (2 * S::kStages + 6 + c); };
-    unsigned* const words = reinterpret_cast<unsigned*>(tail + S::kBarriers * 8);
+    const auto empty_bar = [&](int s) { return bars + 8u * (kMaxStages + s); };
+    const auto acc_full_bar = [&](int a) { return bars + 8u * (2 * kMaxStages + a); };
+    const auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * kMaxStages + 2 + a); };
+    const auto conv_full_bar = [&](int c) { return bars + 8u * (2 * kMaxStages + 4 + c); };
+    const auto conv_empty_bar = [&](int c) { return bars + 8u * (2 * kMaxStages + 6 + c); };
+    unsigned* const words = reinterpret_cast<unsigned*>(tail + kBarriers * 8);
     unsigned* const tmem_slot = words;                 // base address of the tensor memory allocation
     volatile unsigned* const abort_flag = words + 1;   // raised by the first wait that runs out
     volatile unsigned* const fix = words + 2;          // [0] this CTA reduces the tile, [1] first and [2] last contributing CTA
@@ -287,7 +314,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const unsigned grid = gridDim.x, cta = blockIdx.x;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < S::kStages; ++s) {
+        for (int s = 0; s < stages; ++s) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), W8 ? 1 + 4 : 1);  // the MMA's commit (+ one arrival per converter warp)
         }
@@ -304,7 +331,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         ptx::tma_prefetch_descriptor(&map_w);
     }
     if (warp == 1) {
-        ptx::tmem_alloc(ptx::smem_addr(tmem_slot), S::kTmemCols);
+        ptx::tmem_alloc(ptx::smem_addr(tmem_slot), kTmemCols);
         ptx::tmem_relinquish();
     }
     ptx::tc_fence_before_sync();
@@ -328,12 +355,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         ok = false;
                         break;
                     }
-                    const uint32_t dst = stages_addr + stage * S::kStageBytes;
-                    ptx::mbar_arrive_expect_tx(full_bar(stage), S::kStageBytes);
+                    const uint32_t dst = stages_addr + stage * stage_bytes;
+                    ptx::mbar_arrive_expect_tx(full_bar(stage), stage_bytes);
                     ptx::tma_load_2d(dst, &map_x, full_bar(stage), static_cast<int>(kk * kBK), static_cast<int>(m_tile * kBM));
-                    ptx::tma_load_2d(dst + S::kXBytes, &map_w, full_bar(stage), static_cast<int>(kk * kBK), static_cast<int>(n_tile * BN));
+                    ptx::tma_load_2d(dst + kXBytes, &map_w, full_bar(stage), static_cast<int>(kk * kBK), static_cast<int>(n_tile * bn));
                     ++issued;
-                    if (++stage == S::kStages) {
+                    if (++stage == stages) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -342,12 +369,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             if (!ok) {
                 // Giving up: let the copies still in flight land before the CTA's shared memory is released. The last
                 // min(issued, stages) fills are the ones that may not have been consumed; each has its own full barrier.
-                const unsigned pending = issued < static_cast<unsigned>(S::kStages) ? issued : static_cast<unsigned>(S::kStages);
+                const unsigned pending = issued < static_cast<unsigned>(stages) ? issued : static_cast<unsigned>(stages);
                 int s = stage;
                 unsigned ph = phase;
                 for (unsigned i = 0; i < pending; ++i) {
                     if (--s < 0) {
-                        s = S::kStages - 1;
+                        s = stages - 1;
                         ph ^= 1u;
                     }
                     const long long t0 = clock64();
@@ -359,7 +386,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = ptx::instr_desc_f16_f32acc(kBM, BN);
+            const uint32_t idesc = ptx::instr_desc_f16_f32acc(kBM, bn);
             Walker walk(p, cta, grid);
             unsigned tile, kb, ke;
             int stage = 0;
@@ -372,22 +399,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             while (ok && walk.next(tile, kb, ke)) {
                 if (!wait_barrier(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kStatusMmaAccEmpty)) break;
                 ptx::tc_fence_after_sync();
-                const uint32_t d = tmem_base + static_cast<uint32_t>(acc * BN);
+                const uint32_t d = tmem_base + static_cast<uint32_t>(acc * kAccStride);
                 for (unsigned kk = kb; kk < ke; ++kk) {
                     if (!wait_barrier(full_bar(stage), phase, abort_flag, p.status, kStatusMmaFull)) {
                         ok = false;
                         break;
                     }
-                    uint32_t w_tile = stages_addr + stage * S::kStageBytes + S::kXBytes;
+                    uint32_t w_tile = stages_addr + stage * stage_bytes + kXBytes;
                     if constexpr (W8) {
                         if (!wait_barrier(conv_full_bar(conv), conv_phase, abort_flag, p.status, kStatusMmaConvFull)) {
                             ok = false;
                             break;
                         }
-                        w_tile = conv_addr + conv * S::kConvBytes;
+                        w_tile = conv_addr + conv * conv_bytes;
                     }
                     ptx::tc_fence_after_sync();
-                    const uint64_t desc_x = ptx::smem_desc_k_major_sw128(stages_addr + stage * S::kStageBytes);
+                    const uint64_t desc_x = ptx::smem_desc_k_major_sw128(stages_addr + stage * stage_bytes);
                     const uint64_t desc_w = ptx::smem_desc_k_major_sw128(w_tile);
 #pragma unroll
                     for (int j = 0; j < kBK / 16; ++j) {
@@ -402,7 +429,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                             conv_phase ^= 1u;
                         }
                     }
-                    if (++stage == S::kStages) {
+                    if (++stage == stages) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -434,18 +461,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             if (!arrived || *abort_flag != 0) break;
             ptx::tc_fence_after_sync();
             const unsigned m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
-            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + static_cast<uint32_t>(acc * BN);
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + static_cast<uint32_t>(acc * kAccStride);
             const bool partial = kb != 0 || ke != p.k_iters;
             if (!partial) {
-                finish_tile<BN>(p, m_tile, n_tile, row_in_tile, descale, [&](unsigned c, float (&v)[32]) { load_acc_tmem(taddr, c, v); });
+                finish_tile(p, m_tile, n_tile, row_in_tile, descale, [&](unsigned c, float (&v)[32]) { load_acc_tmem(taddr, c, v); });
                 ptx::tc_fence_before_sync();
                 ptx::mbar_arrive(acc_empty_bar(acc));
             } else {
                 // Leave the partial sums in this CTA's scratch slot (0 for its first unit, 1 otherwise) and hand the accumulator back.
                 const unsigned slot = 2 * cta + (unit == 0 ? 0u : 1u);
-                float4* dst = reinterpret_cast<float4*>(p.partials) + static_cast<size_t>(slot) * (kBM * BN / 4) + row_in_tile;
+                float4* dst = reinterpret_cast<float4*>(p.partials) + static_cast<size_t>(slot) * (kSlotFloats / 4) + row_in_tile;
 #pragma unroll 1
-                for (unsigned c = 0; c < BN; c += 32) {
+                for (unsigned c = 0; c < bn; c += 32) {
                     float v[32];
                     load_acc_tmem(taddr, c, v);
 #pragma unroll
@@ -479,8 +506,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 epilogue_barrier();  // the words may be rewritten by the next partial unit
                 if (reduce) {
                     __threadfence();
-                    finish_tile<BN>(p, m_tile, n_tile, row_in_tile, descale, [&](unsigned c, float (&v)[32]) {
-                        load_acc_partials<BN>(p, total, grid, tile_start, c_first, c_last, row_in_tile, c, v);
+                    finish_tile(p, m_tile, n_tile, row_in_tile, descale, [&](unsigned c, float (&v)[32]) {
+                        load_acc_partials(p, total, grid, tile_start, c_first, c_last, row_in_tile, c, v);
                     });
                 }
             }
@@ -493,7 +520,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     } else {
         // ---------------------------------------------------------------- int8 -> binary16 converters (W8 only)
         if constexpr (W8) {
-            // The raw tile is [BN rows][64 bytes] unswizzled; thread i of the 128 converters takes 16-byte piece i, i + 128, ... of it,
+            // The raw tile is [bn rows][64 bytes] unswizzled (bn is 128 or 256 here); thread i of the 128 converters takes 16-byte piece i, i + 128, ... of it,
             // that is row (piece / 4), k offset 16 * (piece % 4): a warp reads 512 contiguous bytes. Its 16 values become two 16-byte
             // pieces (2 j, 2 j + 1) of the row's 128-byte binary16 row, stored at piece index XOR (row % 8): the 128-byte swizzle.
             // int8 -> binary16 exactly: byte ^ 0x80 is b + 128 in [1, 255]; 0x6400 | that is the binary16 number 1024 + 128 + b (spacing
@@ -512,12 +539,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 const unsigned n_tile = tile / p.m_tiles;
                 for (unsigned kk = kb; kk < ke; ++kk) {
                     // scales of this thread's rows for the group of this k block (rows past N read as zero)
-                    __half2 sc[BN / 32];
+                    __half2 sc[8];
                     const __half* srow = p.scales_t + static_cast<size_t>((kk * kBK) / kGroup) * p.ld_st;
 #pragma unroll
-                    for (int i = 0; i < BN / 32; ++i) {
-                        const unsigned n = n_tile * BN + (ct + 128 * i) / 4;
-                        sc[i] = n < p.n ? __half2half2(srow[n]) : __half2half2(__ushort_as_half(0));
+                    for (int i = 0; i < 8; ++i) {
+                        const unsigned n = n_tile * bn + (ct + 128 * i) / 4;
+                        sc[i] = (i < static_cast<int>(bn / 32) && n < p.n) ? __half2half2(srow[n]) : __half2half2(__ushort_as_half(0));
                     }
                     bool got = wait_barrier(full_bar(stage), phase, abort_flag, p.status, kStatusConvFull);
                     got = got && wait_barrier(conv_empty_bar(conv), conv_phase ^ 1u, abort_flag, p.status, kStatusConvEmpty);
@@ -525,10 +552,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         ok = false;
                         break;
                     }
-                    const uint8_t* raw = smem + stage * S::kStageBytes + S::kXBytes;
-                    uint8_t* out = smem + S::kStages * S::kStageBytes + conv * S::kConvBytes;
+                    const uint8_t* raw = smem + stage * stage_bytes + kXBytes;
+                    uint8_t* out = smem + stages * stage_bytes + conv * conv_bytes;
 #pragma unroll
-                    for (int i = 0; i < BN / 32; ++i) {
+                    for (int i = 0; i < 8; ++i) {
+                        if (i >= static_cast<int>(bn / 32)) break;
                         const unsigned piece = ct + 128 * i;
                         const unsigned row = piece / 4, part = piece % 4;
                         const uint4 q = *reinterpret_cast<const uint4*>(raw + piece * 16);
@@ -559,7 +587,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         conv = 0;
                         conv_phase ^= 1u;
                     }
-                    if (++stage == S::kStages) {
+                    if (++stage == stages) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -572,41 +600,622 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __syncthreads();
     if (warp == 1) {
         ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc(tmem_base, S::kTmemCols);
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 
-template <int BN, bool W8>
-void launch_config(const Context& ctx, const CUtensorMap& map_x, const CUtensorMap& map_w, GemmParams p, bool stream_k, cudaStream_t stream) {
-    using S = Shape<BN, W8>;
+// ---- the same product on CTA pairs ---------------------------------------------------------------------------------------------
+//
+// An SM takes 64 bytes per cycle from the L2. A lone CTA computing a 128 x 256 tile needs 96 (one k step of 16: 4 KB of X and 8 KB of
+// W for 128 cycles of tensor pipe), so it runs at two thirds of the pipe. Two CTAs of a cluster computing a 256 x bn tile together
+// (tcgen05.mma.cta_group::2: each CTA holds 128 rows of X and of the accumulator, and HALF of the W tile, which the pair's MMA reads
+// from both shared memories) need 64 each. One thread of the pair's first CTA issues the MMAs; tcgen05.commit signals both CTAs.
+// Whole tiles only (no split of k), fp16 weights only. No TMA multicast: each CTA loads its own operands.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+    const unsigned bn = p.bn, half = p.bn / 2;
+    const int stages = static_cast<int>(p.stages);
+    const unsigned stage_bytes = p.stage_bytes;  // per CTA: 128 rows of X and bn / 2 rows of W
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_addr(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* const smem = smem_raw + (base - raw_addr);
+    const uint32_t stages_addr = base;
+    uint8_t* const tail = smem + stages * stage_bytes;
+    const uint32_t bars = ptx::smem_addr(tail);
+    const auto full_bar = [&](int s) { return bars + 8u * s; };
+    const auto empty_bar = [&](int s) { return bars + 8u * (kMaxStages + s); };
+    const auto acc_full_bar = [&](int a) { return bars + 8u * (2 * kMaxStages + a); };
+    const auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * kMaxStages + 2 + a); };
+    unsigned* const words = reinterpret_cast<unsigned*>(tail + kBarriers * 8);
+    unsigned* const tmem_slot = words;
+    volatile unsigned* const abort_flag = words + 1;
+
+    const unsigned warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const unsigned rank = ptx::cluster_ctarank();       // 0: issues the MMAs; 1: its partner
+    const unsigned pair = blockIdx.x / 2, pairs = gridDim.x / 2;
+    const unsigned m_pair_tiles = (p.m + 2 * kBM - 1) / (2 * kBM);
+    const unsigned pair_tiles = m_pair_tiles * p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            ptx::mbar_init(full_bar(s), 1);   // the first CTA's producer announces the bytes of both CTAs
+            ptx::mbar_init(empty_bar(s), 1);  // the commit of the pair's MMAs, delivered to both CTAs
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(acc_full_bar(a), 1);
+            ptx::mbar_init(acc_empty_bar(a), 256);  // the epilogue threads of both CTAs (used in the first CTA only)
+        }
+        words[1] = 0;
+        ptx::fence_barrier_init();
+        ptx::tma_prefetch_descriptor(&map_x);
+        ptx::tma_prefetch_descriptor(&map_w);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_addr(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();  // the partner's barriers exist before anything signals them
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            unsigned phase = 0, issued = 0;
+            bool ok = true;
+            for (unsigned tile = pair; ok && tile < pair_tiles; tile += pairs) {
+                const unsigned m_pt = tile % m_pair_tiles, n_tile = tile / m_pair_tiles;
+                const int row_x = static_cast<int>(m_pt * 2 * kBM + rank * kBM);
+                const int row_w = static_cast<int>(n_tile * bn + rank * half);
+                for (unsigned kk = 0; kk < p.k_iters; ++kk) {
+                    if (!wait_barrier(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kStatusProducerEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t dst = stages_addr + stage * stage_bytes;
+                    const uint32_t full_first = ptx::map_to_cta(full_bar(stage), 0);  // completion is counted in the first CTA
+                    if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * stage_bytes);
+                    ptx::tma_load_2d_pair(dst, &map_x, full_first, static_cast<int>(kk * kBK), row_x);
+                    ptx::tma_load_2d_pair(dst + kXBytes, &map_w, full_first, static_cast<int>(kk * kBK), row_w);
+                    ++issued;
+                    if (++stage == stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            (void)issued;  // an aborted pair ends at the cluster barrier below, after every wait of both CTAs has run out
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = ptx::instr_desc_f16_f32acc(2 * kBM, bn);
+            int stage = 0;
+            unsigned phase = 0;
+            int acc = 0;
+            unsigned acc_phase = 0;
+            bool ok = true;
+            for (unsigned tile = pair; ok && tile < pair_tiles; tile += pairs) {
+                if (!wait_barrier(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kStatusMmaAccEmpty)) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t d = tmem_base + static_cast<uint32_t>(acc * kAccStride);
+                for (unsigned kk = 0; kk < p.k_iters; ++kk) {
+                    if (!wait_barrier(full_bar(stage), phase, abort_flag, p.status, kStatusMmaFull)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint64_t desc_x = ptx::smem_desc_k_major_sw128(stages_addr + stage * stage_bytes);
+                    const uint64_t desc_w = ptx::smem_desc_k_major_sw128(stages_addr + stage * stage_bytes + kXBytes);
+#pragma unroll
+                    for (int j = 0; j < kBK / 16; ++j) ptx::mma_f16_ss_pair(d, desc_x + 2u * j, desc_w + 2u * j, idesc, (kk > 0 || j > 0) ? 1u : 0u);
+                    ptx::mma_commit_pair(empty_bar(stage), 3);
+                    if (++stage == stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::mma_commit_pair(acc_full_bar(acc), 3);
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        const unsigned quarter = warp % 4;
+        const unsigned row_in_tile = quarter * 32 + lane;
+        int acc = 0;
+        unsigned acc_phase = 0;
+        for (unsigned tile = pair; tile < pair_tiles; tile += pairs) {
+            const bool arrived = wait_barrier(acc_full_bar(acc), acc_phase, abort_flag, p.status, kStatusEpilogueAccFull);
+            epilogue_barrier();
+            if (!arrived || *abort_flag != 0) break;
+            ptx::tc_fence_after_sync();
+            const unsigned m_pt = tile % m_pair_tiles, n_tile = tile / m_pair_tiles;
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + static_cast<uint32_t>(acc * kAccStride);
+            finish_tile(p, m_pt * 2 + rank, n_tile, row_in_tile, 1.0f, [&](unsigned c, float (&v)[32]) { load_acc_tmem(taddr, c, v); });
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    }
+
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();  // neither CTA leaves while the other may still signal its barriers or read its shared memory
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
+// ---- int8 weights on CTA pairs -------------------------------------------------------------------------------------------------
+//
+// Three rings in shared memory, each with its own barriers, because the three kinds of data have different lifetimes:
+//   X boxes    [128 rows x 64 k] binary16, 128-byte swizzle, counted on the FIRST CTA's barrier (the MMA needs both CTAs' boxes);
+//   raw boxes  this CTA's HALF of the W tile for one scale group: [bn / 2 rows x 128 k] int8, 128-byte swizzle, own barrier;
+//   converted  the same half as two [bn / 2 x 64] binary16 boxes in the layout the MMA reads.
+// The converter warps turn raw boxes into converted ones: the row's 128 bytes as 16-byte pieces, each byte widened exactly
+// (byte ^ 0x80 under the exponent of 1024, minus 1152) and multiplied by the row's prepared scale of this group, which was fetched a
+// group ahead. Splitting W over the pair halves the conversion work per SM; the tensor pipe reads both halves. The converted ring
+// is three deep so that the round trip converter -> (arrival at the first CTA) -> MMA -> (commit back to both CTAs) is covered.
+constexpr int kW8Group = 128;                       // values of k per raw / converted box (one scale group)
+constexpr int kW8XBoxes = kMaxStages;               // barrier slots; the ring itself holds p.stages boxes (as many as fit)
+constexpr int kW8RawBoxes = 3;
+constexpr int kW8ConvBoxes = kMaxStages;            // barrier slots; the ring holds p.stage_bytes boxes (as many as fit)
+constexpr int kW8ConvWarps = 8;
+constexpr int kW8Threads = 192 + 32 * kW8ConvWarps;
+constexpr int kW8Barriers = 2 * kW8XBoxes + 2 * kW8RawBoxes + 2 * kW8ConvBoxes + 4;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kW8Threads, 1)
+gemm_w8_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+    const unsigned bn = p.bn, half = p.bn / 2;
+    const unsigned raw_bytes = half * kW8Group;         // int8
+    const unsigned conv_box = half * 128;               // one converted [half x 64] binary16 box
+    const unsigned conv_bytes = 2 * conv_box;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_addr(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* const smem = smem_raw + (base - raw_addr);
+    const int x_boxes = static_cast<int>(p.stages);
+    const int conv_boxes = static_cast<int>(p.stage_bytes);  // (the field carries the depth of the converted ring in this kernel)
+    const uint32_t x_addr = base;
+    const unsigned raw_off = x_boxes * kXBytes;
+    const unsigned conv_off = raw_off + kW8RawBoxes * raw_bytes;
+    const uint32_t conv_addr = base + conv_off;
+    const unsigned scale_off = conv_off + conv_boxes * conv_bytes;  // the prepared scales of each raw box's rows, 256 bytes a box
+    uint8_t* const tail = smem + scale_off + kW8RawBoxes * 256;
+    const uint32_t bars = ptx::smem_addr(tail);
+    const auto x_full_bar = [&](int s) { return bars + 8u * s; };
+    const auto x_empty_bar = [&](int s) { return bars + 8u * (kW8XBoxes + s); };
+    const auto raw_full_bar = [&](int s) { return bars + 8u * (2 * kW8XBoxes + s); };
+    const auto raw_empty_bar = [&](int s) { return bars + 8u * (2 * kW8XBoxes + kW8RawBoxes + s); };
+    const auto conv_full_bar = [&](int s) { return bars + 8u * (2 * kW8XBoxes + 2 * kW8RawBoxes + s); };
+    const auto conv_empty_bar = [&](int s) { return bars + 8u * (2 * kW8XBoxes + 2 * kW8RawBoxes + kW8ConvBoxes + s); };
+    const auto acc_full_bar = [&](int a) { return bars + 8u * (kW8Barriers - 4 + a); };
+    const auto acc_empty_bar = [&](int a) { return bars + 8u * (kW8Barriers - 2 + a); };
+    unsigned* const words = reinterpret_cast<unsigned*>(tail + kW8Barriers * 8);
+    unsigned* const tmem_slot = words;
+    volatile unsigned* const abort_flag = words + 1;
+
+    const unsigned warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const unsigned rank = ptx::cluster_ctarank();
+    const unsigned pair = blockIdx.x / 2, pairs = gridDim.x / 2;
+    const unsigned m_pair_tiles = (p.m + 2 * kBM - 1) / (2 * kBM);
+    const unsigned pair_tiles = m_pair_tiles * p.n_tiles;
+    const unsigned groups = p.k / kW8Group;  // K is a multiple of 128
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < x_boxes; ++s) {
+            ptx::mbar_init(x_full_bar(s), 1);
+            ptx::mbar_init(x_empty_bar(s), 1);
+        }
+        for (int s = 0; s < kW8RawBoxes; ++s) {
+            ptx::mbar_init(raw_full_bar(s), 1);
+            ptx::mbar_init(raw_empty_bar(s), kW8ConvWarps);
+        }
+        for (int s = 0; s < conv_boxes; ++s) {
+            ptx::mbar_init(conv_full_bar(s), 2 * kW8ConvWarps);  // the converter warps of both CTAs (used in the first CTA only)
+            ptx::mbar_init(conv_empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(acc_full_bar(a), 1);
+            ptx::mbar_init(acc_empty_bar(a), 256);
+        }
+        words[1] = 0;
+        ptx::fence_barrier_init();
+        ptx::tma_prefetch_descriptor(&map_x);
+        ptx::tma_prefetch_descriptor(&map_w);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_addr(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int xs = 0, rs = 0;
+            unsigned x_phase = 0, r_phase = 0;
+            bool ok = true;
+            for (unsigned tile = pair; ok && tile < pair_tiles; tile += pairs) {
+                const unsigned m_pt = tile % m_pair_tiles, n_tile = tile / m_pair_tiles;
+                const int row_x = static_cast<int>(m_pt * 2 * kBM + rank * kBM);
+                const int row_w = static_cast<int>(n_tile * bn + rank * half);
+                for (unsigned g = 0; ok && g < groups; ++g) {
+                    if (!wait_barrier(raw_empty_bar(rs), r_phase ^ 1u, abort_flag, p.status, kStatusProducerEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::mbar_arrive_expect_tx(raw_full_bar(rs), raw_bytes + half * 2);
+                    ptx::tma_load_2d(base + raw_off + rs * raw_bytes, &map_w, raw_full_bar(rs), static_cast<int>(g * kW8Group), row_w);
+                    ptx::bulk_load(base + scale_off + rs * 256, p.scales_t + static_cast<size_t>(g) * p.ld_st + row_w, half * 2, raw_full_bar(rs));
+                    if (++rs == kW8RawBoxes) {
+                        rs = 0;
+                        r_phase ^= 1u;
+                    }
+                    for (int sub = 0; sub < 2; ++sub) {
+                        if (!wait_barrier(x_empty_bar(xs), x_phase ^ 1u, abort_flag, p.status, kStatusProducerEmpty)) {
+                            ok = false;
+                            break;
+                        }
+                        if (rank == 0) ptx::mbar_arrive_expect_tx(x_full_bar(xs), 2 * kXBytes);
+                        ptx::tma_load_2d_pair(x_addr + xs * kXBytes, &map_x, ptx::map_to_cta(x_full_bar(xs), 0),
+                                              static_cast<int>(g * kW8Group + sub * kBK), row_x);
+                        if (++xs == x_boxes) {
+                            xs = 0;
+                            x_phase ^= 1u;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = ptx::instr_desc_f16_f32acc(2 * kBM, bn);
+            int xs = 0, acc = 0, conv = 0;
+            unsigned x_phase = 0, acc_phase = 0, conv_phase = 0;
+            bool ok = true;
+            for (unsigned tile = pair; ok && tile < pair_tiles; tile += pairs) {
+                if (!wait_barrier(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kStatusMmaAccEmpty)) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t d = tmem_base + static_cast<uint32_t>(acc * kAccStride);
+                for (unsigned g = 0; ok && g < groups; ++g) {
+                    if (!wait_barrier(conv_full_bar(conv), conv_phase, abort_flag, p.status, kStatusMmaConvFull)) {
+                        ok = false;
+                        break;
+                    }
+                    for (int sub = 0; sub < 2; ++sub) {
+                        if (!wait_barrier(x_full_bar(xs), x_phase, abort_flag, p.status, kStatusMmaFull)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after_sync();
+                        const uint64_t desc_x = ptx::smem_desc_k_major_sw128(x_addr + xs * kXBytes);
+                        const uint64_t desc_w = ptx::smem_desc_k_major_sw128(conv_addr + conv * conv_bytes + sub * conv_box);
+#pragma unroll
+                        for (int j = 0; j < kBK / 16; ++j)
+                            ptx::mma_f16_ss_pair(d, desc_x + 2u * j, desc_w + 2u * j, idesc, (g > 0 || sub > 0 || j > 0) ? 1u : 0u);
+                        ptx::mma_commit_pair(x_empty_bar(xs), 3);
+                        if (++xs == x_boxes) {
+                            xs = 0;
+                            x_phase ^= 1u;
+                        }
+                    }
+                    if (!ok) break;
+                    ptx::mma_commit_pair(conv_empty_bar(conv), 3);
+                    if (++conv == conv_boxes) {
+                        conv = 0;
+                        conv_phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::mma_commit_pair(acc_full_bar(acc), 3);
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp < 6) {
+        const unsigned quarter = warp % 4;
+        const unsigned row_in_tile = quarter * 32 + lane;
+        const float descale = __ldg(p.descale);
+        int acc = 0;
+        unsigned acc_phase = 0;
+        for (unsigned tile = pair; tile < pair_tiles; tile += pairs) {
+            const bool arrived = wait_barrier(acc_full_bar(acc), acc_phase, abort_flag, p.status, kStatusEpilogueAccFull);
+            epilogue_barrier();
+            if (!arrived || *abort_flag != 0) break;
+            ptx::tc_fence_after_sync();
+            const unsigned m_pt = tile % m_pair_tiles, n_tile = tile / m_pair_tiles;
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + static_cast<uint32_t>(acc * kAccStride);
+            finish_tile(p, m_pt * 2 + rank, n_tile, row_in_tile, descale, [&](unsigned c, float (&v)[32]) { load_acc_tmem(taddr, c, v); });
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // converters: 256 threads share the 8 * half 16-byte pieces of a raw box; piece p is row p % half, 16-byte column p / half, and
+        // thread t takes pieces t, t + 256, ... (at most four). Eight consecutive threads take eight consecutive rows of one column,
+        // eight different swizzle phases, so a quarter warp's shared-memory accesses do not collide.
+        const unsigned ct = threadIdx.x - 192;
+        const unsigned total_pieces = 8u * half;
+        unsigned prow[4], pcol[4];
+        bool live[4];
+#pragma unroll
+        for (unsigned i = 0; i < 4; ++i) {
+            const unsigned piece = ct + 256u * i;
+            live[i] = piece < total_pieces;
+            prow[i] = live[i] ? piece % half : 0u;
+            pcol[i] = live[i] ? piece / half : 0u;
+        }
+        const __half2 offset = __half2half2(__ushort_as_half(0x6480));  // 1152
+        const __half zero = __ushort_as_half(0);
+        int rs = 0, conv = 0;
+        unsigned r_phase = 0, conv_phase = 0;
+        bool ok = true;
+        for (unsigned tile = pair; ok && tile < pair_tiles; tile += pairs) {
+            const unsigned n_tile = tile / m_pair_tiles;
+            const unsigned n0 = n_tile * bn + rank * half;
+            bool in_n[4];  // rows past N multiply by zero (their raw bytes are zero-filled, the scale slot may hold anything)
+#pragma unroll
+            for (unsigned i = 0; i < 4; ++i) in_n[i] = live[i] && n0 + prow[i] < p.n;
+            for (unsigned g = 0; g < groups; ++g) {
+                bool got = wait_barrier(raw_full_bar(rs), r_phase, abort_flag, p.status, kStatusConvFull);
+                got = got && wait_barrier(conv_empty_bar(conv), conv_phase ^ 1u, abort_flag, p.status, kStatusConvEmpty);
+                if (!__all_sync(0xFFFFFFFFu, got)) {
+                    ok = false;
+                    break;
+                }
+                const uint8_t* raw = smem + raw_off + rs * raw_bytes;
+                const __half* srow = reinterpret_cast<const __half*>(smem + scale_off + rs * 256);
+                uint8_t* out = smem + conv_off + conv * conv_bytes;
+#pragma unroll
+                for (unsigned i = 0; i < 4; ++i) {
+                    if (!live[i]) continue;
+                    const unsigned row = prow[i], c = pcol[i];  // k offsets 16 c .. 16 c + 15 of the row
+                    const unsigned sw = row & 7u;
+                    const __half2 sc = __half2half2(in_n[i] ? srow[row] : zero);
+                    const uint4 q = *reinterpret_cast<const uint4*>(raw + row * 128 + ((c ^ sw) * 16));
+                    const unsigned w[4] = {q.x ^ 0x80808080u, q.y ^ 0x80808080u, q.z ^ 0x80808080u, q.w ^ 0x80808080u};
+                    unsigned h[8];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        unsigned lo = __byte_perm(w[j], 0x64646464u, 0x5140);
+                        unsigned hi = __byte_perm(w[j], 0x64646464u, 0x5342);
+                        __half2 a = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&lo), offset), sc);
+                        __half2 b = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&hi), offset), sc);
+                        h[2 * j] = *reinterpret_cast<unsigned*>(&a);
+                        h[2 * j + 1] = *reinterpret_cast<unsigned*>(&b);
+                    }
+                    uint8_t* box = out + (c / 4) * conv_box + row * 128;  // k 0..63 -> first box, 64..127 -> second
+                    const unsigned j2 = (2 * c) % 8;
+                    *reinterpret_cast<uint4*>(box + ((j2 ^ sw) * 16)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(box + (((j2 + 1) ^ sw) * 16)) = make_uint4(h[4], h[5], h[6], h[7]);
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive_cluster(ptx::map_to_cta(conv_full_bar(conv), 0));
+                    ptx::mbar_arrive(raw_empty_bar(rs));
+                }
+                if (++conv == conv_boxes) {
+                    conv = 0;
+                    conv_phase ^= 1u;
+                }
+                if (++rs == kW8RawBoxes) {
+                    rs = 0;
+                    r_phase ^= 1u;
+                }
+            }
+        }
+    }
+
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
+int max_pairs_of(const Context& ctx, const void* kernel, unsigned threads, int (&cache)[64]) {
+    const int slot = ctx.device < 64 ? ctx.device : 63;
+    if (cache[slot] == 0) {
+        check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit), "cudaFuncSetAttribute");
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>(ctx.sm_count) & ~1u);
+        cfg.blockDim = dim3(threads);
+        cfg.dynamicSmemBytes = kSmemLimit;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters <= 0) {
+            (void)cudaGetLastError();
+            clusters = ctx.sm_count / 2;
+        }
+        cache[slot] = clusters < ctx.sm_count / 2 ? clusters : ctx.sm_count / 2;
+    }
+    return cache[slot];
+}
+
+void launch_w8_pair(const Context& ctx, const CUtensorMap& map_x, const CUtensorMap& map_w, GemmParams p, unsigned bn, cudaStream_t stream) {
+    const unsigned half = bn / 2;
+    p.bn = bn;
+    // Shared memory: three raw boxes, five X boxes, then as many converted boxes as fit (at least three), then more X boxes.
+    const unsigned conv_bytes = 2 * half * 128;
+    unsigned fixed = 1024 + kW8RawBoxes * half * kW8Group + kW8RawBoxes * 256 + kW8Barriers * 8 + 64;
+    unsigned conv_boxes = (kSmemLimit - fixed - 5 * kXBytes) / conv_bytes;
+    if (conv_boxes > static_cast<unsigned>(kW8ConvBoxes)) conv_boxes = kW8ConvBoxes;
+    if (conv_boxes < 3) conv_boxes = 3;
+    fixed += conv_boxes * conv_bytes;
+    const unsigned fit = (kSmemLimit - fixed) / kXBytes;
+    p.stages = fit > static_cast<unsigned>(kW8XBoxes) ? static_cast<unsigned>(kW8XBoxes) : fit;  // X boxes in the ring
+    p.stage_bytes = conv_boxes;
     p.m_tiles = (p.m + kBM - 1) / kBM;
-    p.n_tiles = (p.n + BN - 1) / BN;
+    p.n_tiles = (p.n + bn - 1) / bn;
+    p.k_iters = p.k / kW8Group;
+    p.tiles = p.m_tiles * p.n_tiles;
+    p.stream_k = 0;
+    const unsigned pair_tiles = ((p.m + 2 * kBM - 1) / (2 * kBM)) * p.n_tiles;
+    const unsigned smem = fixed + p.stages * kXBytes;
+    static int cache[64] = {};
+    unsigned pairs = static_cast<unsigned>(max_pairs_of(ctx, reinterpret_cast<const void*>(gemm_w8_pair_kernel), kW8Threads, cache));
+    if (pair_tiles < pairs) pairs = pair_tiles;
+    gemm_w8_pair_kernel<<<2 * pairs, kW8Threads, smem, stream>>>(map_x, map_w, p);
+    check(cudaGetLastError(), "gemm_w8_pair_kernel launch");
+    ++g_launches;
+}
+
+// Per-CTA stage of the pair kernel: 128 rows of X and bn / 2 rows of W.
+unsigned pair_stage_bytes(unsigned bn) { return kXBytes + (bn / 2) * kBK * 2; }
+unsigned pair_stages_for(unsigned bn) {
+    const unsigned s = (kSmemLimit - 1024 - kTailBytes) / pair_stage_bytes(bn);
+    return s > kMaxStages ? kMaxStages : s;
+}
+
+void launch_pair(const Context& ctx, const CUtensorMap& map_x, const CUtensorMap& map_w, GemmParams p, unsigned bn, cudaStream_t stream) {
+    p.bn = bn;
+    p.stages = pair_stages_for(bn);
+    p.stage_bytes = pair_stage_bytes(bn);
+    p.m_tiles = (p.m + kBM - 1) / kBM;
+    p.n_tiles = (p.n + bn - 1) / bn;
+    p.k_iters = (p.k + kBK - 1) / kBK;
+    p.tiles = p.m_tiles * p.n_tiles;
+    p.stream_k = 0;
+    const unsigned pair_tiles = ((p.m + 2 * kBM - 1) / (2 * kBM)) * p.n_tiles;
+    const unsigned smem = 1024 + p.stages * p.stage_bytes + kTailBytes;
+    static int max_pairs[64] = {};  // co-resident clusters of two on each device (0 = not asked yet)
+    const int slot = ctx.device < 64 ? ctx.device : 63;
+    if (max_pairs[slot] == 0) {
+        check(cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit), "cudaFuncSetAttribute");
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>(ctx.sm_count) & ~1u);
+        cfg.blockDim = dim3(192);
+        cfg.dynamicSmemBytes = kSmemLimit;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel, &cfg) != cudaSuccess || clusters <= 0) {
+            (void)cudaGetLastError();
+            clusters = ctx.sm_count / 2;
+        }
+        max_pairs[slot] = clusters < ctx.sm_count / 2 ? clusters : ctx.sm_count / 2;
+    }
+    unsigned pairs = static_cast<unsigned>(max_pairs[slot]);
+    if (pair_tiles < pairs) pairs = pair_tiles;
+    gemm_pair_kernel<<<2 * pairs, 192, smem, stream>>>(map_x, map_w, p);
+    check(cudaGetLastError(), "gemm_pair_kernel launch");
+    ++g_launches;
+}
+
+template <bool W8>
+void launch_config(const Context& ctx, const CUtensorMap& map_x, const CUtensorMap& map_w, GemmParams p, unsigned bn, bool stream_k, cudaStream_t stream) {
+    using S = Shape<W8>;
+    p.bn = bn;
+    p.stages = S::stages_for(bn);
+    p.stage_bytes = S::stage_bytes(bn);
+    p.m_tiles = (p.m + kBM - 1) / kBM;
+    p.n_tiles = (p.n + bn - 1) / bn;
     p.k_iters = (p.k + kBK - 1) / kBK;
     p.tiles = p.m_tiles * p.n_tiles;
     p.stream_k = stream_k ? 1u : 0u;
-    if (p.tiles > ctx.scratch.counter_count) throw std::invalid_argument("sepal_b200: more output tiles than the context has counters for");
     const unsigned long long total = static_cast<unsigned long long>(p.tiles) * p.k_iters;
     if (total > 0xFFFFFFFFull) throw std::invalid_argument("sepal_b200: the product is too large for one launch");
     unsigned grid = static_cast<unsigned>(ctx.sm_count);
     if (stream_k) {
+        if (p.tiles > ctx.scratch.counter_count) throw std::invalid_argument("sepal_b200: more output tiles than the context has counters for");
         // Not more CTAs than there are pieces of at least four k iterations (or whole tiles, when there are enough of them).
         const unsigned long long pieces = total / 4 > p.tiles ? total / 4 : p.tiles;
         if (pieces < grid) grid = static_cast<unsigned>(pieces);
-        const std::size_t need = static_cast<std::size_t>(grid) * 2u * kBM * BN * sizeof(float);
+        const std::size_t need = static_cast<std::size_t>(grid) * 2u * kSlotFloats * sizeof(float);
         if (need > ctx.scratch.partial_bytes) {
-            // Fall back to whole tiles rather than write past the scratch the context owns.
-            p.stream_k = 0;
+            // Fewer CTAs rather than writing past the scratch the context owns (whole tiles when not even two fit).
+            const std::size_t fit = ctx.scratch.partial_bytes / (2u * kSlotFloats * sizeof(float));
+            if (fit >= 2)
+                grid = static_cast<unsigned>(fit);
+            else
+                p.stream_k = 0;
         }
     }
     if (p.stream_k == 0 && p.tiles < grid) grid = p.tiles;
     static bool configured[64] = {};  // per device; a benign race: every writer sets the same attribute
     if (ctx.device >= 64 || !configured[ctx.device]) {
-        check(cudaFuncSetAttribute(gemm_tc_kernel<BN, W8>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes), "cudaFuncSetAttribute");
+        check(cudaFuncSetAttribute(gemm_tc_kernel<W8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit), "cudaFuncSetAttribute");
         if (ctx.device < 64) configured[ctx.device] = true;
     }
-    gemm_tc_kernel<BN, W8><<<grid, S::kThreads, S::kSmemBytes, stream>>>(map_x, map_w, p);
+    gemm_tc_kernel<W8><<<grid, S::kThreads, S::smem_bytes(bn, p.stages), stream>>>(map_x, map_w, p);
     check(cudaGetLastError(), "gemm_tc_kernel launch");
     ++g_launches;
+}
+
+// The tile width for a shape when the caller leaves it open. Measured on B200 over the trunk's shapes (M 900 and 4096, N 2048 .. 19456,
+// K 2048 .. 9728), the widest tile wins or ties almost everywhere: the time of a k step barely shrinks with the tile width (the
+// operand rings, not the tensor pipe, set the pace of a narrow tile), so narrower tiles only add k steps. Narrow outputs get one tile
+// of their own width.
+unsigned pick_bn(std::size_t n, bool coarse) {
+    if (n >= 256) return 256;
+    if (coarse) return n <= 128 ? 128u : 256u;
+    return static_cast<unsigned>((n + 15) / 16 * 16);
+}
+
+// CTA pairs pay a cluster launch and two cluster barriers; measured, they win from about 24 GFLOP per product up (fp16 weights).
+bool pick_pair(std::size_t t, std::size_t n, std::size_t k) {
+    return t > kBM && static_cast<double>(t) * static_cast<double>(n) * static_cast<double>(k) >= 1.2e10;
+}
+
+// config: -1 picks; 0..3 are the four fixed schedules of gemm.hpp; otherwise the tile width (a multiple of 16 in [16, 256]) plus 1
+// for the even split of k, or plus 2 for CTA pairs.
+void decode_config(int config, std::size_t n, bool coarse, bool auto_pair, const char* who, unsigned& bn, bool& stream_k, bool& pair) {
+    const bool pairs_allowed = true;
+    pair = false;
+    stream_k = false;
+    if (config == -1) {
+        pair = auto_pair;
+        bn = pick_bn(n, coarse);
+        return;
+    }
+    if (config >= 0 && config < kConfigs) {
+        bn = config >= 2 ? 128u : 256u;
+        stream_k = (config & 1) != 0;
+        return;
+    }
+    const int width = config & ~3;
+    const int flags = config & 3;
+    if (config < 0 || width < 16 || width > 256 || width % 16 != 0 || flags == 3 || (coarse && width != 128 && width != 256) ||
+        (flags == 2 && !pairs_allowed))
+        throw std::invalid_argument(std::string(who) + ": config must be -1, 0 .. 3, or a tile width (multiple of 16 up to 256" +
+                                    (coarse ? "; 128 or 256 here" : "") + ") plus 1 for the even split of k or 2 for CTA pairs" +
+                                    (pairs_allowed ? "" : " (no pairs here)"));
+    bn = static_cast<unsigned>(width);
+    stream_k = flags == 1;
+    pair = flags == 2;
 }
 
 void require_aligned(const void* ptr, const char* what) {
@@ -632,13 +1241,6 @@ GemmParams common_params(Context& ctx, void* y, std::size_t ld_y, bool y_half, s
     return p;
 }
 
-// -1: the even split unless the whole tiles already fill the CTAs evenly (or there are so many waves that the tail does not matter).
-bool pick_stream_k(const Context& ctx, unsigned tiles) {
-    const unsigned sms = static_cast<unsigned>(ctx.sm_count);
-    if (tiles % sms == 0) return false;
-    return true;
-}
-
 }  // namespace
 
 std::uint64_t take_launch_count() {
@@ -654,23 +1256,21 @@ void launch_gemm_f16(Context& ctx, const void* x, std::size_t ld_x, const void* 
         throw std::invalid_argument("launch_gemm_f16: unsupported shape [" + std::to_string(t) + " x " + std::to_string(k) + "] by [" + std::to_string(n) +
                                     " x " + std::to_string(k) + "] (K and the strides of X and W multiples of 8, N and the stride of Y even, "
                                     "SwiGLU needs N a multiple of 128)");
-    if (config < -1 || config >= kConfigs) throw std::invalid_argument("launch_gemm_f16: config must be -1 .. 3");
     if (t == 0) return;
     if (x == nullptr || w == nullptr) throw std::invalid_argument("launch_gemm_f16: null operand");
     require_aligned(x, "X");
     require_aligned(w, "W");
     check(cudaSetDevice(ctx.device), "cudaSetDevice");
+    unsigned bn = 256;
+    bool stream_k = false, pair = false;
+    decode_config(config, n, epilogue == Epilogue::SwiGLU, pick_pair(t, n, k), "launch_gemm_f16", bn, stream_k, pair);
     GemmParams p = common_params(ctx, y, ld_y, y_half, t, n, k, epilogue);
-    const bool narrow = config >= 0 ? config >= 2 : (n <= 128);
-    const unsigned bn = narrow ? 128 : 256;
     const CUtensorMap map_x = make_tensor_map_2d(ctx, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, t, k, ld_x, kBM, kBK, true);
-    const CUtensorMap map_w = make_tensor_map_2d(ctx, w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n, k, ld_w, bn, kBK, true);
-    const unsigned tiles = static_cast<unsigned>(((t + kBM - 1) / kBM) * ((n + bn - 1) / bn));
-    const bool stream_k = config >= 0 ? (config & 1) != 0 : pick_stream_k(ctx, tiles);
-    if (narrow)
-        launch_config<128, false>(ctx, map_x, map_w, p, stream_k, stream);
+    const CUtensorMap map_w = make_tensor_map_2d(ctx, w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n, k, ld_w, pair ? bn / 2 : bn, kBK, true);
+    if (pair)
+        launch_pair(ctx, map_x, map_w, p, bn, stream);
     else
-        launch_config<256, false>(ctx, map_x, map_w, p, stream_k, stream);
+        launch_config<false>(ctx, map_x, map_w, p, bn, stream_k, stream);
 }
 
 void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMatrix& wm, void* y, std::size_t ld_y, bool y_half, std::size_t t,
@@ -683,26 +1283,32 @@ void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMat
         throw std::invalid_argument("launch_gemm_w8g: unsupported shape [" + std::to_string(t) + " x " + std::to_string(k) + "] by [" + std::to_string(n) +
                                     " x " + std::to_string(k) + "] (K a multiple of 128, the stride of X a multiple of 8, of q a multiple of 16, "
                                     "N and the stride of Y even, SwiGLU needs N a multiple of 128)");
-    if (config < -1 || config >= kConfigs) throw std::invalid_argument("launch_gemm_w8g: config must be -1 .. 3");
     if (t == 0) return;
     if (x == nullptr || q == nullptr || scales_t == nullptr || descale == nullptr) throw std::invalid_argument("launch_gemm_w8g: null operand");
     require_aligned(x, "X");
     require_aligned(q, "q");
     check(cudaSetDevice(ctx.device), "cudaSetDevice");
+    unsigned bn = 256;
+    bool stream_k = false, pair = false;
+    // The pair kernel takes any tile width; the lone-CTA kernel (few rows, or the even split of k) takes 128 or 256.
+    const bool wants_pair = config == -1 ? t > kBM : (config >= kConfigs && (config & 3) == 2);
+    decode_config(config, n, epilogue == Epilogue::SwiGLU || !wants_pair, wants_pair, "launch_gemm_w8g", bn, stream_k, pair);
     GemmParams p = common_params(ctx, y, ld_y, y_half, t, n, k, epilogue);
     p.scales_t = static_cast<const __half*>(scales_t);
     p.ld_st = ld_st;
     p.descale = descale;
-    const bool narrow = config >= 0 ? config >= 2 : (n <= 128);
-    const unsigned bn = narrow ? 128 : 256;
     const CUtensorMap map_x = make_tensor_map_2d(ctx, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, t, k, ld_x, kBM, kBK, true);
-    const CUtensorMap map_w = make_tensor_map_2d(ctx, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k, ld_q, bn, kBK, false);
-    const unsigned tiles = static_cast<unsigned>(((t + kBM - 1) / kBM) * ((n + bn - 1) / bn));
-    const bool stream_k = config >= 0 ? (config & 1) != 0 : pick_stream_k(ctx, tiles);
-    if (narrow)
-        launch_config<128, true>(ctx, map_x, map_w, p, stream_k, stream);
-    else
-        launch_config<256, true>(ctx, map_x, map_w, p, stream_k, stream);
+    if (pair) {
+        // The pair kernel copies the scales of a tile's rows in 16-byte pieces: rows of scales_t must be padded to whole tiles.
+        if (ld_st % 8 != 0 || ld_st < (n + 255) / 256 * 256 || reinterpret_cast<std::uintptr_t>(scales_t) % 16 != 0)
+            throw std::invalid_argument("launch_gemm_w8g: scales_t must be 16-byte aligned with a row stride of at least N rounded up to 256 "
+                                        "(as sepal_b200_prepare_w8g_scales is documented to be given)");
+        const CUtensorMap map_w = make_tensor_map_2d(ctx, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k, ld_q, bn / 2, kW8Group, true);
+        launch_w8_pair(ctx, map_x, map_w, p, bn, stream);
+    } else {
+        const CUtensorMap map_w = make_tensor_map_2d(ctx, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k, ld_q, bn, kBK, false);
+        launch_config<true>(ctx, map_x, map_w, p, bn, stream_k, stream);
+    }
 }
 
 // ---- the product for callers that cannot allocate ---------------------------------------------------------------------------------
@@ -773,7 +1379,7 @@ void launch_gemm_f16_noalloc(const void* x, std::size_t ld_x, const void* w, std
     GemmParams p = common_params(ctx, y, ld_y, y_half, t, n, k, epilogue);
     const CUtensorMap map_x = make_tensor_map_2d(ctx, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, t, k, ld_x, kBM, kBK, true);
     const CUtensorMap map_w = make_tensor_map_2d(ctx, w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n, k, ld_w, 128, kBK, true);
-    launch_config<128, false>(ctx, map_x, map_w, p, /*stream_k=*/true, stream);
+    launch_config<false>(ctx, map_x, map_w, p, 128, /*stream_k=*/true, stream);
     if (status_out != nullptr) {
         int value = 0;
         check(cudaMemcpyAsync(&value, ctx.status, sizeof(int), cudaMemcpyDeviceToHost, stream), "cudaMemcpyAsync(status)");

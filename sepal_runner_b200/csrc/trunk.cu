@@ -1,0 +1,318 @@
+#include "trunk.hpp"
+
+#include <cstring>
+#include <stdexcept>
+#include <string>
+
+#include <cuda_fp16.h>
+
+namespace sepal::b200 {
+
+void count_launch();
+
+namespace {
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {  // splitmix64 finaliser
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__device__ __forceinline__ float normal_at(unsigned long long seed, unsigned long long i) {
+    const unsigned long long h = mix64(seed * 0xD1B54A32D192ED03ull + i);
+    const float u1 = (static_cast<float>(static_cast<unsigned>(h >> 40)) + 1.0f) * (1.0f / 16777217.0f);  // (0, 1)
+    const float u2 = static_cast<float>(static_cast<unsigned>(h & 0xFFFFFFu)) * (1.0f / 16777216.0f);
+    return sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+}
+__device__ __forceinline__ float to_bf16_grid(float v) {
+    const unsigned bits = __float_as_uint(v);
+    return __uint_as_float((bits + 0x7FFFu + ((bits >> 16) & 1u)) & 0xFFFF0000u);
+}
+__global__ void fill_normal_half_kernel(__half* dst, std::size_t count, unsigned long long seed, float stddev) {
+    const std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < count) dst[i] = __float2half_rn(to_bf16_grid(normal_at(seed, i) * stddev));
+}
+__global__ void fill_normal_float_kernel(float* dst, std::size_t count, unsigned long long seed, float stddev) {
+    const std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < count) dst[i] = to_bf16_grid(normal_at(seed, i) * stddev);
+}
+
+// One block per token: a row of the binary16 table widened to the float32 residual stream, 8 values per thread and step.
+__global__ void embed_kernel(const __half* table, const std::uint32_t* tokens, float* x, std::size_t hidden, std::size_t vocab) {
+    const std::size_t row = blockIdx.x;
+    std::size_t id = tokens[row];
+    if (id >= vocab) id = vocab - 1;  // the host checks the ids; never read outside the table
+    const uint4* src = reinterpret_cast<const uint4*>(table + id * hidden);
+    float4* dst = reinterpret_cast<float4*>(x + row * hidden);
+    for (std::size_t v = threadIdx.x; v < hidden / 8; v += blockDim.x) {
+        const uint4 raw = src[v];
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+        const float2 a = __half22float2(h[0]), b = __half22float2(h[1]), c = __half22float2(h[2]), d = __half22float2(h[3]);
+        dst[2 * v] = make_float4(a.x, a.y, b.x, b.y);
+        dst[2 * v + 1] = make_float4(c.x, c.y, d.x, d.y);
+    }
+}
+
+// One block per row. The sum of squares is taken in a fixed order (thread-strided partial sums, then a tree), so a row's result does
+// not depend on the other rows.
+__global__ void rms_norm_half_kernel(const float* x, std::size_t ld_x, const float* w, __half* y, std::size_t ld_y, std::size_t cols, float eps) {
+    __shared__ float partial[32];
+    const float* xr = x + static_cast<std::size_t>(blockIdx.x) * ld_x;
+    __half* yr = y + static_cast<std::size_t>(blockIdx.x) * ld_y;
+    float ss = 0.0f;
+    for (std::size_t c = threadIdx.x * 4; c < cols; c += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + c);
+        ss = fmaf(v.x, v.x, ss);
+        ss = fmaf(v.y, v.y, ss);
+        ss = fmaf(v.z, v.z, ss);
+        ss = fmaf(v.w, v.w, ss);
+    }
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+    if (threadIdx.x % 32 == 0) partial[threadIdx.x / 32] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < blockDim.x / 32 ? partial[threadIdx.x] : 0.0f;
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+        if (threadIdx.x == 0) partial[0] = t;
+    }
+    __syncthreads();
+    const float inv = rsqrtf(partial[0] / static_cast<float>(cols) + eps);
+    for (std::size_t c = threadIdx.x * 4; c < cols; c += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + c);
+        const float4 g = *reinterpret_cast<const float4*>(w + c);
+        const __half2 lo = __floats2half2_rn(__fmul_rn(__fmul_rn(v.x, inv), 1.0f + g.x), __fmul_rn(__fmul_rn(v.y, inv), 1.0f + g.y));
+        const __half2 hi = __floats2half2_rn(__fmul_rn(__fmul_rn(v.z, inv), 1.0f + g.z), __fmul_rn(__fmul_rn(v.w, inv), 1.0f + g.w));
+        uint2 packed;
+        packed.x = *reinterpret_cast<const unsigned*>(&lo);
+        packed.y = *reinterpret_cast<const unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(yr + c) = packed;
+    }
+}
+
+unsigned blocks_for(std::size_t n, unsigned per) { return static_cast<unsigned>((n + per - 1) / per); }
+
+}  // namespace
+
+void launch_embed(const void* table_half, const std::uint32_t* tokens, float* x, std::size_t rows, std::size_t hidden, std::size_t vocab, cudaStream_t stream) {
+    if (hidden % 8 != 0) throw std::invalid_argument("launch_embed: the hidden size must be a multiple of 8");
+    if (rows == 0) return;
+    embed_kernel<<<static_cast<unsigned>(rows), 128, 0, stream>>>(static_cast<const __half*>(table_half), tokens, x, hidden, vocab);
+    check(cudaGetLastError(), "embed_kernel launch");
+    count_launch();
+}
+
+void launch_rms_norm_half(const float* x, std::size_t ld_x, const float* w, void* y_half, std::size_t ld_y, std::size_t rows, std::size_t cols, float eps,
+                          cudaStream_t stream) {
+    if (cols % 4 != 0 || ld_x % 4 != 0 || ld_y % 4 != 0) throw std::invalid_argument("launch_rms_norm_half: columns and strides must be multiples of 4");
+    if (rows == 0) return;
+    rms_norm_half_kernel<<<static_cast<unsigned>(rows), 256, 0, stream>>>(x, ld_x, w, static_cast<__half*>(y_half), ld_y, cols, eps);
+    check(cudaGetLastError(), "rms_norm_half_kernel launch");
+    count_launch();
+}
+
+void launch_fill_normal_half(void* dst_half, std::size_t count, std::uint64_t seed, float stddev, cudaStream_t stream) {
+    if (count == 0) return;
+    fill_normal_half_kernel<<<blocks_for(count, 256), 256, 0, stream>>>(static_cast<__half*>(dst_half), count, seed, stddev);
+    check(cudaGetLastError(), "fill_normal_half_kernel launch");
+    count_launch();
+}
+void launch_fill_normal_float(float* dst, std::size_t count, std::uint64_t seed, float stddev, cudaStream_t stream) {
+    if (count == 0) return;
+    fill_normal_float_kernel<<<blocks_for(count, 256), 256, 0, stream>>>(dst, count, seed, stddev);
+    check(cudaGetLastError(), "fill_normal_float_kernel launch");
+    count_launch();
+}
+
+void* Trunk::alloc(std::size_t bytes) {
+    void* p = nullptr;
+    check(cudaMalloc(&p, bytes), "cudaMalloc(trunk)");
+    allocations_.push_back(p);
+    return p;
+}
+
+Trunk::Trunk(int device, const TrunkConfig& config) : cfg_(config), ctx_(device, 0) {
+    const TrunkConfig& c = cfg_;
+    if (c.layers == 0 || c.hidden % 128 != 0 || c.intermediate % 128 != 0 || c.attn_q % 128 != 0 || c.attn_kv % 8 != 0 || c.dn_in % 8 != 0 ||
+        c.dn_v % 128 != 0 || c.dn_v_offset % 8 != 0 || c.dn_v_offset + c.dn_v > c.dn_in || c.max_call_tokens == 0 || c.vocab == 0)
+        throw std::invalid_argument("sepal_b200 trunk: widths must be multiples of 128 (k and v, the fused in-projection: of 8), the v band inside "
+                                    "the in-projection, and layers, vocabulary and call size non-zero");
+    check(cudaSetDevice(device), "cudaSetDevice");
+    check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+    for (auto& e : ev_) check(cudaEventCreate(&e), "cudaEventCreate");
+    const std::size_t H = c.hidden, I = c.intermediate, T = c.max_call_tokens;
+    const std::size_t attn_in = c.attn_q + 2 * static_cast<std::size_t>(c.attn_kv);
+    p_width_ = static_cast<std::uint32_t>(attn_in > c.dn_in ? attn_in : c.dn_in);
+    std::uint64_t stream_seed = c.seed * 1000003ull;
+    const auto fill_half = [&](void* dst, std::size_t count) { launch_fill_normal_half(dst, count, ++stream_seed, 0.02f, stream_); };
+
+    embedding_ = alloc(static_cast<std::size_t>(c.vocab) * H * 2);
+    fill_half(embedding_, static_cast<std::size_t>(c.vocab) * H);
+    weight_bytes_ += static_cast<std::size_t>(c.vocab) * H * 2;
+
+    // scratch for building the MLP weights: the stacked [gate; up] before packing, and float32 copies for the quantiser
+    void* stacked = alloc(2 * I * H * 2);
+    float* wide = c.mlp_int8 ? static_cast<float*>(alloc(2 * I * H * 4)) : nullptr;
+    float* scales = c.mlp_int8 ? static_cast<float*>(alloc(2 * I * (H / kGroup + I / kGroup + 2) * 4)) : nullptr;
+    void* packed = c.mlp_int8 ? alloc(2 * I * H * 2) : nullptr;
+
+    layers_.resize(c.layers);
+    for (std::uint32_t l = 0; l < c.layers; ++l) {
+        Layer& L = layers_[l];
+        L.attention = l % 4 == 3;
+        L.mix_in_n = static_cast<std::uint32_t>(L.attention ? attn_in : c.dn_in);
+        L.mix_out_k = L.attention ? c.attn_q : c.dn_v;
+        L.band = L.attention ? 0u : c.dn_v_offset;
+        L.norm_in = static_cast<float*>(alloc(H * 4));
+        L.norm_post = static_cast<float*>(alloc(H * 4));
+        launch_fill_normal_float(L.norm_in, H, ++stream_seed, 0.02f, stream_);
+        launch_fill_normal_float(L.norm_post, H, ++stream_seed, 0.02f, stream_);
+        L.mix_in = alloc(static_cast<std::size_t>(L.mix_in_n) * H * 2);
+        fill_half(L.mix_in, static_cast<std::size_t>(L.mix_in_n) * H);
+        L.mix_out = alloc(H * static_cast<std::size_t>(L.mix_out_k) * 2);
+        fill_half(L.mix_out, H * static_cast<std::size_t>(L.mix_out_k));
+        weight_bytes_ += (static_cast<std::size_t>(L.mix_in_n) * H + H * static_cast<std::size_t>(L.mix_out_k)) * 2 + 2 * H * 4;
+        fill_half(stacked, 2 * I * H);  // rows 0 .. I-1 gate, I .. 2I-1 up
+        if (!c.mlp_int8) {
+            L.gate_up = alloc(2 * I * H * 2);
+            launch_pack_gate_up(stacked, H * 2, L.gate_up, H * 2, I, H * 2, stream_);
+            L.down = alloc(H * I * 2);
+            fill_half(L.down, H * I);
+            weight_bytes_ += (2 * I * H + H * I) * 2;
+        } else {
+            // pack in binary16, widen, quantise per group of 128, prepare the scales (the placement of runner/cuda/src/cuda_engine.cpp:580-627)
+            launch_pack_gate_up(stacked, H * 2, packed, H * 2, I, H * 2, stream_);
+            launch_half_to_float(packed, wide, 2 * I * H, stream_);
+            std::int8_t* q = static_cast<std::int8_t*>(alloc(2 * I * H));
+            launch_quantize_group_s8(wide, H, q, H, scales, H / kGroup, 2 * I, H, stream_);
+            const std::size_t ld_st = (2 * I + 255) / 256 * 256;
+            void* st = alloc((H / kGroup) * ld_st * 2);
+            check(cudaMemsetAsync(st, 0, (H / kGroup) * ld_st * 2, stream_), "cudaMemsetAsync");
+            float* ds = static_cast<float*>(alloc(8));
+            launch_prepare_w8g_scales(scales, H / kGroup, 2 * I, H / kGroup, st, ld_st, ds, reinterpret_cast<unsigned*>(ds + 1), stream_);
+            L.gate_up_q = W8gMatrix{q, H, st, ld_st, ds};
+            L.gate_up = q;
+            // down: [H, I]
+            fill_half(stacked, H * I);
+            launch_half_to_float(stacked, wide, H * I, stream_);
+            std::int8_t* qd = static_cast<std::int8_t*>(alloc(H * I));
+            launch_quantize_group_s8(wide, I, qd, I, scales, I / kGroup, H, I, stream_);
+            const std::size_t ld_sd = (H + 255) / 256 * 256;
+            void* sd = alloc((I / kGroup) * ld_sd * 2);
+            check(cudaMemsetAsync(sd, 0, (I / kGroup) * ld_sd * 2, stream_), "cudaMemsetAsync");
+            float* dd = static_cast<float*>(alloc(8));
+            launch_prepare_w8g_scales(scales, I / kGroup, H, I / kGroup, sd, ld_sd, dd, reinterpret_cast<unsigned*>(dd + 1), stream_);
+            L.down_q = W8gMatrix{qd, I, sd, ld_sd, dd};
+            L.down = qd;
+            weight_bytes_ += 2 * I * H + H * I + ((H / kGroup) * ld_st + (I / kGroup) * ld_sd) * 2;
+        }
+    }
+    x_ = static_cast<float*>(alloc(T * H * 4));
+    a1_ = alloc(T * H * 2);
+    p_ = alloc(T * static_cast<std::size_t>(p_width_) * 2);
+    a3_ = alloc(T * I * 2);
+    tokens_dev_ = static_cast<std::uint32_t*>(alloc(T * 4));
+    check(cudaMallocHost(reinterpret_cast<void**>(&tokens_pinned_), T * 4), "cudaMallocHost");
+    check(cudaMallocHost(reinterpret_cast<void**>(&out_pinned_), H * 4), "cudaMallocHost");
+    check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+}
+
+Trunk::~Trunk() {
+    (void)cudaSetDevice(ctx_.device);
+    if (stream_ != nullptr) (void)cudaStreamSynchronize(stream_);
+    for (void* p : allocations_) (void)cudaFree(p);
+    if (tokens_pinned_ != nullptr) (void)cudaFreeHost(tokens_pinned_);
+    if (out_pinned_ != nullptr) (void)cudaFreeHost(out_pinned_);
+    for (auto& e : ev_)
+        if (e != nullptr) (void)cudaEventDestroy(e);
+    if (stream_ != nullptr) (void)cudaStreamDestroy(stream_);
+}
+
+std::uint64_t Trunk::gemm_flops_per_token() const {
+    std::uint64_t params = 0;
+    for (const Layer& L : layers_)
+        params += static_cast<std::uint64_t>(L.mix_in_n) * cfg_.hidden + static_cast<std::uint64_t>(cfg_.hidden) * L.mix_out_k +
+                  3ull * cfg_.intermediate * cfg_.hidden;
+    return 2 * params;
+}
+
+void Trunk::forward_call(const std::uint32_t* tokens_dev, std::size_t rows) {
+    const TrunkConfig& c = cfg_;
+    const std::size_t H = c.hidden, I = c.intermediate;
+    launch_embed(embedding_, tokens_dev, x_, rows, H, c.vocab, stream_);
+    for (const Layer& L : layers_) {
+        launch_rms_norm_half(x_, H, L.norm_in, a1_, H, rows, H, c.eps, stream_);
+        launch_gemm_f16(ctx_, a1_, H, L.mix_in, H, p_, p_width_, true, rows, L.mix_in_n, H, Epilogue::Store, -1, stream_);
+        const __half* band = static_cast<const __half*>(p_) + L.band;
+        launch_gemm_f16(ctx_, band, p_width_, L.mix_out, L.mix_out_k, x_, H, false, rows, H, L.mix_out_k, Epilogue::Add, -1, stream_);
+        launch_rms_norm_half(x_, H, L.norm_post, a1_, H, rows, H, c.eps, stream_);
+        if (c.mlp_int8 == 0) {
+            launch_gemm_f16(ctx_, a1_, H, L.gate_up, H, a3_, I, true, rows, 2 * I, H, Epilogue::SwiGLU, -1, stream_);
+            launch_gemm_f16(ctx_, a3_, I, L.down, I, x_, H, false, rows, H, I, Epilogue::Add, -1, stream_);
+        } else {
+            launch_gemm_w8g(ctx_, a1_, H, L.gate_up_q, a3_, I, true, rows, 2 * I, H, Epilogue::SwiGLU, -1, stream_);
+            launch_gemm_w8g(ctx_, a3_, I, L.down_q, x_, H, false, rows, H, I, Epilogue::Add, -1, stream_);
+        }
+    }
+}
+
+void Trunk::run(const std::uint32_t* tokens, std::size_t n, float* last_hidden, float* all_hidden, double* times_ms) {
+    if (n == 0) throw std::invalid_argument("sepal_b200 trunk: a request needs at least one token");
+    if (tokens == nullptr || last_hidden == nullptr) throw std::invalid_argument("sepal_b200 trunk: null pointer");
+    for (std::size_t i = 0; i < n; ++i)
+        if (tokens[i] >= cfg_.vocab) throw std::invalid_argument("sepal_b200 trunk: token id " + std::to_string(tokens[i]) + " is outside the vocabulary");
+    check(cudaSetDevice(ctx_.device), "cudaSetDevice");
+    const std::size_t H = cfg_.hidden, T = cfg_.max_call_tokens;
+    check(cudaEventRecord(ev_[0], stream_), "cudaEventRecord");
+    for (std::size_t start = 0; start < n; start += T) {
+        const std::size_t rows = n - start < T ? n - start : T;
+        if (start != 0) check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");  // the pinned token buffer is reused
+        std::memcpy(tokens_pinned_, tokens + start, rows * 4);
+        check(cudaMemcpyAsync(tokens_dev_, tokens_pinned_, rows * 4, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(tokens)");
+        forward_call(tokens_dev_, rows);
+        if (all_hidden != nullptr)
+            check(cudaMemcpyAsync(all_hidden + start * H, x_, rows * H * 4, cudaMemcpyDeviceToHost, stream_), "cudaMemcpyAsync(hidden)");
+        if (start + rows == n)
+            check(cudaMemcpyAsync(out_pinned_, x_ + (rows - 1) * H, H * 4, cudaMemcpyDeviceToHost, stream_), "cudaMemcpyAsync(last hidden)");
+    }
+    check(cudaEventRecord(ev_[1], stream_), "cudaEventRecord");
+    const int status = ctx_.read_status(stream_);  // waits for the stream
+    if (status != 0) throw std::runtime_error("sepal_b200 trunk: a kernel gave up waiting (status " + std::to_string(status) + ")");
+    std::memcpy(last_hidden, out_pinned_, H * 4);
+    if (times_ms != nullptr) {
+        float ms = 0.0f;
+        check(cudaEventElapsedTime(&ms, ev_[0], ev_[1]), "cudaEventElapsedTime");
+        times_ms[0] = ms;
+        times_ms[1] = 0.0;
+    }
+}
+
+std::size_t Trunk::weight(std::uint32_t layer, TrunkWeight which, void* host_out, std::size_t capacity) {
+    const TrunkConfig& c = cfg_;
+    const std::size_t H = c.hidden, I = c.intermediate;
+    const void* src = nullptr;
+    std::size_t bytes = 0;
+    if (which == TrunkWeight::Embedding) {
+        src = embedding_;
+        bytes = static_cast<std::size_t>(c.vocab) * H * 2;
+    } else {
+        if (layer >= c.layers) throw std::invalid_argument("sepal_b200 trunk: no such layer");
+        const Layer& L = layers_[layer];
+        switch (which) {
+        case TrunkWeight::NormIn: src = L.norm_in; bytes = H * 4; break;
+        case TrunkWeight::NormPost: src = L.norm_post; bytes = H * 4; break;
+        case TrunkWeight::MixIn: src = L.mix_in; bytes = static_cast<std::size_t>(L.mix_in_n) * H * 2; break;
+        case TrunkWeight::MixOut: src = L.mix_out; bytes = H * static_cast<std::size_t>(L.mix_out_k) * 2; break;
+        case TrunkWeight::GateUp: src = L.gate_up; bytes = 2 * I * H * (c.mlp_int8 ? 1 : 2); break;
+        case TrunkWeight::Down: src = L.down; bytes = H * I * (c.mlp_int8 ? 1 : 2); break;
+        default: throw std::invalid_argument("sepal_b200 trunk: no such weight");
+        }
+    }
+    if (host_out != nullptr) {
+        if (capacity < bytes) throw std::length_error("sepal_b200 trunk: buffer too small: " + std::to_string(bytes) + " bytes needed");
+        check(cudaSetDevice(ctx_.device), "cudaSetDevice");
+        check(cudaMemcpy(host_out, src, bytes, cudaMemcpyDeviceToHost), "cudaMemcpy(weight)");
+    }
+    return bytes;
+}
+
+}  // namespace sepal::b200

@@ -47,6 +47,13 @@ SIGNATURES = {
     "sepal_b200_pack_gate_up": (_i32, [_vp, _u64, _vp, _u64, _u64, _u64, _vp]),
     "sepal_b200_float_to_half": (_i32, [_vp, _vp, _u64, _vp]),
     "sepal_b200_half_to_float": (_i32, [_vp, _vp, _u64, _vp]),
+    "sepal_b200_embed": (_i32, [_vp, _vp, _vp, _u64, _u64, _u64, _vp]),
+    "sepal_b200_rms_norm_half": (_i32, [_vp, _u64, _vp, _vp, _u64, _u64, _u64, C.c_float, _vp]),
+    "sepal_b200_trunk_open": (_i32, [_i32, _vp, C.POINTER(_vp)]),
+    "sepal_b200_trunk_close": (None, [_vp]),
+    "sepal_b200_trunk_run": (_i32, [_vp, _vp, _u64, _vp, _vp, _vp]),
+    "sepal_b200_trunk_weight": (_i32, [_vp, _u32, _i32, _vp, _u64, C.POINTER(_u64)]),
+    "sepal_b200_trunk_info": (_i32, [_vp, C.POINTER(_u64), C.POINTER(_u64)]),
     "sepal_b200_provider_open": (_i32, [_i32, _u64, C.POINTER(_vp)]),
     "sepal_b200_provider_close": (None, [_vp]),
     "sepal_b200_provider_upload_weights": (_i32, [_vp, _vp, _i32, _u64, _u64, C.POINTER(_u32)]),
@@ -97,7 +104,7 @@ class W8gWeight:
 
     q: "object"          # torch.int8 [N, K]
     scales: "object"     # torch.float32 [N, K / 128]: the quantiser's (and the reference's) layout, kept for checks
-    scales_t: "object"   # torch.float16 [K / 128, N]: prepared
+    scales_t: "object"   # torch.float16 [K / 128, N rounded up to 256]: prepared
     descale: "object"    # torch.float32 [1]
 
 
@@ -183,9 +190,10 @@ class Context:
         n, k = q.shape
         groups = k // GROUP
         assert s.shape == (n, groups)
-        st = torch.empty((groups, n), dtype=torch.float16, device=q.device)
+        ld_st = (n + 255) // 256 * 256  # rows padded to whole tiles (zeros): the kernels copy a tile's scales in 16-byte pieces
+        st = torch.zeros((groups, ld_st), dtype=torch.float16, device=q.device)
         descale = torch.empty((2,), dtype=torch.float32, device=q.device)  # [0] the factor, [1] scratch for the maximum
-        _check(self._lib.sepal_b200_prepare_w8g_scales(s.data_ptr(), groups, n, groups, st.data_ptr(), n, descale.data_ptr(),
+        _check(self._lib.sepal_b200_prepare_w8g_scales(s.data_ptr(), groups, n, groups, st.data_ptr(), ld_st, descale.data_ptr(),
                                                        descale.data_ptr() + 4, _stream_ptr(stream)))
         return W8gWeight(q=q, scales=s, scales_t=st, descale=descale)
 
@@ -225,6 +233,73 @@ class Context:
     @staticmethod
     def take_launch_count() -> int:
         return int(library().sepal_b200_take_launch_count())
+
+
+class TrunkConfig(C.Structure):
+    """sepal_b200_trunk_config. The defaults are BASELINE's long-log geometry: 36 layers, hidden 2560, MLP 9728, 3 DeltaNet : 1 attention."""
+
+    _fields_ = [("layers", _u32), ("hidden", _u32), ("intermediate", _u32), ("vocab", _u32), ("attn_q", _u32), ("attn_kv", _u32),
+                ("dn_in", _u32), ("dn_v_offset", _u32), ("dn_v", _u32), ("max_call_tokens", _u32), ("mlp_int8", _u32), ("eps", C.c_float),
+                ("seed", _u64)]
+
+    def __init__(self, **kw):
+        base = dict(layers=36, hidden=2560, intermediate=9728, vocab=151936, attn_q=4096, attn_kv=1024, dn_in=8192, dn_v_offset=4096, dn_v=2048,
+                    max_call_tokens=4096, mlp_int8=0, eps=1e-6, seed=1)
+        base.update(kw)
+        super().__init__(**base)
+
+
+class Trunk:
+    """The synthetic GEMM-chain trunk (sepal_b200_trunk_*): whole requests of host token ids in, final hidden states out."""
+
+    WEIGHTS = {"embedding": 0, "norm_in": 1, "mix_in": 2, "mix_out": 3, "norm_post": 4, "gate_up": 5, "down": 6}
+
+    def __init__(self, device: int = 0, config: Optional[TrunkConfig] = None) -> None:
+        self._lib = library()
+        self.config = config if config is not None else TrunkConfig()
+        handle = _vp()
+        _check(self._lib.sepal_b200_trunk_open(device, C.addressof(self.config), C.byref(handle)))
+        self._h = handle
+        flops, nbytes = _u64(), _u64()
+        _check(self._lib.sepal_b200_trunk_info(self._h, C.byref(flops), C.byref(nbytes)))
+        self.gemm_flops_per_token = flops.value
+        self.weight_bytes = nbytes.value
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.sepal_b200_trunk_close(self._h)
+            self._h = None
+
+    def __del__(self) -> None:  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def run(self, tokens, want_all: bool = False):
+        """tokens: uint32 numpy array. Returns (last hidden [hidden], all hidden [n, hidden] or None, device ms)."""
+        import numpy as np
+
+        tokens = np.ascontiguousarray(tokens, dtype=np.uint32)
+        n = tokens.shape[0]
+        last = np.empty(self.config.hidden, np.float32)
+        allh = np.empty((n, self.config.hidden), np.float32) if want_all else None
+        times = (C.c_double * 2)()
+        _check(self._lib.sepal_b200_trunk_run(self._h, tokens.ctypes.data, n, last.ctypes.data, allh.ctypes.data if want_all else None, times))
+        return last, allh, float(times[0])
+
+    def weight(self, which: str, layer: int = 0):
+        """A stored weight as a numpy array (float16 matrices as flat arrays: reshape with the known geometry)."""
+        import numpy as np
+
+        code = self.WEIGHTS[which]
+        needed = _u64()
+        _check(self._lib.sepal_b200_trunk_weight(self._h, layer, code, None, 0, C.byref(needed)))
+        is_norm = code in (1, 4)
+        int8 = self.config.mlp_int8 and code in (5, 6)
+        out = np.empty(needed.value // (4 if is_norm else 1 if int8 else 2), np.float32 if is_norm else np.int8 if int8 else np.float16)
+        _check(self._lib.sepal_b200_trunk_weight(self._h, layer, code, out.ctypes.data, needed.value, C.byref(needed)))
+        return out
 
 
 class Provider:

@@ -40,7 +40,7 @@ def make(oracle, seed, t, n, k, wscale=0.02):
 
 
 @pytest.mark.parametrize("name", ["g0", "g1", "g2", "g3"])
-@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3])
+@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3, 192, 145, 48, 17, 258, 130, 194, 34])
 def test_golden_vectors(ctx, golden, name, config):
     import torch
 
@@ -62,7 +62,7 @@ SHAPES = [(1, 8, 8), (1, 130, 72), (7, 2, 8), (37, 200, 256), (128, 256, 64), (1
 
 
 @pytest.mark.parametrize("t,n,k", SHAPES)
-@pytest.mark.parametrize("config", [0, 1, 2, 3])
+@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3, 240, 177, 96, 258, 226, 146])
 def test_ragged_shapes_every_schedule(ctx, oracle, t, n, k, config):
     x, w = make(oracle, 100 + t + n + k, t, n, k)
     want = oracle.gemm(x, w)
@@ -82,7 +82,7 @@ def test_every_row_count_up_to_a_few_tiles(ctx, oracle):
     for t in list(range(1, 300, 7)) + [127, 128, 129, 255, 256, 257, 300]:
         buf = torch.full((t + 2, n + 8), float("nan"), dtype=torch.float32, device="cuda")
         y = buf[1 : t + 1, :n]
-        ctx.gemm_f16(xd[:t], wd, y, config=1 if t % 2 else 0)
+        ctx.gemm_f16(xd[:t], wd, y, config=(1, 0, -1, 144, 209, 258, 178)[t % 7])
         ctx.check_status()
         assert rel_fro(y.cpu().numpy(), want[:t]) < 1e-5, t
         assert torch.isnan(buf[0]).all() and torch.isnan(buf[t + 1]).all() and torch.isnan(buf[1 : t + 1, n:]).all(), t
@@ -113,7 +113,7 @@ def test_rows_do_not_depend_on_their_batch_mates(ctx, oracle):
     t, n, k = 260, 512, 640
     x, w = make(oracle, 31, t, n, k)
     xd, wd = dev(x).half(), dev(w).half()
-    for config in (0, 1):
+    for config in (0, 1, 258, -1):
         base = ctx.gemm_f16(xd, wd, y_half=False, config=config)
         other = xd.clone()
         other[:100] = other[:100] * 3 + 1
@@ -133,7 +133,7 @@ def test_epilogue_add_is_one_float32_addition(ctx, oracle):
     x, w = make(oracle, 41, t, n, k)
     rng = np.random.default_rng(42)
     res = rng.standard_normal((t, n), dtype=np.float32)
-    for config in (0, 1, 2, 3):
+    for config in (0, 1, 2, 3, -1, 160, 225, 258, 210):
         y = dev(res)
         ctx.gemm_f16(dev(x).half(), dev(w).half(), y, epilogue=1, config=config)
         plain = ctx.gemm_f16(dev(x).half(), dev(w).half(), y_half=False, config=config)
@@ -154,7 +154,7 @@ def test_epilogue_swiglu_matches_the_unfused_form(ctx, oracle):
     packed = ctx.pack_gate_up(stacked)
     assert np.array_equal(packed.cpu().numpy().astype(np.float32), oracle.pack_gate_up(gate, up))
     want = oracle.swiglu_packed(oracle.gemm(x, oracle.pack_gate_up(gate, up)), inter)
-    for config in (0, 1, 2, 3):
+    for config in (0, 1, 2, 3, -1, 258, 130):
         y = ctx.gemm_f16(dev(x).half(), packed, epilogue=sb.SWIGLU, y_half=False, config=config)
         ctx.check_status()
         assert y.shape == (t, inter)
@@ -189,6 +189,11 @@ def test_refused_arguments(ctx):
         ctx.gemm_f16(x, w, epilogue=sb.SWIGLU)  # SwiGLU needs N a multiple of 128
     with pytest.raises(sb.SepalB200Error, match="config"):
         ctx.gemm_f16(x, w, config=9)
+    with pytest.raises(sb.SepalB200Error, match="config"):
+        ctx.gemm_f16(x, w, config=272)
+    with pytest.raises(sb.SepalB200Error, match="config"):
+        ctx.gemm_f16(torch.zeros((4, 64), dtype=torch.float16, device="cuda"), torch.zeros((128, 64), dtype=torch.float16, device="cuda"),
+                     epilogue=sb.SWIGLU, config=192)  # the fused SwiGLU takes tiles of 128 or 256 columns only
     with pytest.raises(sb.SepalB200Error, match="aligned"):
         ctx.gemm_f16(x.flatten()[4:4 + 3 * 64].view(3, 64)[:, :56], w[:, :56])
     y = ctx.gemm_f16(x[:0], w)  # no rows: a no-op
@@ -212,7 +217,7 @@ def test_group_quantiser_is_bit_exact(ctx, oracle):
 
 
 @pytest.mark.parametrize("t,n,k", [(37, 200, 256), (130, 128, 512), (300, 96, 384), (1, 260, 2560), (257, 514, 1152), (900, 640, 1280)])
-@pytest.mark.parametrize("config", [0, 1, 2, 3])
+@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3, 258, 130, 146, 210, 18])
 def test_w8g_against_the_dequantised_product(ctx, oracle, t, n, k, config):
     rng = np.random.default_rng(1000 + t)
     x = grid(oracle, rng.standard_normal((t, k), dtype=np.float32))
@@ -239,9 +244,13 @@ def test_w8g_baseline_distribution_and_tiny_scales(ctx, oracle):
     s[7] *= 2.0 ** -20
     s[9, 3] = 0.0
     wq = ctx.prepare_w8g(dev(q), dev(s))
+    want = oracle.gemm(x, oracle.dequant_group_s8(q, s))
+    for config in (0, 258, 194):
+        y = ctx.gemm_w8g(dev(x).half(), wq, y_half=False, config=config)
+        ctx.check_status()
+        assert rel_fro(y.cpu().numpy(), want) < 1e-3, config
     y = ctx.gemm_w8g(dev(x).half(), wq, y_half=False)
     ctx.check_status()
-    want = oracle.gemm(x, oracle.dequant_group_s8(q, s))
     assert rel_fro(y.cpu().numpy(), want) < 1e-3
     rows = [r for r in range(n) if r != 7]
     assert rel_fro(y.cpu().numpy()[:, rows], want[:, rows]) < 1e-3
@@ -263,15 +272,21 @@ def test_w8g_epilogues(ctx, oracle):
     q, s = ctx.quantize_group_s8(dev(packed))
     wq = ctx.prepare_w8g(q, s)
     wd = oracle.dequant_group_s8(*oracle.quantize_group_s8(packed))
-    y = ctx.gemm_w8g(dev(x).half(), wq, epilogue=sb.SWIGLU, y_half=True)
-    ctx.check_status()
-    assert rel_fro(y.float().cpu().numpy(), oracle.swiglu_packed(oracle.gemm(x, wd), inter)) < TOL_W8G
+    for config in (-1, 0, 3, 258, 130):
+        y = ctx.gemm_w8g(dev(x).half(), wq, epilogue=sb.SWIGLU, y_half=True, config=config)
+        ctx.check_status()
+        assert rel_fro(y.float().cpu().numpy(), oracle.swiglu_packed(oracle.gemm(x, wd), inter)) < TOL_W8G, config
     res = rng.standard_normal((t, 2 * inter), dtype=np.float32)
-    yd = dev(res)
-    ctx.gemm_w8g(dev(x).half(), wq, yd, epilogue=sb.ADD)
-    ctx.check_status()
-    assert rel_fro(yd.cpu().numpy(), oracle.add(res, oracle.gemm(x, wd))) < TOL_W8G
-    assert torch.isfinite(yd).all()
+    for config in (-1, 1, 258, 178):
+        yd = dev(res)
+        ctx.gemm_w8g(dev(x).half(), wq, yd, epilogue=sb.ADD, config=config)
+        ctx.check_status()
+        assert rel_fro(yd.cpu().numpy(), oracle.add(res, oracle.gemm(x, wd))) < TOL_W8G, config
+        assert torch.isfinite(yd).all()
+    with pytest.raises(sb.SepalB200Error, match="config"):
+        ctx.gemm_w8g(dev(x).half(), wq, epilogue=sb.SWIGLU, config=194)  # the fused SwiGLU takes tiles of 128 or 256 columns
+    with pytest.raises(sb.SepalB200Error, match="config"):
+        ctx.gemm_w8g(dev(x).half(), wq, config=193)  # the even split of k runs on lone CTAs with tiles of 128 or 256 columns
 
 
 # ---- BASELINE's full sizes ---------------------------------------------------------------------------------------------------------
@@ -326,9 +341,13 @@ def test_properties_at_4096_rows(ctx, oracle):
     y0 = ctx.gemm_f16(x1, w, y_half=False, config=0)
     y1 = ctx.gemm_f16(x1, w, y_half=False, config=1)
     y3 = ctx.gemm_f16(x1, w, y_half=False, config=3)
+    yp = ctx.gemm_f16(x1, w, y_half=False, config=258)
+    ya = ctx.gemm_f16(x1, w, y_half=False, config=-1)
     ctx.check_status()
     assert torch.equal(y0, ctx.gemm_f16(x1, w, y_half=False, config=0))
+    assert torch.equal(yp, ctx.gemm_f16(x1, w, y_half=False, config=258))
     assert (y0 - y1).norm() / y0.norm() < 1e-6 and (y0 - y3).norm() / y0.norm() < 1e-6
+    assert (y0 - yp).norm() / y0.norm() < 1e-6 and (y0 - ya).norm() / y0.norm() < 1e-6
     xs = (x1.float() * 0.5 + x2.float() * 0.25).half()  # exact in binary16 up to rounding of the sum
     ys = ctx.gemm_f16(xs, w, y_half=False, config=1)
     y2 = ctx.gemm_f16(x2, w, y_half=False, config=1)

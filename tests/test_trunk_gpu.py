@@ -1,0 +1,118 @@
+"""The GEMM-chain trunk (embedding, RMSNorm, the projection GEMMs with fused SwiGLU and residual epilogues) against a CPU composition of
+the oracle's functions, with the weights the trunk generated on the device copied back. Tolerance: relative Frobenius error 2e-3 of the
+final hidden state (BASELINE's fp16 bound); the operands of every GEMM are rounded to binary16 on both sides."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_fro(a, b):
+    a = np.asarray(a, np.float64)
+    b = np.asarray(b, np.float64)
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-300))
+
+
+def small_config(sb, **kw):
+    base = dict(layers=8, hidden=256, intermediate=512, vocab=1000, attn_q=256, attn_kv=128, dn_in=1024, dn_v_offset=512, dn_v=256,
+                max_call_tokens=300, mlp_int8=0, eps=1e-6, seed=7)
+    base.update(kw)
+    return sb.TrunkConfig(**base)
+
+
+def oracle_forward(oracle, trunk, cfg, tokens):
+    """The trunk's arithmetic on the CPU: float64-accumulated products, binary16 rounding wherever the device stores binary16."""
+    H, I = cfg.hidden, cfg.intermediate
+    f16 = oracle.to_f16_grid
+    emb = trunk.weight("embedding").reshape(cfg.vocab, H).astype(np.float32)
+    x = emb[tokens].copy()
+    for l in range(cfg.layers):
+        attention = l % 4 == 3
+        n_in = cfg.attn_q + 2 * cfg.attn_kv if attention else cfg.dn_in
+        k_out = cfg.attn_q if attention else cfg.dn_v
+        off = 0 if attention else cfg.dn_v_offset
+        w_in = trunk.weight("mix_in", l).reshape(n_in, H).astype(np.float32)
+        w_out = trunk.weight("mix_out", l).reshape(H, k_out).astype(np.float32)
+        gate_up = trunk.weight("gate_up", l).reshape(2 * I, H).astype(np.float32)
+        down = trunk.weight("down", l).reshape(H, I).astype(np.float32)
+        a1 = f16(oracle.rmsnorm(x, trunk.weight("norm_in", l), cfg.eps))
+        p = f16(oracle.gemm(a1, w_in))
+        x = oracle.add(x, oracle.gemm(np.ascontiguousarray(p[:, off:off + k_out]), w_out))
+        a1 = f16(oracle.rmsnorm(x, trunk.weight("norm_post", l), cfg.eps))
+        a3 = f16(oracle.swiglu_packed(oracle.gemm(a1, gate_up), I))
+        x = oracle.add(x, oracle.gemm(a3, down))
+    return x
+
+
+def test_embed_and_rms_norm_kernels(oracle):
+    import ctypes as C
+
+    import torch
+
+    import sepal_runner_b200 as sb
+
+    lib = sb.library()
+    rng = np.random.default_rng(17)
+    vocab, hidden, rows = 500, 384, 77
+    table = (rng.standard_normal((vocab, hidden)) * 0.02).astype(np.float16)
+    tokens = rng.integers(0, vocab, rows).astype(np.uint32)
+    td, kd = torch.from_numpy(table).cuda(), torch.from_numpy(tokens.view(np.int32)).cuda()
+    x = torch.empty((rows, hidden), dtype=torch.float32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.sepal_b200_embed(td.data_ptr(), kd.data_ptr(), x.data_ptr(), rows, hidden, vocab, stream) == 0
+    assert np.array_equal(x.cpu().numpy(), table[tokens].astype(np.float32))
+    xs = (rng.standard_normal((rows, hidden)) * 3).astype(np.float32)
+    w = (rng.standard_normal(hidden) * 0.1).astype(np.float32)
+    y = torch.empty((rows, hidden), dtype=torch.float16, device="cuda")
+    assert lib.sepal_b200_rms_norm_half(torch.from_numpy(xs).cuda().data_ptr(), hidden, torch.from_numpy(w).cuda().data_ptr(), y.data_ptr(), hidden,
+                                        rows, hidden, C.c_float(1e-6), stream) == 0
+    torch.cuda.synchronize()
+    want = oracle.rmsnorm(xs, w, 1e-6)
+    assert np.abs(y.float().cpu().numpy() - want).max() <= np.abs(want).max() * 2.0 ** -10  # one binary16 rounding
+    assert rel_fro(y.float().cpu().numpy(), want) < 5e-4
+
+
+def test_trunk_matches_the_cpu_composition(oracle):
+    import sepal_runner_b200 as sb
+
+    cfg = small_config(sb)
+    trunk = sb.Trunk(0, cfg)
+    try:
+        assert trunk.gemm_flops_per_token == 2 * sum(
+            ((cfg.attn_q + 2 * cfg.attn_kv) * cfg.hidden + cfg.hidden * cfg.attn_q if l % 4 == 3 else cfg.dn_in * cfg.hidden + cfg.hidden * cfg.dn_v)
+            + 3 * cfg.intermediate * cfg.hidden for l in range(cfg.layers))
+        rng = np.random.default_rng(4004)
+        tokens = rng.integers(0, cfg.vocab, 700).astype(np.uint32)  # three calls: 300 + 300 + 100 rows
+        last, allh, ms = trunk.run(tokens, want_all=True)
+        assert ms > 0 and np.isfinite(allh).all()
+        assert np.array_equal(last, allh[-1])
+        want = oracle_forward(oracle, trunk, cfg, tokens)
+        assert rel_fro(allh, want) < 2e-3
+        # weights are N(0, 0.02) on the bfloat16 grid
+        w = trunk.weight("down", 3).astype(np.float32)
+        assert abs(w.std() - 0.02) < 0.002 and np.array_equal(oracle.to_bf16_grid(w).astype(np.float16).astype(np.float32), w)
+        # a token's result does not depend on the other tokens of its call or on how the request is cut into calls
+        last2, all2, _ = trunk.run(tokens[250:420], want_all=True)
+        assert np.array_equal(all2, allh[250:420]) or rel_fro(all2, allh[250:420]) < 1e-5
+        with pytest.raises(sb.SepalB200Error, match="outside the vocabulary"):
+            trunk.run(np.array([cfg.vocab], np.uint32))
+    finally:
+        trunk.close()
+
+
+def test_trunk_with_int8_mlp_stays_close_to_the_fp16_trunk(oracle):
+    """The same seed gives the same fp16 weights; storing the MLP as int8 groups perturbs each MLP product by about 1 % (the bound the
+    reference gives its int8 weights against the unquantised product, test_gemm_s8_kernels.cpp:246-250), the residual stream far less."""
+    import sepal_runner_b200 as sb
+
+    tokens = np.random.default_rng(5).integers(0, 1000, 333).astype(np.uint32)
+    a = sb.Trunk(0, small_config(sb))
+    b = sb.Trunk(0, small_config(sb, mlp_int8=1))
+    try:
+        _, ha, _ = a.run(tokens, want_all=True)
+        _, hb, _ = b.run(tokens, want_all=True)
+        assert np.isfinite(hb).all()
+        assert rel_fro(hb, ha) < 2e-2
+    finally:
+        a.close()
+        b.close()

@@ -376,14 +376,9 @@ def run_serve(args):
     torch.cuda.set_device(local)
     rng = np.random.default_rng(5005)
     lengths = [int(v) for v in rng.integers(600, 1201, 64)] + [15900] * 4
-    order = sorted(range(len(lengths)), key=lambda i: -lengths[i])
-    load = [0] * world
-    mine = []
-    for i in order:
-        g = min(range(world), key=lambda r: load[r])
-        load[g] += lengths[i]
-        if g == rank:
-            mine.append(i)
+    from sepal_runner_b200.sharding import deal_requests, ideal_speedup
+
+    mine = deal_requests(lengths, world)[rank]
     trunk = sb.Trunk(local, sb.TrunkConfig(mlp_int8=1 if args.int8 else 0))
     tok_rng = np.random.default_rng(4004 + rank)
     requests = {i: tok_rng.integers(0, 151936, lengths[i]).astype(np.uint32) for i in mine}
@@ -443,7 +438,7 @@ def run_serve(args):
             "dtype": "f16 x int8-group MLP" if args.int8 else "f16 x f16 -> f32 accumulate",
             "data": "synthetic",
             "config": {"workload": "serve (BASELINE configs[4]): 64 requests of 600-1200 tokens + 4 of 15900, whole requests per GPU, longest first",
-                       "total_tokens": total, "p50_latency_s": round(all_lat[len(all_lat) // 2], 4),
+                       "total_tokens": total, "ideal_speedup_over_1_gpu": round(ideal_speedup(lengths, world), 3), "p50_latency_s": round(all_lat[len(all_lat) // 2], 4),
                        "p95_latency_s": round(all_lat[min(len(all_lat) - 1, int(0.95 * len(all_lat)))], 4),
                        "per_gpu": [{"requests": g[3], "tokens": g[4], "span_s": round(g[0], 4), "device_s": round(g[2] / 1e3, 4)} for g in gathered],
                        "l2": "weights 7.3 GB per replica: far larger than the L2", "parallelism": f"request-sharded x{world}, full replica per GPU, no collective"},

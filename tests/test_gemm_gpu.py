@@ -40,7 +40,7 @@ def make(oracle, seed, t, n, k, wscale=0.02):
 
 
 @pytest.mark.parametrize("name", ["g0", "g1", "g2", "g3"])
-@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3, 192, 145, 48, 17, 258, 130, 194, 34])
+@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3, 192, 145, 48, 17, 258, 130, 194, 34, 259, 131])
 def test_golden_vectors(ctx, golden, name, config):
     import torch
 
@@ -62,7 +62,7 @@ SHAPES = [(1, 8, 8), (1, 130, 72), (7, 2, 8), (37, 200, 256), (128, 256, 64), (1
 
 
 @pytest.mark.parametrize("t,n,k", SHAPES)
-@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3, 240, 177, 96, 258, 226, 146])
+@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3, 240, 177, 96, 258, 226, 146, 259, 131])
 def test_ragged_shapes_every_schedule(ctx, oracle, t, n, k, config):
     x, w = make(oracle, 100 + t + n + k, t, n, k)
     want = oracle.gemm(x, w)
@@ -82,7 +82,7 @@ def test_every_row_count_up_to_a_few_tiles(ctx, oracle):
     for t in list(range(1, 300, 7)) + [127, 128, 129, 255, 256, 257, 300]:
         buf = torch.full((t + 2, n + 8), float("nan"), dtype=torch.float32, device="cuda")
         y = buf[1 : t + 1, :n]
-        ctx.gemm_f16(xd[:t], wd, y, config=(1, 0, -1, 144, 209, 258, 178)[t % 7])
+        ctx.gemm_f16(xd[:t], wd, y, config=(1, 0, -1, 144, 209, 258, 178, 259)[t % 8])
         ctx.check_status()
         assert rel_fro(y.cpu().numpy(), want[:t]) < 1e-5, t
         assert torch.isnan(buf[0]).all() and torch.isnan(buf[t + 1]).all() and torch.isnan(buf[1 : t + 1, n:]).all(), t
@@ -113,7 +113,7 @@ def test_rows_do_not_depend_on_their_batch_mates(ctx, oracle):
     t, n, k = 260, 512, 640
     x, w = make(oracle, 31, t, n, k)
     xd, wd = dev(x).half(), dev(w).half()
-    for config in (0, 1, 258, -1):
+    for config in (0, 1, 258, 259, -1):
         base = ctx.gemm_f16(xd, wd, y_half=False, config=config)
         other = xd.clone()
         other[:100] = other[:100] * 3 + 1
@@ -133,7 +133,7 @@ def test_epilogue_add_is_one_float32_addition(ctx, oracle):
     x, w = make(oracle, 41, t, n, k)
     rng = np.random.default_rng(42)
     res = rng.standard_normal((t, n), dtype=np.float32)
-    for config in (0, 1, 2, 3, -1, 160, 225, 258, 210):
+    for config in (0, 1, 2, 3, -1, 160, 225, 258, 210, 259, 131):
         y = dev(res)
         ctx.gemm_f16(dev(x).half(), dev(w).half(), y, epilogue=1, config=config)
         plain = ctx.gemm_f16(dev(x).half(), dev(w).half(), y_half=False, config=config)
@@ -154,7 +154,7 @@ def test_epilogue_swiglu_matches_the_unfused_form(ctx, oracle):
     packed = ctx.pack_gate_up(stacked)
     assert np.array_equal(packed.cpu().numpy().astype(np.float32), oracle.pack_gate_up(gate, up))
     want = oracle.swiglu_packed(oracle.gemm(x, oracle.pack_gate_up(gate, up)), inter)
-    for config in (0, 1, 2, 3, -1, 258, 130):
+    for config in (0, 1, 2, 3, -1, 258, 130, 259, 131):
         y = ctx.gemm_f16(dev(x).half(), packed, epilogue=sb.SWIGLU, y_half=False, config=config)
         ctx.check_status()
         assert y.shape == (t, inter)
@@ -342,12 +342,15 @@ def test_properties_at_4096_rows(ctx, oracle):
     y1 = ctx.gemm_f16(x1, w, y_half=False, config=1)
     y3 = ctx.gemm_f16(x1, w, y_half=False, config=3)
     yp = ctx.gemm_f16(x1, w, y_half=False, config=258)
+    yq = ctx.gemm_f16(x1, w, y_half=False, config=259)
+    assert torch.equal(yq, ctx.gemm_f16(x1, w, y_half=False, config=259))
     ya = ctx.gemm_f16(x1, w, y_half=False, config=-1)
     ctx.check_status()
     assert torch.equal(y0, ctx.gemm_f16(x1, w, y_half=False, config=0))
     assert torch.equal(yp, ctx.gemm_f16(x1, w, y_half=False, config=258))
     assert (y0 - y1).norm() / y0.norm() < 1e-6 and (y0 - y3).norm() / y0.norm() < 1e-6
     assert (y0 - yp).norm() / y0.norm() < 1e-6 and (y0 - ya).norm() / y0.norm() < 1e-6
+    assert (y0 - yq).norm() / y0.norm() < 1e-6
     xs = (x1.float() * 0.5 + x2.float() * 0.25).half()  # exact in binary16 up to rounding of the sum
     ys = ctx.gemm_f16(xs, w, y_half=False, config=1)
     y2 = ctx.gemm_f16(x2, w, y_half=False, config=1)

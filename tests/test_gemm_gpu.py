@@ -217,7 +217,7 @@ def test_group_quantiser_is_bit_exact(ctx, oracle):
 
 
 @pytest.mark.parametrize("t,n,k", [(37, 200, 256), (130, 128, 512), (300, 96, 384), (1, 260, 2560), (257, 514, 1152), (900, 640, 1280)])
-@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3, 258, 130, 146, 210, 18])
+@pytest.mark.parametrize("config", [-1, 0, 1, 2, 3, 258, 130, 146, 210, 18, 259, 131, 147, 211])
 def test_w8g_against_the_dequantised_product(ctx, oracle, t, n, k, config):
     rng = np.random.default_rng(1000 + t)
     x = grid(oracle, rng.standard_normal((t, k), dtype=np.float32))
@@ -245,7 +245,7 @@ def test_w8g_baseline_distribution_and_tiny_scales(ctx, oracle):
     s[9, 3] = 0.0
     wq = ctx.prepare_w8g(dev(q), dev(s))
     want = oracle.gemm(x, oracle.dequant_group_s8(q, s))
-    for config in (0, 258, 194):
+    for config in (0, 258, 194, 259):
         y = ctx.gemm_w8g(dev(x).half(), wq, y_half=False, config=config)
         ctx.check_status()
         assert rel_fro(y.cpu().numpy(), want) < 1e-3, config
@@ -272,12 +272,12 @@ def test_w8g_epilogues(ctx, oracle):
     q, s = ctx.quantize_group_s8(dev(packed))
     wq = ctx.prepare_w8g(q, s)
     wd = oracle.dequant_group_s8(*oracle.quantize_group_s8(packed))
-    for config in (-1, 0, 3, 258, 130):
+    for config in (-1, 0, 3, 258, 130, 259, 131):
         y = ctx.gemm_w8g(dev(x).half(), wq, epilogue=sb.SWIGLU, y_half=True, config=config)
         ctx.check_status()
         assert rel_fro(y.float().cpu().numpy(), oracle.swiglu_packed(oracle.gemm(x, wd), inter)) < TOL_W8G, config
     res = rng.standard_normal((t, 2 * inter), dtype=np.float32)
-    for config in (-1, 1, 258, 178):
+    for config in (-1, 1, 258, 178, 259, 179):
         yd = dev(res)
         ctx.gemm_w8g(dev(x).half(), wq, yd, epilogue=sb.ADD, config=config)
         ctx.check_status()
@@ -327,6 +327,20 @@ def test_config2_full_size(ctx, oracle):
     rows = rng.integers(0, t, 5000).astype(np.uint32)
     cols = rng.integers(0, n, 5000).astype(np.uint32)
     assert rel_fro(got[rows, cols], oracle.gemm_sample(x, wd, rows, cols)) < TOL_W8G
+    # whole tiles and the even split of k over the pairs: the same sums up to float32 rounding, and each the same on every run
+    whole = ctx.gemm_w8g(dev(x).half(), wq, y_half=False, config=258)
+    split = ctx.gemm_w8g(dev(x).half(), wq, y_half=False, config=259)
+    ctx.check_status()
+    assert rel_fro(split.cpu().numpy(), whole.cpu().numpy()) < 1e-5
+    for _ in range(3):
+        assert torch_equal(split, ctx.gemm_w8g(dev(x).half(), wq, y_half=False, config=259))
+    ctx.check_status()
+
+
+def torch_equal(a, b):
+    import torch
+
+    return bool(torch.equal(a, b))
 
 
 def test_properties_at_4096_rows(ctx, oracle):

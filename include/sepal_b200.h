@@ -107,13 +107,29 @@ SEPAL_B200_API int32_t sepal_b200_gemm_f16_noalloc(const void* x, uint64_t ld_x,
                                                    int32_t* status_out);
 
 /* binary16 activations x int8 weights with one scale per output row and group of 128 values of k (the gpu-w8g layout). Replaces
- * launch_gemm_simt with SimtWeight::Int8Group (runner/cuda/src/gemm_simt_kernels.hpp:42-56) and launch_gemm_w8a16
- * (runner/cuda/src/gemm_s8_kernels.hpp:51-57). q is int8 [N, ld_q]; scales_t / descale come from sepal_b200_prepare_w8g_scales.
+ * launch_gemm_simt with SimtWeight::Int8Group (runner/cuda/src/gemm_simt_kernels.hpp:42-56). q is int8 [N, ld_q]; scales_t / descale come from sepal_b200_prepare_w8g_scales.
  * Requires K a multiple of 128, ld_x a multiple of 8, ld_q a multiple of 16, scales_t 16-byte aligned with ld_st >= N rounded up to
  * 256 (the padding zero). */
 SEPAL_B200_API int32_t sepal_b200_gemm_w8g(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const int8_t* q, uint64_t ld_q, const void* scales_t,
                                            uint64_t ld_st, const float* descale, void* y, uint64_t ld_y, int32_t y_half, uint64_t t, uint64_t n,
                                            uint64_t k, int32_t epilogue, int32_t config, void* stream);
+
+/* binary16 activations x int8 weights with ONE float32 scale per output row (the gpu-q8w layout): Y[t, n] = sw[n] * sum_k x[t, k] q[n, k].
+ * Replaces launch_gemm_w8a16 (runner/cuda/src/gemm_s8_kernels.hpp:51-57; its engine use cuda_engine.cpp:1118-1129). The bytes are
+ * widened exactly to binary16 on their way to the tensor cores, summed in float32, and the finished sum is multiplied by sw[n] in
+ * float32, as the reference does. q is int8 [N, ld_q] in plain row-major order (the reference's S8WeightLayout::Plain; its Fp16Pairs
+ * byte permutation serves its own mma.sync fragments and has no use here). Requires K a multiple of 128, ld_x a multiple of 8, ld_q a
+ * multiple of 16, N at most 65536. Epilogues and `config` as sepal_b200_gemm_w8g. */
+SEPAL_B200_API int32_t sepal_b200_gemm_w8r(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const int8_t* q, uint64_t ld_q, const float* sw, void* y,
+                                           uint64_t ld_y, int32_t y_half, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t config,
+                                           void* stream);
+
+/* Per-output-row int8 quantisation of a binary16 weight matrix w [N, ld_w], bit for bit launch_quantize_weights_s8 with the Plain layout
+ * (runner/cuda/src/gemm_s8_kernels.hpp:36-41, gemm_s8_kernels.cu:28-31,83-118): scales[r] = max|w[r, :]| / 127, q[r, c] = round to
+ * nearest even of w[r, c] * (127 / max), clamped to [-127, 127]; a zero row gets scale 0 and zeros. col_scale: NULL, or K floats by
+ * which the columns are multiplied in float32 first (the smoothing factors). K, ld_w and ld_q multiples of 16. */
+SEPAL_B200_API int32_t sepal_b200_quantize_rows_s8(const void* w, uint64_t ld_w, int8_t* q, uint64_t ld_q, float* scales, uint64_t n, uint64_t k,
+                                                   const float* col_scale, void* stream);
 
 /* The group quantiser, bit for bit launch_quantize_group_s8 (runner/cuda/src/gemm_simt_kernels.hpp:64-65): src float32 [rows, K],
  * q int8 [rows, ld_q], s float32 [rows, ld_s] with one scale per group of 128. */

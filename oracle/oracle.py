@@ -55,6 +55,8 @@ class Oracle:
         L.oracle_gemm_f64acc.argtypes = [_f32p, _sz, _f32p, _sz, _f32p, _sz, _sz, _sz, _sz, C.c_float]
         L.oracle_gemm_fma_chain.argtypes = [_f32p, _sz, _f32p, _sz, _f32p, _sz, _sz, _sz, _sz]
         L.oracle_gemm_f64acc_sample.argtypes = [_f32p, _sz, _f32p, _sz, _sz, _u32p, _u32p, _sz, _f64p]
+        L.oracle_quantize_rows_s8.restype = C.c_int
+        L.oracle_quantize_rows_s8.argtypes = [_f32p, _sz, _i8p, _sz, _f32p, _sz, _sz, C.c_void_p]
         L.oracle_quantize_group_s8.restype = C.c_int
         L.oracle_quantize_group_s8.argtypes = [_f32p, _sz, _i8p, _sz, _f32p, _sz, _sz, _sz]
         L.oracle_dequant_group_s8.argtypes = [_i8p, _sz, _f32p, _sz, _f32p, _sz, _sz, _sz]
@@ -91,6 +93,20 @@ class Oracle:
         out = np.zeros(rows.shape[0], np.float64)
         self.lib.oracle_gemm_f64acc_sample(x, x.shape[1], w, w.shape[1], x.shape[1], rows, cols, rows.shape[0], out)
         return out
+
+    def quantize_rows_s8(self, w, col_scale=None):
+        """float32 values on the binary16 grid [N, K] -> (int8 [N, K], float32 [N]): the reference's per-output-row quantiser."""
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        n, k = w.shape
+        q = np.empty((n, k), dtype=np.int8)
+        s = np.empty((n,), dtype=np.float32)
+        cs = None
+        if col_scale is not None:
+            cs = np.ascontiguousarray(col_scale, dtype=np.float32)
+            assert cs.shape == (k,)
+        if self.lib.oracle_quantize_rows_s8(w, k, q, k, s, n, k, cs.ctypes.data if cs is not None else None) != 0:
+            raise ValueError("oracle_quantize_rows_s8 rejected its arguments")
+        return q, s
 
     def quantize_group_s8(self, w):
         w = f32(w)

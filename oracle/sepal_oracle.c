@@ -197,6 +197,37 @@ void oracle_gemm_f64acc_sample(const float* x, size_t ldx, const float* w, size_
 
 /* ---- int8 weights, one float32 scale per output row and group of 128 values of k ---------------------------------------- */
 
+/* Per-output-row int8 quantiser of the reference's gpu-q8w weights (runner/cuda/src/gemm_s8_kernels.cu:28-31 quantize_one, :83-118
+ * quantize_weights_s8_kernel, Plain layout): amax = max |w[r, c] * col_scale[c]| over the row (w is binary16 widened to float32; given
+ * here as float32 values on the binary16 grid), inv = 127 / amax (0 for a zero row), scales[r] = amax / 127, q = round-to-nearest-even of
+ * (w * col_scale) * inv, clamped to [-127, 127]. Every operation is a correctly rounded float32 one, so it has one result. */
+int oracle_quantize_rows_s8(const float* w, size_t ld_w, int8_t* q, size_t ld_q, float* scales, size_t n, size_t k, const float* col_scale) {
+    if (ld_w < k || ld_q < k) return 1;
+    for (size_t r = 0; r < n; ++r) {
+        float amax = 0.0f;
+        for (size_t c = 0; c < k; ++c) {
+            volatile float v = w[r * ld_w + c];
+            if (col_scale) v = v * col_scale[c];
+            const float a = fabsf(v);
+            if (a > amax) amax = a;
+        }
+        volatile float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+        volatile float scale = amax / 127.0f;
+        scales[r] = scale;
+        for (size_t c = 0; c < k; ++c) {
+            volatile float v = w[r * ld_w + c];
+            if (col_scale) v = v * col_scale[c];
+            volatile float scaled = v * inv;
+            long iv = lrintf(scaled); /* round to nearest even in the default rounding mode */
+            if (iv > 127) iv = 127;
+            if (iv < -127) iv = -127;
+            q[r * ld_q + c] = (int8_t)iv;
+        }
+    }
+    return 0;
+}
+
+
 /* The group quantiser, runner/cuda/src/gemm_simt_kernels.cu:267-286 (host twin: runner/cuda/tests/test_gemm_simt_kernels.cpp:73-90):
  * scale = max|w| / 127 (IEEE float division), q = clamp(rint(w / scale), -127, 127); an all-zero group gets scale 0, q 0.
  * src [rows, K] stride ld_src; q [rows, K] stride ld_q bytes; s [rows, K/128] stride ld_s. K a multiple of 128. */

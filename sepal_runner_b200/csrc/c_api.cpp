@@ -134,6 +134,19 @@ int32_t sepal_b200_gemm_w8g(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, c
     });
 }
 
+int32_t sepal_b200_gemm_w8r(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const int8_t* q, uint64_t ld_q, const float* sw, void* y, uint64_t ld_y,
+                            int32_t y_half, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t config, void* stream) {
+    return guarded([&] {
+        require(ctx, "ctx");
+        launch_gemm_w8r(ctx->ctx, x, ld_x, q, ld_q, sw, y, ld_y, y_half != 0, t, n, k, epilogue_of(epilogue), config, static_cast<cudaStream_t>(stream));
+    });
+}
+
+int32_t sepal_b200_quantize_rows_s8(const void* w, uint64_t ld_w, int8_t* q, uint64_t ld_q, float* scales, uint64_t n, uint64_t k, const float* col_scale,
+                                    void* stream) {
+    return guarded([&] { launch_quantize_rows_s8(w, ld_w, q, ld_q, scales, n, k, col_scale, static_cast<cudaStream_t>(stream)); });
+}
+
 int32_t sepal_b200_quantize_group_s8(const float* src, uint64_t ld_src, int8_t* q, uint64_t ld_q, float* s, uint64_t ld_s, uint64_t rows, uint64_t k,
                                      void* stream) {
     return guarded([&] { launch_quantize_group_s8(src, ld_src, q, ld_q, s, ld_s, rows, k, static_cast<cudaStream_t>(stream)); });

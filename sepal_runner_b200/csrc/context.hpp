@@ -40,6 +40,9 @@ struct Context {
     int* status = nullptr;       // device word: 0 = fine; otherwise the code of the first wait that ran out (see kStatus*)
     int* status_host = nullptr;  // pinned host copy for sepal_b200_status
     TensorMapEncodeFn encode = nullptr;
+    void* unit_scales = nullptr;  // kUnitScales binary16 ones: the scale table of an int8 multiply whose scales are applied per output column
+    float* unit = nullptr;        // device float 1.0
+    static constexpr std::size_t kUnitScales = 1u << 16;
 
     Context(int device, std::size_t workspace_bytes);
     /// A context over device memory that somebody else owns: nothing is allocated here, and such a context must never be destroyed

@@ -38,6 +38,33 @@ __global__ void quantize_group_s8_kernel(const float* src, std::size_t ld_src, s
     if (lane == 0) s[row * ld_s + g] = scale;
 }
 
+// One block per row of a binary16 weight matrix: the row's largest magnitude (a maximum does not depend on the order it is taken in),
+// then every element on its own. Same arithmetic as the reference (runner/cuda/src/gemm_s8_kernels.cu:28-31,83-118): inv = 127 / max
+// (IEEE division), q = round-to-nearest-even of w * inv clamped to [-127, 127], scale = max / 127.
+__global__ void quantize_rows_s8_kernel(const __half* w, std::size_t ld_w, std::int8_t* q, std::size_t ld_q, float* scales, std::size_t k,
+                                        const float* col_scale) {
+    __shared__ float warp_max[8];
+    const std::size_t row = blockIdx.x;
+    const __half* wr = w + row * ld_w;
+    const auto value = [&](std::size_t c) {
+        const float v = __half2float(wr[c]);
+        return col_scale != nullptr ? __fmul_rn(v, col_scale[c]) : v;
+    };
+    float amax = 0.0f;
+    for (std::size_t c = threadIdx.x; c < k; c += blockDim.x) amax = fmaxf(amax, fabsf(value(c)));
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    if (threadIdx.x % 32 == 0) warp_max[threadIdx.x / 32] = amax;
+    __syncthreads();
+    amax = warp_max[0];
+    for (unsigned i = 1; i < blockDim.x / 32; ++i) amax = fmaxf(amax, warp_max[i]);
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    if (threadIdx.x == 0) scales[row] = __fdiv_rn(amax, 127.0f);
+    for (std::size_t c = threadIdx.x; c < k; c += blockDim.x) {
+        const int r = __float2int_rn(__fmul_rn(value(c), inv));
+        q[row * ld_q + c] = static_cast<std::int8_t>(min(127, max(-127, r)));
+    }
+}
+
 // Largest scale of the matrix, as the bit pattern of a non-negative float (which orders like an unsigned integer).
 __global__ void scale_max_kernel(const float* s, std::size_t ld_s, std::size_t n, std::size_t groups, unsigned* max_bits) {
     const std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -99,6 +126,18 @@ void launch_quantize_group_s8(const float* src, std::size_t ld_src, std::int8_t*
     if (src == nullptr || q == nullptr || s == nullptr) throw std::invalid_argument("launch_quantize_group_s8: null pointer");
     quantize_group_s8_kernel<<<blocks_for(rows * groups * 32, 256), 256, 0, stream>>>(src, ld_src, q, ld_q, s, ld_s, rows, groups);
     check(cudaGetLastError(), "quantize_group_s8_kernel launch");
+    count_launch();
+}
+
+void launch_quantize_rows_s8(const void* w, std::size_t ld_w, std::int8_t* q, std::size_t ld_q, float* scales, std::size_t n, std::size_t k,
+                             const float* col_scale, cudaStream_t stream) {
+    if (k % 16 != 0 || ld_w % 16 != 0 || ld_q % 16 != 0 || ld_w < k || ld_q < k)
+        throw std::invalid_argument("launch_quantize_rows_s8: K and the strides must be multiples of 16, and the strides must hold a row");
+    if (n * k == 0) return;
+    if (w == nullptr || q == nullptr || scales == nullptr) throw std::invalid_argument("launch_quantize_rows_s8: null pointer");
+    if (n > 0x7FFFFFFFu) throw std::invalid_argument("launch_quantize_rows_s8: too many rows for one launch");
+    quantize_rows_s8_kernel<<<static_cast<unsigned>(n), 256, 0, stream>>>(static_cast<const __half*>(w), ld_w, q, ld_q, scales, k, col_scale);
+    check(cudaGetLastError(), "quantize_rows_s8_kernel launch");
     count_launch();
 }
 

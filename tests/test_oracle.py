@@ -122,6 +122,30 @@ def test_quantiser_matches_a_numpy_restatement(oracle):
     assert np.array_equal(s, scale) and np.array_equal(q, want)
 
 
+def test_row_quantiser_known_answers_and_numpy_restatement(oracle):
+    # runner/cuda/src/gemm_s8_kernels.cu:28-31 (quantize_one) and :83-118 (one scale per output row, Plain layout)
+    w = np.zeros((4, 32), np.float32)
+    w[0, :8] = [127.0, 0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 126.5]  # amax 127: inv = 1, scale = 1, ties go to even
+    w[1, :4] = [0.25, -0.125, 0.0625, 0.0]                        # amax 0.25: inv = 508
+    w[3, :3] = [1.0, 2.0, 4.0]
+    q, s = oracle.quantize_rows_s8(w)
+    assert s[0] == 1.0 and list(q[0, :8]) == [127, 0, 2, 2, 0, -2, -2, 126]
+    assert s[1] == np.float32(0.25) / np.float32(127.0) and list(q[1, :4]) == [127, -64, 32, 0]  # -63.5 -> -64, 31.75 -> 32
+    assert s[2] == 0.0 and not q[2].any()                         # a zero row: scale 0 and zeros
+    col = np.ones(32, np.float32)
+    col[:3] = [4.0, 2.0, 1.0]                                    # smoothing factors multiply the columns first: all three become 4
+    q, s = oracle.quantize_rows_s8(w, col)
+    assert list(q[3, :3]) == [127, 127, 127] and s[3] == np.float32(4.0) / np.float32(127.0)
+    rng = np.random.default_rng(12)
+    w = oracle.to_f16_grid((rng.standard_normal((24, 256)) * 0.02).astype(np.float32))
+    q, s = oracle.quantize_rows_s8(w)
+    amax = np.abs(w).max(axis=1)
+    inv = (np.float32(127.0) / amax).astype(np.float32)
+    want = np.clip(np.rint((w * inv[:, None]).astype(np.float32)), -127, 127).astype(np.int8)
+    assert np.array_equal(q, want) and np.array_equal(s, (amax / np.float32(127.0)).astype(np.float32))
+    assert np.all(np.abs(q.astype(np.float32) * s[:, None] - w) <= 0.5 * s[:, None] * (1 + 1e-5))
+
+
 # ---- against the reference's code itself, where it was built -------------------------------------------------------------------
 
 

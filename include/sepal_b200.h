@@ -183,6 +183,14 @@ SEPAL_B200_API void sepal_b200_trunk_close(sepal_b200_trunk* trunk);
  * [n, hidden] floats (host). times_ms: NULL or 2 doubles (device time of the request by CUDA events; reserved). Returns when done. */
 SEPAL_B200_API int32_t sepal_b200_trunk_run(sepal_b200_trunk* trunk, const uint32_t* tokens, uint64_t n, float* last_hidden, float* all_hidden,
                                             double* times_ms);
+/* Many requests at once, with the flat arrays of sepal_score (runner/include/sepal/c_api.h:46-60): tokens holds the requests end to end,
+ * request r being tokens[offsets[r] .. offsets[r + 1]). They are packed into calls as the reference's engine packs them
+ * (runner/cuda/src/gpu_decision_engine.cpp:233-266: segments of at most max_call_tokens in request order, a new call when the next
+ * segment does not fit, at most 64 segments a call), so short requests share a call and its large-M GEMMs. last_hidden: [n_requests,
+ * hidden] floats (host); times_s: NULL or n_requests doubles, the seconds from the start of this function's device work until the
+ * request's result was complete (CUDA events). Returns when everything is on the host. */
+SEPAL_B200_API int32_t sepal_b200_trunk_score(sepal_b200_trunk* trunk, uint64_t n_requests, const uint32_t* tokens, const uint64_t* offsets,
+                                              float* last_hidden, double* times_s);
 /* Copies a stored weight to the host (size-query protocol: host_out NULL only reports *needed). which: 0 embedding, 1 input norm,
  * 2 mixer in-projection, 3 mixer out-projection, 4 post norm, 5 packed [gate; up], 6 down. */
 SEPAL_B200_API int32_t sepal_b200_trunk_weight(sepal_b200_trunk* trunk, uint32_t layer, int32_t which, void* host_out, uint64_t capacity,

@@ -232,6 +232,13 @@ int32_t sepal_b200_trunk_run(sepal_b200_trunk* trunk, const uint32_t* tokens, ui
         trunk->trunk.run(tokens, n, last_hidden, all_hidden, times_ms);
     });
 }
+int32_t sepal_b200_trunk_score(sepal_b200_trunk* trunk, uint64_t n_requests, const uint32_t* tokens, const uint64_t* offsets, float* last_hidden,
+                               double* times_s) {
+    return guarded([&] {
+        require(trunk, "trunk");
+        trunk->trunk.score(n_requests, tokens, offsets, last_hidden, times_s);
+    });
+}
 int32_t sepal_b200_trunk_weight(sepal_b200_trunk* trunk, uint32_t layer, int32_t which, void* host_out, uint64_t capacity, uint64_t* needed) {
     return guarded([&] {
         require(trunk, "trunk");

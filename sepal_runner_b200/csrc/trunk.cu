@@ -210,9 +210,10 @@ Trunk::Trunk(int device, const TrunkConfig& config) : cfg_(config), ctx_(device,
     a1_ = alloc(T * H * 2);
     p_ = alloc(T * static_cast<std::size_t>(p_width_) * 2);
     a3_ = alloc(T * I * 2);
-    tokens_dev_ = static_cast<std::uint32_t*>(alloc(T * 4));
-    check(cudaMallocHost(reinterpret_cast<void**>(&tokens_pinned_), T * 4), "cudaMallocHost");
-    check(cudaMallocHost(reinterpret_cast<void**>(&out_pinned_), H * 4), "cudaMallocHost");
+    tokens_dev_ = static_cast<std::uint32_t*>(alloc(2 * T * 4));
+    check(cudaMallocHost(reinterpret_cast<void**>(&tokens_pinned_), 2 * T * 4), "cudaMallocHost");
+    check(cudaMallocHost(reinterpret_cast<void**>(&out_pinned_), 2 * kMaxCallRows * H * 4), "cudaMallocHost");
+    for (cudaEvent_t& e : call_done_) check(cudaEventCreate(&e), "cudaEventCreate");
     check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
 }
 
@@ -220,6 +221,8 @@ Trunk::~Trunk() {
     (void)cudaSetDevice(ctx_.device);
     if (stream_ != nullptr) (void)cudaStreamSynchronize(stream_);
     for (void* p : allocations_) (void)cudaFree(p);
+    for (cudaEvent_t e : call_done_)
+        if (e != nullptr) (void)cudaEventDestroy(e);
     if (tokens_pinned_ != nullptr) (void)cudaFreeHost(tokens_pinned_);
     if (out_pinned_ != nullptr) (void)cudaFreeHost(out_pinned_);
     for (auto& e : ev_)
@@ -284,6 +287,105 @@ void Trunk::run(const std::uint32_t* tokens, std::size_t n, float* last_hidden, 
         times_ms[0] = ms;
         times_ms[1] = 0.0;
     }
+}
+
+void Trunk::score(std::size_t n_requests, const std::uint32_t* tokens, const std::uint64_t* offsets, float* last_hidden, double* times_s) {
+    if (n_requests == 0) return;
+    if (tokens == nullptr || offsets == nullptr || last_hidden == nullptr) throw std::invalid_argument("sepal_b200 trunk: null pointer");
+    const std::size_t H = cfg_.hidden, C = cfg_.max_call_tokens;
+    for (std::size_t r = 0; r < n_requests; ++r) {
+        if (offsets[r + 1] <= offsets[r]) throw std::invalid_argument("sepal_b200 trunk: request " + std::to_string(r) + " is empty or the offsets decrease");
+        for (std::uint64_t i = offsets[r]; i < offsets[r + 1]; ++i)
+            if (tokens[i] >= cfg_.vocab) throw std::invalid_argument("sepal_b200 trunk: token id " + std::to_string(tokens[i]) + " is outside the vocabulary");
+    }
+    // Segments in the order of the requests; a call takes segments until the next one does not fit.
+    struct Segment {
+        std::size_t request, begin, end;
+        bool last;  // the request ends with this segment
+    };
+    std::vector<Segment> segments;
+    for (std::size_t r = 0; r < n_requests; ++r) {
+        std::size_t at = offsets[r];
+        const std::size_t end = offsets[r + 1];
+        while (end - at > C) {
+            segments.push_back({r, at, at + C, false});
+            at += C;
+        }
+        segments.push_back({r, at, end, true});
+    }
+    check(cudaSetDevice(ctx_.device), "cudaSetDevice");
+    struct Call {
+        std::size_t first, count;  // its segments
+    };
+    std::vector<Call> calls;
+    for (std::size_t i = 0, in_call = 0; i < segments.size(); ++i) {
+        const std::size_t n = segments[i].end - segments[i].begin;
+        if (calls.empty() || in_call + n > C || calls.back().count >= kMaxCallRows) {
+            calls.push_back({i, 0});
+            in_call = 0;
+        }
+        ++calls.back().count;
+        in_call += n;
+    }
+    std::vector<cudaEvent_t> stamps;  // one per call, for the completion times
+    const auto drop_stamps = [&] {
+        for (cudaEvent_t e : stamps) (void)cudaEventDestroy(e);
+    };
+    try {
+        check(cudaEventRecord(ev_[0], stream_), "cudaEventRecord");
+        // Results of call c land in half c % 2 of the pinned output; they are copied out when call c + 1 has been enqueued.
+        const auto collect = [&](std::size_t c) {
+            check(cudaEventSynchronize(call_done_[c % 2]), "cudaEventSynchronize");
+            std::size_t slot = 0;
+            for (std::size_t i = calls[c].first; i < calls[c].first + calls[c].count; ++i)
+                if (segments[i].last) std::memcpy(last_hidden + segments[i].request * H, out_pinned_ + ((c % 2) * kMaxCallRows + slot++) * H, H * 4);
+        };
+        for (std::size_t c = 0; c < calls.size(); ++c) {
+            const std::size_t half = c % 2;
+            if (c >= 2) collect(c - 2);  // also: the buffers of this half are free again
+            std::uint32_t* pinned = tokens_pinned_ + half * C;
+            std::uint32_t* dev = tokens_dev_ + half * C;
+            std::size_t rows = 0;
+            for (std::size_t i = calls[c].first; i < calls[c].first + calls[c].count; ++i) {
+                const std::size_t n = segments[i].end - segments[i].begin;
+                std::memcpy(pinned + rows, tokens + segments[i].begin, n * 4);
+                rows += n;
+            }
+            check(cudaMemcpyAsync(dev, pinned, rows * 4, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(tokens)");
+            forward_call(dev, rows);
+            std::size_t row = 0, slot = 0;
+            for (std::size_t i = calls[c].first; i < calls[c].first + calls[c].count; ++i) {
+                row += segments[i].end - segments[i].begin;
+                if (segments[i].last)
+                    check(cudaMemcpyAsync(out_pinned_ + (half * kMaxCallRows + slot++) * H, x_ + (row - 1) * H, H * 4, cudaMemcpyDeviceToHost, stream_),
+                          "cudaMemcpyAsync(last hidden)");
+            }
+            check(cudaEventRecord(call_done_[half], stream_), "cudaEventRecord");
+            if (times_s != nullptr) {
+                cudaEvent_t e = nullptr;
+                check(cudaEventCreate(&e), "cudaEventCreate");
+                stamps.push_back(e);
+                check(cudaEventRecord(e, stream_), "cudaEventRecord");
+            }
+        }
+        if (calls.size() >= 2) collect(calls.size() - 2);
+        collect(calls.size() - 1);
+        const int status = ctx_.read_status(stream_);
+        if (status != 0) throw std::runtime_error("sepal_b200 trunk: a kernel gave up waiting (status " + std::to_string(status) + ")");
+        if (times_s != nullptr) {
+            for (std::size_t c = 0; c < calls.size(); ++c) {
+                float ms = 0.0f;
+                check(cudaEventElapsedTime(&ms, ev_[0], stamps[c]), "cudaEventElapsedTime");
+                for (std::size_t i = calls[c].first; i < calls[c].first + calls[c].count; ++i)
+                    if (segments[i].last) times_s[segments[i].request] = ms * 1e-3;
+            }
+        }
+    } catch (...) {
+        (void)cudaStreamSynchronize(stream_);
+        drop_stamps();
+        throw;
+    }
+    drop_stamps();
 }
 
 std::size_t Trunk::weight(std::uint32_t layer, TrunkWeight which, void* host_out, std::size_t capacity) {

@@ -54,6 +54,7 @@ SIGNATURES = {
     "sepal_b200_trunk_open": (_i32, [_i32, _vp, C.POINTER(_vp)]),
     "sepal_b200_trunk_close": (None, [_vp]),
     "sepal_b200_trunk_run": (_i32, [_vp, _vp, _u64, _vp, _vp, _vp]),
+    "sepal_b200_trunk_score": (_i32, [_vp, _u64, _vp, _vp, _vp, _vp]),
     "sepal_b200_trunk_weight": (_i32, [_vp, _u32, _i32, _vp, _u64, C.POINTER(_u64)]),
     "sepal_b200_trunk_info": (_i32, [_vp, C.POINTER(_u64), C.POINTER(_u64)]),
     "sepal_b200_provider_open": (_i32, [_i32, _u64, C.POINTER(_vp)]),
@@ -318,6 +319,19 @@ class Trunk:
         times = (C.c_double * 2)()
         _check(self._lib.sepal_b200_trunk_run(self._h, tokens.ctypes.data, n, last.ctypes.data, allh.ctypes.data if want_all else None, times))
         return last, allh, float(times[0])
+
+    def score(self, requests):
+        """requests: a list of uint32 token arrays. They are packed into calls of up to max_call_tokens rows (short requests share a call).
+        Returns (last hidden [n_requests, hidden], seconds until each request's result was complete on the device)."""
+        import numpy as np
+
+        offsets = np.zeros(len(requests) + 1, np.uint64)
+        offsets[1:] = np.cumsum([len(r) for r in requests])
+        flat = np.ascontiguousarray(np.concatenate([np.asarray(r, np.uint32) for r in requests])) if requests else np.zeros(0, np.uint32)
+        last = np.empty((len(requests), self.config.hidden), np.float32)
+        times = np.zeros(len(requests), np.float64)
+        _check(self._lib.sepal_b200_trunk_score(self._h, len(requests), flat.ctypes.data, offsets.ctypes.data, last.ctypes.data, times.ctypes.data))
+        return last, times
 
     def weight(self, which: str, layer: int = 0):
         """A stored weight as a numpy array (float16 matrices as flat arrays: reshape with the known geometry)."""

@@ -116,3 +116,33 @@ def test_trunk_with_int8_mlp_stays_close_to_the_fp16_trunk(oracle):
     finally:
         a.close()
         b.close()
+
+
+def test_score_packs_requests_into_calls_and_matches_one_by_one(oracle):
+    """Many requests at once (the flat arrays of sepal_score): short ones share a call, one longer than a call is cut into segments,
+    empty ones are refused; each result equals the request run on its own (the rows of a call do not see one another)."""
+    import sepal_runner_b200 as sb
+
+    cfg = small_config(sb)
+    trunk = sb.Trunk(0, cfg)
+    try:
+        rng = np.random.default_rng(99)
+        lengths = [1, 299, 2, 150, 150, 1, 700, 37, 300, 301] + [3] * 70  # 70 tiny ones: more segments than one call may hold
+        requests = [rng.integers(0, cfg.vocab, n).astype(np.uint32) for n in lengths]
+        hidden, times = trunk.score(requests)
+        assert hidden.shape == (len(requests), cfg.hidden) and np.isfinite(hidden).all()
+        assert (times > 0).all() and (np.diff(times) >= 0).all()  # requests finish in the order of their calls
+        for i in (0, 1, 3, 6, 8, 9, 40, len(requests) - 1):
+            alone, _, _ = trunk.run(requests[i])
+            assert rel_fro(hidden[i], alone) < 1e-5, i
+        again, _ = trunk.score(requests)
+        assert np.array_equal(again, hidden)
+        one, _ = trunk.score(requests[6:7])
+        assert rel_fro(one[0], hidden[6]) < 1e-5
+        with pytest.raises(sb.SepalB200Error, match="empty"):
+            trunk.score([requests[0], np.zeros(0, np.uint32)])
+        with pytest.raises(sb.SepalB200Error, match="outside the vocabulary"):
+            trunk.score([np.array([1, cfg.vocab + 5], np.uint32)])
+        assert trunk.score([])[0].shape == (0, cfg.hidden)
+    finally:
+        trunk.close()

@@ -75,6 +75,12 @@ SEPAL_B200_API int32_t sepal_b200_status(sepal_b200_ctx* ctx, void* stream, int3
 /* Kernels of this library the calling thread has launched since the previous call of this function. */
 SEPAL_B200_API uint64_t sepal_b200_take_launch_count(void);
 
+/* Process-wide switch, on by default: the GEMM kernels (and the trunk's embedding and norm kernels) are launched as programmatic
+ * dependents of the kernel before them in the stream, so a kernel's set-up overlaps the end of the one before it; each of them waits for
+ * that kernel to complete before it touches global memory, so results do not change. No counterpart in the reference (whose engine
+ * launches its kernels one after the other, runner/cuda/src/cuda_engine.cpp:1724-1952); off = plain stream order, for comparisons. */
+SEPAL_B200_API void sepal_b200_set_launch_overlap(int32_t on);
+
 /* ---- launchers on device pointers ------------------------------------------------------------------------------------------ */
 
 /* binary16 x binary16 -> float32 accumulation on the tensor cores (tcgen05.mma), result binary16 (y_half != 0) or float32.

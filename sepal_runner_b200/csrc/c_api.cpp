@@ -101,6 +101,8 @@ int32_t sepal_b200_status(sepal_b200_ctx* ctx, void* stream, int32_t* status_out
 
 uint64_t sepal_b200_take_launch_count(void) { return take_launch_count(); }
 
+void sepal_b200_set_launch_overlap(int32_t on) { set_launch_overlap(on != 0); }
+
 int32_t sepal_b200_gemm_f16(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const void* w, uint64_t ld_w, void* y, uint64_t ld_y, int32_t y_half,
                             uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t config, void* stream) {
     return guarded([&] {

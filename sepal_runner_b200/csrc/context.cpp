@@ -1,9 +1,16 @@
 #include "context.hpp"
 
+#include <atomic>
 #include <cstring>
 #include <vector>
 
 namespace sepal::b200 {
+
+namespace {
+std::atomic<bool> g_launch_overlap{true};
+}
+bool launch_overlap() { return g_launch_overlap.load(std::memory_order_relaxed); }
+void set_launch_overlap(bool on) { g_launch_overlap.store(on, std::memory_order_relaxed); }
 
 std::size_t default_workspace_bytes(int sm_count) {
     return static_cast<std::size_t>(sm_count) * 2u * (128u * 256u * sizeof(float));

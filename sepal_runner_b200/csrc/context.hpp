@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <utility>
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -56,6 +57,28 @@ struct Context {
     /// Reads the status word after waiting for `stream`, and clears it. 0 means no kernel reported a problem.
     int read_status(cudaStream_t stream);
 };
+
+/// Whether kernels are launched as programmatic dependents of the kernel before them in the stream (on by default): the next
+/// kernel's CTAs take the SMs as this one's CTAs leave, set up their barriers and tensor memory, and wait in griddepcontrol.wait until
+/// this kernel has completed. Every kernel launched this way executes that wait before it touches global memory.
+bool launch_overlap();
+void set_launch_overlap(bool on);
+
+/// kernel<<<grid, block, smem, stream>>>(args...), as a programmatic dependent when launch_overlap() is on.
+template <class... Params, class... Args>
+void launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, std::size_t smem, cudaStream_t stream, const char* what, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = launch_overlap() ? 1 : 0;
+    check(cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...), what);
+}
 
 /// Default scratch size: two 128 x 256 float32 tiles for each of `sm_count` CTAs.
 std::size_t default_workspace_bytes(int sm_count);

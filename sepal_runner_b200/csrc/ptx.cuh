@@ -44,6 +44,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Generic-proxy writes to shared memory (st.shared) made visible to the async proxy (tcgen05.mma reading the tile).
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Programmatic dependent launch. wait: returns once the kernel launched before this one in the stream has completed and its writes are
+// visible (at once when this kernel was not launched as a dependent). launch_dependents: the kernel after this one may start
+// occupying free SMs (it then sits in its own wait); takes effect when every CTA of this grid has called it or has exited.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 // Orders this thread's ordinary accesses (any state space) with accesses made through the async proxy (bulk copies).
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 

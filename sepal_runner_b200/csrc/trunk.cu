@@ -1,5 +1,7 @@
 #include "trunk.hpp"
 
+#include "ptx.cuh"
+
 #include <cstring>
 #include <stdexcept>
 #include <string>
@@ -39,6 +41,8 @@ __global__ void fill_normal_float_kernel(float* dst, std::size_t count, unsigned
 
 // One block per token: a row of the binary16 table widened to the float32 residual stream, 8 values per thread and step.
 __global__ void embed_kernel(const __half* table, const std::uint32_t* tokens, float* x, std::size_t hidden, std::size_t vocab) {
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();  // the kernel before this one may still read the rows this one overwrites
     const std::size_t row = blockIdx.x;
     std::size_t id = tokens[row];
     if (id >= vocab) id = vocab - 1;  // the host checks the ids; never read outside the table
@@ -57,6 +61,8 @@ __global__ void embed_kernel(const __half* table, const std::uint32_t* tokens, f
 // not depend on the other rows.
 __global__ void rms_norm_half_kernel(const float* x, std::size_t ld_x, const float* w, __half* y, std::size_t ld_y, std::size_t cols, float eps) {
     __shared__ float partial[32];
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();  // x is the output of the multiply launched before this kernel
     const float* xr = x + static_cast<std::size_t>(blockIdx.x) * ld_x;
     __half* yr = y + static_cast<std::size_t>(blockIdx.x) * ld_y;
     float ss = 0.0f;
@@ -96,8 +102,8 @@ unsigned blocks_for(std::size_t n, unsigned per) { return static_cast<unsigned>(
 void launch_embed(const void* table_half, const std::uint32_t* tokens, float* x, std::size_t rows, std::size_t hidden, std::size_t vocab, cudaStream_t stream) {
     if (hidden % 8 != 0) throw std::invalid_argument("launch_embed: the hidden size must be a multiple of 8");
     if (rows == 0) return;
-    embed_kernel<<<static_cast<unsigned>(rows), 128, 0, stream>>>(static_cast<const __half*>(table_half), tokens, x, hidden, vocab);
-    check(cudaGetLastError(), "embed_kernel launch");
+    launch_kernel(embed_kernel, dim3(static_cast<unsigned>(rows)), dim3(128), 0, stream, "embed_kernel launch", static_cast<const __half*>(table_half), tokens, x,
+                  hidden, vocab);
     count_launch();
 }
 
@@ -105,8 +111,8 @@ void launch_rms_norm_half(const float* x, std::size_t ld_x, const float* w, void
                           cudaStream_t stream) {
     if (cols % 4 != 0 || ld_x % 4 != 0 || ld_y % 4 != 0) throw std::invalid_argument("launch_rms_norm_half: columns and strides must be multiples of 4");
     if (rows == 0) return;
-    rms_norm_half_kernel<<<static_cast<unsigned>(rows), 256, 0, stream>>>(x, ld_x, w, static_cast<__half*>(y_half), ld_y, cols, eps);
-    check(cudaGetLastError(), "rms_norm_half_kernel launch");
+    launch_kernel(rms_norm_half_kernel, dim3(static_cast<unsigned>(rows)), dim3(256), 0, stream, "rms_norm_half_kernel launch", x, ld_x, w,
+                  static_cast<__half*>(y_half), ld_y, cols, eps);
     count_launch();
 }
 

@@ -53,6 +53,7 @@ SIGNATURES = {
     "sepal_b200_rms_norm_half": (_i32, [_vp, _u64, _vp, _vp, _u64, _u64, _u64, C.c_float, _vp]),
     "sepal_b200_trunk_open": (_i32, [_i32, _vp, C.POINTER(_vp)]),
     "sepal_b200_trunk_close": (None, [_vp]),
+    "sepal_b200_set_launch_overlap": (None, [_i32]),
     "sepal_b200_trunk_run": (_i32, [_vp, _vp, _u64, _vp, _vp, _vp]),
     "sepal_b200_trunk_score": (_i32, [_vp, _u64, _vp, _vp, _vp, _vp]),
     "sepal_b200_trunk_weight": (_i32, [_vp, _u32, _i32, _vp, _u64, C.POINTER(_u64)]),

@@ -40,10 +40,13 @@ WORKLOADS = {
     "w8g_down_m4096": ("w8g", 4096, 2560, 9728, 1),
     "f16_up_m4096": ("f16", 4096, 9728, 2560, 0),
 }
-# Every named trunk GEMM (N x K) for the per-shape table: SURVEY's list of projections at hidden 2560, MLP 9728.
+# Every named trunk GEMM (N x K) for the per-shape table: the projections of a layer at hidden 2560, MLP 9728.
 TRUNK_SHAPES = [("gate_up+swiglu", 19456, 2560, "swiglu"), ("up (config 0)", 9728, 2560, "store"), ("down+residual", 2560, 9728, "add"),
                 ("q", 4096, 2560, "store"), ("k or v", 1024, 2560, "store"), ("qkv fused", 6144, 2560, "store"), ("o+residual", 2560, 4096, "add"),
                 ("dn_in", 8192, 2560, "store"), ("dn_out+residual", 2560, 2048, "add")]
+# DRAM bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the workload's kernel; the summaries under
+# profiles/ give the command). None: not captured.
+NCU_TRAFFIC = {"w8g_down_m900": 52.0e6, "f16_up_m4096": None}
 L2_BYTES = 126 * 1024 * 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -253,7 +256,8 @@ def run_ours(args):
             "unit": "TFLOP/s",
             "frac": round(tflops_gpu / peak_tf, 4),
             "peak_source": f"bf16_tflops of MEASURED_PEAKS.json ({peak_kind}; burst: the kernel is timed alone)",
-            "traffic": args.traffic,
+            "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC.get(args.workload),
+            "traffic_source": "--traffic" if args.traffic is not None else ("profiles/gemm_w8_pair_kernel_w8g_down_m900.md" if NCU_TRAFFIC.get(args.workload) else None),
             "algorithmic_bytes": algorithmic_bytes(kind, m, n, k),
             "hbm_gbs_achieved": round(algorithmic_bytes(kind, m, n, k) / (per_call_ms * 1e-3) / 1e9, 1),
             "us_per_launch": round(per_call_ms * 1e3, 2),

@@ -160,9 +160,14 @@ SEPAL_B200_API int32_t sepal_b200_half_to_float(const void* src, float* dst, uin
 
 /* Token embedding gather and the zero-centred RMSNorm that produce a multiply's binary16 operand from the float32 residual stream
  * (launch_embed / launch_rms_norm of runner/cuda/src/kernels_elementwise.hpp:41-46,85-95): x[t, :] = table[tokens[t], :] widened;
- * y = x / sqrt(mean(x^2) + eps) * (1 + w), float32 in, binary16 out. hidden a multiple of 8; cols, ld_x, ld_y multiples of 4. */
+ * y = (x / sqrt(sum(x^2) / cols + eps)) * (1 + w), float32 in, binary16 out, with the reference's float32 arithmetic and its fixed order
+ * of summation (runner/cuda/src/kernels_elementwise.cu:6-11,114-141), so a row's bits are the reference kernel's. hidden a multiple of
+ * 8; cols, ld_x, ld_y multiples of 4. sepal_b200_embed_rms_norm_half does both for the first layer in one pass over the row (the
+ * engine's back-to-back launches at runner/cuda/src/cuda_engine.cpp:1676-1692). */
 SEPAL_B200_API int32_t sepal_b200_embed(const void* table_half, const uint32_t* tokens, float* x, uint64_t rows, uint64_t hidden, uint64_t vocab,
                                         void* stream);
+SEPAL_B200_API int32_t sepal_b200_embed_rms_norm_half(const void* table_half, const uint32_t* tokens, float* x, const float* w, void* y_half,
+                                                      uint64_t ld_y, uint64_t rows, uint64_t hidden, uint64_t vocab, float eps, void* stream);
 SEPAL_B200_API int32_t sepal_b200_rms_norm_half(const float* x, uint64_t ld_x, const float* w, void* y_half, uint64_t ld_y, uint64_t rows,
                                                 uint64_t cols, float eps, void* stream);
 

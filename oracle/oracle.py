@@ -55,6 +55,8 @@ class Oracle:
         L.oracle_gemm_f64acc.argtypes = [_f32p, _sz, _f32p, _sz, _f32p, _sz, _sz, _sz, _sz, C.c_float]
         L.oracle_gemm_fma_chain.argtypes = [_f32p, _sz, _f32p, _sz, _f32p, _sz, _sz, _sz, _sz]
         L.oracle_gemm_f64acc_sample.argtypes = [_f32p, _sz, _f32p, _sz, _sz, _u32p, _u32p, _sz, _f64p]
+        L.oracle_rmsnorm_f32_ordered.restype = C.c_int
+        L.oracle_rmsnorm_f32_ordered.argtypes = [_f32p, _sz, _f32p, _sz, _sz, _sz, _f32p, C.c_float]
         L.oracle_quantize_rows_s8.restype = C.c_int
         L.oracle_quantize_rows_s8.argtypes = [_f32p, _sz, _i8p, _sz, _f32p, _sz, _sz, C.c_void_p]
         L.oracle_quantize_group_s8.restype = C.c_int
@@ -93,6 +95,16 @@ class Oracle:
         out = np.zeros(rows.shape[0], np.float64)
         self.lib.oracle_gemm_f64acc_sample(x, x.shape[1], w, w.shape[1], x.shape[1], rows, cols, rows.shape[0], out)
         return out
+
+    def rmsnorm_ordered(self, x, w, eps):
+        """The norm with the float32 arithmetic and summation order of the reference's CUDA kernel (bit for bit); float32 result."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        rows, cols = x.shape
+        y = np.empty_like(x)
+        if self.lib.oracle_rmsnorm_f32_ordered(x, cols, y, cols, rows, cols, w, np.float32(eps)) != 0:
+            raise ValueError("oracle_rmsnorm_f32_ordered: the row length must be a multiple of 4")
+        return y
 
     def quantize_rows_s8(self, w, col_scale=None):
         """float32 values on the binary16 grid [N, K] -> (int8 [N, K], float32 [N]): the reference's per-output-row quantiser."""

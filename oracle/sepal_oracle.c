@@ -295,6 +295,52 @@ void oracle_add(float* y, size_t ld_y, const float* acc, size_t ld_acc, size_t t
         for (size_t c = 0; c < n; ++c) y[r * ld_y + c] = y[r * ld_y + c] + acc[r * ld_acc + c];
 }
 
+/* The same norm with the float32 arithmetic and the order of summation of the reference's CUDA kernel, bit for bit
+ * (runner/cuda/src/kernels_elementwise.cu:6-11 for the order, :114-141 for the operations): the row in chunks of four consecutive
+ * elements, chunk c summed by "thread" c mod 256 in ascending chunk order with one fused multiply-add per element; a butterfly over each
+ * group of 32 partial sums (p[l] += p[l ^ o] for o = 16, 8, 4, 2, 1, all lanes at once); the eight group sums added in order;
+ * rms = sqrt(sum / cols + eps); y = (x / rms) * (1 + w); every step rounded to float32. cols must be a multiple of 4. The result is
+ * left in float32; the device rounds it to binary16. */
+int oracle_rmsnorm_f32_ordered(const float* x, size_t ldx, float* y, size_t ldy, size_t rows, size_t cols, const float* w, float eps) {
+    if (cols % 4 != 0) return 1;
+    const size_t chunks = cols / 4;
+    for (size_t r = 0; r < rows; ++r) {
+        const float* xr = x + r * ldx;
+        float partial[256];
+        for (size_t t = 0; t < 256; ++t) {
+            float acc = 0.0f;
+            for (size_t c = t; c < chunks; c += 256)
+                for (size_t e = 0; e < 4; ++e) acc = fmaf(xr[4 * c + e], xr[4 * c + e], acc);
+            partial[t] = acc;
+        }
+        float group[8];
+        for (size_t g = 0; g < 8; ++g) {
+            float lane[32], next[32];
+            memcpy(lane, partial + 32 * g, sizeof lane);
+            for (unsigned o = 16; o > 0; o >>= 1) {
+                for (unsigned l = 0; l < 32; ++l) {
+                    volatile float sum = lane[l] + lane[l ^ o];
+                    next[l] = sum;
+                }
+                memcpy(lane, next, sizeof lane);
+            }
+            group[g] = lane[0];
+        }
+        volatile float total = group[0];
+        for (size_t g = 1; g < 8; ++g) total = total + group[g];
+        volatile float mean = total / (float)cols;
+        volatile float shifted = mean + eps;
+        const float rms = sqrtf(shifted);
+        for (size_t c = 0; c < cols; ++c) {
+            volatile float q = xr[c] / rms;
+            volatile float g1 = 1.0f + w[c];
+            volatile float v = q * g1;
+            y[r * ldy + c] = v;
+        }
+    }
+    return 0;
+}
+
 /* Zero-centred RMSNorm of a row: y = x / sqrt(mean(x^2) + eps) * (1 + w), runner/cuda/src/kernels_elementwise.hpp:41-46
  * (CPU twin runner/src/cpu/elementwise.cpp:43-59, which takes w1 = 1 + w). The mean is taken in float64 here; the
  * reference kernels sum in float32 in a fixed order, so compare with a tolerance. */

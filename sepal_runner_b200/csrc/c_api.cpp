@@ -193,6 +193,19 @@ int32_t sepal_b200_embed(const void* table_half, const uint32_t* tokens, float* 
         launch_embed(table_half, tokens, x, rows, hidden, vocab, static_cast<cudaStream_t>(stream));
     });
 }
+int32_t sepal_b200_embed_rms_norm_half(const void* table_half, const uint32_t* tokens, float* x, const float* w, void* y_half, uint64_t ld_y, uint64_t rows,
+                                       uint64_t hidden, uint64_t vocab, float eps, void* stream) {
+    return guarded([&] {
+        if (rows != 0) {
+            require(table_half, "table");
+            require(tokens, "tokens");
+            require(x, "x");
+            require(w, "w");
+            require(y_half, "y");
+        }
+        launch_embed_rms_norm_half(table_half, tokens, x, w, y_half, ld_y, rows, hidden, vocab, eps, static_cast<cudaStream_t>(stream));
+    });
+}
 int32_t sepal_b200_rms_norm_half(const float* x, uint64_t ld_x, const float* w, void* y_half, uint64_t ld_y, uint64_t rows, uint64_t cols, float eps,
                                  void* stream) {
     return guarded([&] {

@@ -57,42 +57,95 @@ __global__ void embed_kernel(const __half* table, const std::uint32_t* tokens, f
     }
 }
 
-// One block per row. The sum of squares is taken in a fixed order (thread-strided partial sums, then a tree), so a row's result does
-// not depend on the other rows.
-__global__ void rms_norm_half_kernel(const float* x, std::size_t ld_x, const float* w, __half* y, std::size_t ld_y, std::size_t cols, float eps) {
-    __shared__ float partial[32];
+// The zero-centred RMSNorm with the reference's arithmetic and order of summation (runner/cuda/src/kernels_elementwise.cu:6-11,114-141):
+// a row is cut into chunks of four consecutive elements; chunk c belongs to thread c mod 256 of the row's block; a thread adds the
+// squares of its chunks in ascending order with one fused multiply-add per element; each warp sums its 32 partial sums by a butterfly
+// and the eight warp sums are added in order. rms = sqrt(sum / width + eps); y = (x / rms) * (1 + w), every step rounded to float32, the
+// result to binary16. A row's bits therefore depend on nothing but the row. Rows up to 4096 wide are read from memory once.
+constexpr unsigned kNormThreads = 256;
+constexpr int kNormHeld = 4;
+
+__device__ __forceinline__ float add_squares(float acc, const float4& v) {
+    acc = __fmaf_rn(v.x, v.x, acc);
+    acc = __fmaf_rn(v.y, v.y, acc);
+    acc = __fmaf_rn(v.z, v.z, acc);
+    return __fmaf_rn(v.w, v.w, acc);
+}
+
+__device__ __forceinline__ float norm_block_sum(float partial, float* warp_sums) {
+    for (int o = 16; o > 0; o >>= 1) partial += __shfl_xor_sync(0xFFFFFFFFu, partial, o);
+    if (threadIdx.x % 32 == 0) warp_sums[threadIdx.x / 32] = partial;
+    __syncthreads();
+    float total = warp_sums[0];
+    for (unsigned w = 1; w < kNormThreads / 32; ++w) total += warp_sums[w];
+    return total;
+}
+
+__device__ __forceinline__ void store_normed(__half* yr, std::size_t c, const float4& v, float rms, const float* w) {
+    const float4 g = *reinterpret_cast<const float4*>(w + 4 * c);
+    const __half2 lo = __floats2half2_rn(__fmul_rn(__fdiv_rn(v.x, rms), __fadd_rn(1.0f, g.x)), __fmul_rn(__fdiv_rn(v.y, rms), __fadd_rn(1.0f, g.y)));
+    const __half2 hi = __floats2half2_rn(__fmul_rn(__fdiv_rn(v.z, rms), __fadd_rn(1.0f, g.z)), __fmul_rn(__fdiv_rn(v.w, rms), __fadd_rn(1.0f, g.w)));
+    uint2 packed;
+    packed.x = *reinterpret_cast<const unsigned*>(&lo);
+    packed.y = *reinterpret_cast<const unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(yr + 4 * c) = packed;
+}
+
+// `Load` yields chunk c of the row as four floats (from the float32 stream, or from the binary16 embedding table, written to the stream
+// on the way).
+template <class Load>
+__device__ __forceinline__ void norm_row(Load&& load, const float* w, __half* yr, std::size_t cols, float eps) {
+    __shared__ float warp_sums[kNormThreads / 32];
+    const std::size_t chunks = cols / 4;
+    float4 held[kNormHeld];
+    float partial = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kNormHeld; ++i) {
+        const std::size_t c = threadIdx.x + static_cast<std::size_t>(i) * kNormThreads;
+        if (c < chunks) {
+            held[i] = load(c);
+            partial = add_squares(partial, held[i]);
+        }
+    }
+    for (std::size_t c = threadIdx.x + static_cast<std::size_t>(kNormHeld) * kNormThreads; c < chunks; c += kNormThreads) partial = add_squares(partial, load(c));
+    const float total = norm_block_sum(partial, warp_sums);
+    const float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(cols)), eps));
+#pragma unroll
+    for (int i = 0; i < kNormHeld; ++i) {
+        const std::size_t c = threadIdx.x + static_cast<std::size_t>(i) * kNormThreads;
+        if (c < chunks) store_normed(yr, c, held[i], rms, w);
+    }
+    for (std::size_t c = threadIdx.x + static_cast<std::size_t>(kNormHeld) * kNormThreads; c < chunks; c += kNormThreads) store_normed(yr, c, load(c), rms, w);
+}
+
+__global__ void __launch_bounds__(kNormThreads) rms_norm_half_kernel(const float* x, std::size_t ld_x, const float* w, __half* y, std::size_t ld_y,
+                                                                      std::size_t cols, float eps) {
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();  // x is the output of the multiply launched before this kernel
     const float* xr = x + static_cast<std::size_t>(blockIdx.x) * ld_x;
-    __half* yr = y + static_cast<std::size_t>(blockIdx.x) * ld_y;
-    float ss = 0.0f;
-    for (std::size_t c = threadIdx.x * 4; c < cols; c += blockDim.x * 4) {
-        const float4 v = *reinterpret_cast<const float4*>(xr + c);
-        ss = fmaf(v.x, v.x, ss);
-        ss = fmaf(v.y, v.y, ss);
-        ss = fmaf(v.z, v.z, ss);
-        ss = fmaf(v.w, v.w, ss);
-    }
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-    if (threadIdx.x % 32 == 0) partial[threadIdx.x / 32] = ss;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        float t = threadIdx.x < blockDim.x / 32 ? partial[threadIdx.x] : 0.0f;
-        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
-        if (threadIdx.x == 0) partial[0] = t;
-    }
-    __syncthreads();
-    const float inv = rsqrtf(partial[0] / static_cast<float>(cols) + eps);
-    for (std::size_t c = threadIdx.x * 4; c < cols; c += blockDim.x * 4) {
-        const float4 v = *reinterpret_cast<const float4*>(xr + c);
-        const float4 g = *reinterpret_cast<const float4*>(w + c);
-        const __half2 lo = __floats2half2_rn(__fmul_rn(__fmul_rn(v.x, inv), 1.0f + g.x), __fmul_rn(__fmul_rn(v.y, inv), 1.0f + g.y));
-        const __half2 hi = __floats2half2_rn(__fmul_rn(__fmul_rn(v.z, inv), 1.0f + g.z), __fmul_rn(__fmul_rn(v.w, inv), 1.0f + g.w));
-        uint2 packed;
-        packed.x = *reinterpret_cast<const unsigned*>(&lo);
-        packed.y = *reinterpret_cast<const unsigned*>(&hi);
-        *reinterpret_cast<uint2*>(yr + c) = packed;
-    }
+    norm_row([&](std::size_t c) { return *reinterpret_cast<const float4*>(xr + 4 * c); }, w, y + static_cast<std::size_t>(blockIdx.x) * ld_y, cols, eps);
+}
+
+// The embedding gather and the first layer's input norm in one pass (the reference runs launch_embed and launch_rms_norm back to back,
+// runner/cuda/src/cuda_engine.cpp:1676-1692): the row of the binary16 table is widened (exactly) to the float32 stream and normed from
+// the registers (a row wider than the registers hold is widened a second time for the second pass).
+__global__ void __launch_bounds__(kNormThreads) embed_rms_norm_half_kernel(const __half* table, const std::uint32_t* tokens, float* x, const float* w, __half* y,
+                                                                            std::size_t ld_y, std::size_t hidden, std::size_t vocab, float eps) {
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();  // the kernel before this one may still read the rows this one overwrites
+    std::size_t id = tokens[blockIdx.x];
+    if (id >= vocab) id = vocab - 1;  // the host checks the ids; never read outside the table
+    const __half* src = table + id * hidden;
+    float* xr = x + static_cast<std::size_t>(blockIdx.x) * hidden;
+    norm_row(
+        [&](std::size_t c) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(src + 4 * c);
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+            const float4 v = make_float4(a.x, a.y, b.x, b.y);
+            *reinterpret_cast<float4*>(xr + 4 * c) = v;  // written twice with the same value when the row is wider than the registers hold
+            return v;
+        },
+        w, y + static_cast<std::size_t>(blockIdx.x) * ld_y, hidden, eps);
 }
 
 unsigned blocks_for(std::size_t n, unsigned per) { return static_cast<unsigned>((n + per - 1) / per); }
@@ -107,11 +160,20 @@ void launch_embed(const void* table_half, const std::uint32_t* tokens, float* x,
     count_launch();
 }
 
+void launch_embed_rms_norm_half(const void* table_half, const std::uint32_t* tokens, float* x, const float* w, void* y_half, std::size_t ld_y, std::size_t rows,
+                                std::size_t hidden, std::size_t vocab, float eps, cudaStream_t stream) {
+    if (hidden % 8 != 0 || ld_y % 4 != 0) throw std::invalid_argument("launch_embed_rms_norm_half: the hidden size must be a multiple of 8 and the stride of y of 4");
+    if (rows == 0) return;
+    launch_kernel(embed_rms_norm_half_kernel, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, stream, "embed_rms_norm_half_kernel launch",
+                  static_cast<const __half*>(table_half), tokens, x, w, static_cast<__half*>(y_half), ld_y, hidden, vocab, eps);
+    count_launch();
+}
+
 void launch_rms_norm_half(const float* x, std::size_t ld_x, const float* w, void* y_half, std::size_t ld_y, std::size_t rows, std::size_t cols, float eps,
                           cudaStream_t stream) {
     if (cols % 4 != 0 || ld_x % 4 != 0 || ld_y % 4 != 0) throw std::invalid_argument("launch_rms_norm_half: columns and strides must be multiples of 4");
     if (rows == 0) return;
-    launch_kernel(rms_norm_half_kernel, dim3(static_cast<unsigned>(rows)), dim3(256), 0, stream, "rms_norm_half_kernel launch", x, ld_x, w,
+    launch_kernel(rms_norm_half_kernel, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, stream, "rms_norm_half_kernel launch", x, ld_x, w,
                   static_cast<__half*>(y_half), ld_y, cols, eps);
     count_launch();
 }
@@ -247,9 +309,13 @@ std::uint64_t Trunk::gemm_flops_per_token() const {
 void Trunk::forward_call(const std::uint32_t* tokens_dev, std::size_t rows) {
     const TrunkConfig& c = cfg_;
     const std::size_t H = c.hidden, I = c.intermediate;
-    launch_embed(embedding_, tokens_dev, x_, rows, H, c.vocab, stream_);
+    if (layers_.empty()) {
+        launch_embed(embedding_, tokens_dev, x_, rows, H, c.vocab, stream_);
+        return;
+    }
+    launch_embed_rms_norm_half(embedding_, tokens_dev, x_, layers_.front().norm_in, a1_, H, rows, H, c.vocab, c.eps, stream_);
     for (const Layer& L : layers_) {
-        launch_rms_norm_half(x_, H, L.norm_in, a1_, H, rows, H, c.eps, stream_);
+        if (&L != &layers_.front()) launch_rms_norm_half(x_, H, L.norm_in, a1_, H, rows, H, c.eps, stream_);
         launch_gemm_f16(ctx_, a1_, H, L.mix_in, H, p_, p_width_, true, rows, L.mix_in_n, H, Epilogue::Store, -1, stream_);
         const __half* band = static_cast<const __half*>(p_) + L.band;
         launch_gemm_f16(ctx_, band, p_width_, L.mix_out, L.mix_out_k, x_, H, false, rows, H, L.mix_out_k, Epilogue::Add, -1, stream_);

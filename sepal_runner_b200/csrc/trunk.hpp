@@ -104,6 +104,9 @@ private:
 /// Element-wise kernels of the trunk (also used by tests): token embedding gather and the zero-centred RMSNorm of the reference
 /// (y = x / sqrt(mean(x^2) + eps) * (1 + w), runner/cuda/src/kernels_elementwise.hpp:41-46), float32 in, binary16 out.
 void launch_embed(const void* table_half, const std::uint32_t* tokens, float* x, std::size_t rows, std::size_t hidden, std::size_t vocab, cudaStream_t stream);
+/// Both at once for the first layer: x[t, :] = table[tokens[t], :] widened, y = norm(x) with the weight w, one pass over the row.
+void launch_embed_rms_norm_half(const void* table_half, const std::uint32_t* tokens, float* x, const float* w, void* y_half, std::size_t ld_y, std::size_t rows,
+                                std::size_t hidden, std::size_t vocab, float eps, cudaStream_t stream);
 void launch_rms_norm_half(const float* x, std::size_t ld_x, const float* w, void* y_half, std::size_t ld_y, std::size_t rows, std::size_t cols, float eps,
                           cudaStream_t stream);
 /// Normal(0, stddev) values from a counter-based generator (seed, element index), rounded to bfloat16 and stored as binary16 / float32.

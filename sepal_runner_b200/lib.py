@@ -50,6 +50,7 @@ SIGNATURES = {
     "sepal_b200_float_to_half": (_i32, [_vp, _vp, _u64, _vp]),
     "sepal_b200_half_to_float": (_i32, [_vp, _vp, _u64, _vp]),
     "sepal_b200_embed": (_i32, [_vp, _vp, _vp, _u64, _u64, _u64, _vp]),
+    "sepal_b200_embed_rms_norm_half": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64, C.c_float, _vp]),
     "sepal_b200_rms_norm_half": (_i32, [_vp, _u64, _vp, _vp, _u64, _u64, _u64, C.c_float, _vp]),
     "sepal_b200_trunk_open": (_i32, [_i32, _vp, C.POINTER(_vp)]),
     "sepal_b200_trunk_close": (None, [_vp]),

@@ -69,6 +69,22 @@ def test_rmsnorm(oracle, golden):
     assert np.allclose(got, golden["rn_y"], rtol=2e-6, atol=1e-7)
 
 
+def test_ordered_rmsnorm_agrees_with_the_float64_form(oracle):
+    """The float32 chain in the reference kernel's order against the float64 mean: a few units in the last place, never more."""
+    rng = np.random.default_rng(41)
+    for cols in (4, 256, 1024, 2560, 4100):
+        x = (rng.standard_normal((5, cols)) * 3).astype(np.float32)
+        w = (rng.standard_normal(cols) * 0.1).astype(np.float32)
+        got = oracle.rmsnorm_ordered(x, w, 1e-6)
+        want = oracle.rmsnorm(x, w, 1e-6)
+        assert np.abs(got - want).max() <= 4e-6 * np.abs(want).max()
+    one = np.zeros((1, 8), np.float32)
+    one[0, :4] = [3.0, 4.0, 0.0, 0.0]                    # sum of squares 25, mean 25 / 8, exactly representable steps
+    y = oracle.rmsnorm_ordered(one, np.zeros(8, np.float32), 0.0)
+    rms = np.sqrt(np.float32(25.0) / np.float32(8.0))
+    assert y[0, 0] == np.float32(3.0) / rms and y[0, 1] == np.float32(4.0) / rms and y[0, 2] == 0.0
+
+
 def test_bf16_rounding(oracle, golden):
     got = np.array([oracle.lib.oracle_f32_to_bf16(float(v)) for v in golden["bf_vals"]], np.uint16)
     assert np.array_equal(got, golden["bf_bits"])

@@ -187,9 +187,61 @@ typedef struct sepal_b200_trunk_config {
     uint32_t mlp_int8;                    /* 1: gate_up and down stored as int8 groups */
     float eps;
     uint64_t seed;
+    uint32_t attn_o;                      /* width the attention out-projection reads; 0: attn_q (a real q_proj also carries the output gate) */
+    uint32_t reserved;
 } sepal_b200_trunk_config;
 SEPAL_B200_API int32_t sepal_b200_trunk_open(int32_t device, const sepal_b200_trunk_config* config, sepal_b200_trunk** out);
 SEPAL_B200_API void sepal_b200_trunk_close(sepal_b200_trunk* trunk);
+
+/* ---- checkpoints and weight placement (the data format on the input side of the path) ----------------------------------------------
+ *
+ * The reader of the safetensors format (runner/include/sepal/safetensors.hpp:1-154) and of checkpoint directories with their name
+ * prefixes (runner/include/sepal/loader.hpp:5-8): a file is mapped read-only and checked once (every tensor inside the file, of the size
+ * its shape and type imply, aligned, overlapping no other); `path` is one file or a directory with model.safetensors or the shards
+ * model-0000i-of-0000N.safetensors. Tensors are addressed by their engine names (the prefix dropped), in sorted order by index. */
+typedef struct sepal_b200_checkpoint sepal_b200_checkpoint;
+typedef struct sepal_b200_tensor_info {
+    char name[256];
+    int32_t dtype;      /* 0 F32, 1 F16, 2 BF16, 3 I8, 4 U8, 5 I32, 6 I64, 7 F64, 8 BOOL, 9 I16, 10 U16, 11 U32, 12 U64 */
+    uint32_t rank;
+    uint64_t shape[8];
+    const void* data;   /* host; valid while the checkpoint is open (for sepal_b200_tensor_file_write: the values to write) */
+    uint64_t bytes;
+} sepal_b200_tensor_info;
+SEPAL_B200_API int32_t sepal_b200_checkpoint_open(const char* path, sepal_b200_checkpoint** out);
+SEPAL_B200_API void sepal_b200_checkpoint_close(sepal_b200_checkpoint* checkpoint);
+SEPAL_B200_API int32_t sepal_b200_checkpoint_count(const sepal_b200_checkpoint* checkpoint, uint64_t* count);
+/* By name when name is not NULL, else by index. */
+SEPAL_B200_API int32_t sepal_b200_checkpoint_tensor(const sepal_b200_checkpoint* checkpoint, uint64_t index, const char* name, sepal_b200_tensor_info* info);
+/* A "__metadata__" value ("" when absent; the key "__prefix__" yields the name prefix that was dropped); size-query protocol. */
+SEPAL_B200_API int32_t sepal_b200_checkpoint_metadata(const sepal_b200_checkpoint* checkpoint, const char* key, char* buffer, uint64_t capacity,
+                                                      uint64_t* needed);
+/* Writes a file of the same format (name, dtype, rank, shape, data of each tensor are read; tensors are stored in the order given, the
+ * first on a 256-byte boundary of the file). */
+SEPAL_B200_API int32_t sepal_b200_tensor_file_write(const char* path, uint64_t n, const sepal_b200_tensor_info* tensors, uint64_t n_metadata,
+                                                    const char* const* keys, const char* const* values);
+
+/* The trunk with the weights of a checkpoint instead of random ones: the reference's placement (runner/cuda/src/cuda_engine.cpp:525-711)
+ * for the projections this path has: [q; k; v] and [qkv; z; b; a] stacked, everything converted to binary16 (norms float32), [gate; up]
+ * interleaved in blocks of 64 rows, the MLP quantised per group of 128 from a float32 copy when mlp_int8 is set. The configuration must
+ * agree with the tensors' shapes (attn_q = rows of q_proj, attn_o = columns of o_proj, dn_in = rows of the four in-projections together).
+ * A file written by sepal_b200_trunk_save (metadata format = "sepal_b200.placed.1") is copied to the device as it is. */
+SEPAL_B200_API int32_t sepal_b200_trunk_open_checkpoint(int32_t device, const sepal_b200_trunk_config* config, const sepal_b200_checkpoint* checkpoint,
+                                                        sepal_b200_trunk** out);
+/* Writes the placed weights (stacked, interleaved, quantised: int8 values and their float32 group scales) to one file. */
+SEPAL_B200_API int32_t sepal_b200_trunk_save(sepal_b200_trunk* trunk, const char* path);
+
+/* The planner's byte accounting of the trunk weights (runner/src/plan/planner.cpp:45-130, runner/src/core/config.cpp:156-188): the bytes
+ * every parameter but the embedding table and the head takes under a storage profile ("w16", "w8", "gpu-f16", "gpu-q8w", "cpu-q8",
+ * "gpu-bf16", "gpu-w8g"); per-group scales are counted, per-row scales are not. Presets: "0.8b", "2b", "4b", "9b". Host arithmetic only. */
+typedef struct sepal_b200_model {
+    uint64_t layers, hidden, intermediate, vocab;
+    uint64_t attn_heads, attn_kv_heads, attn_head_dim;
+    uint64_t dn_key_heads, dn_value_heads, dn_key_head_dim, dn_value_head_dim, conv_kernel;
+    uint64_t attention_interval;
+} sepal_b200_model;
+SEPAL_B200_API int32_t sepal_b200_model_preset(const char* name, sepal_b200_model* out);
+SEPAL_B200_API int32_t sepal_b200_plan_weight_bytes(const sepal_b200_model* model, const char* profile, uint64_t* bytes);
 /* One request of n host token ids. last_hidden: `hidden` floats (host) for the last token's final hidden state; all_hidden: NULL or
  * [n, hidden] floats (host). times_ms: NULL or 2 doubles (device time of the request by CUDA events; reserved). Returns when done. */
 SEPAL_B200_API int32_t sepal_b200_trunk_run(sepal_b200_trunk* trunk, const uint32_t* tokens, uint64_t n, float* last_hidden, float* all_hidden,

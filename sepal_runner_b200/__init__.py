@@ -6,6 +6,9 @@ There is no CPU path: loading fails loudly when the library is missing, and `Con
 """
 from .lib import (  # noqa: F401
     ADD,
+    BF16,
+    Checkpoint,
+    Model,
     STORE,
     SWIGLU,
     Context,
@@ -17,4 +20,5 @@ from .lib import (  # noqa: F401
     library,
     library_path,
     pack_gate_up_source,
+    write_tensor_file,
 )

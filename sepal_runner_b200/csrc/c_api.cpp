@@ -5,9 +5,16 @@
 #include <cstring>
 #include <exception>
 #include <new>
+#include <map>
+#include <memory>
+#include <optional>
+#include <stdexcept>
 #include <string>
+#include <vector>
 
+#include "checkpoint.hpp"
 #include "gemm.hpp"
+#include "model.hpp"
 #include "provider.hpp"
 #include "trunk.hpp"
 
@@ -24,7 +31,7 @@ struct sepal_b200_provider {
 
 struct sepal_b200_trunk {
     Trunk trunk;
-    sepal_b200_trunk(int device, const TrunkConfig& c) : trunk(device, c) {}
+    sepal_b200_trunk(int device, const TrunkConfig& c, const Checkpoint* checkpoint) : trunk(device, c, checkpoint) {}
 };
 
 namespace {
@@ -218,28 +225,175 @@ int32_t sepal_b200_rms_norm_half(const float* x, uint64_t ld_x, const float* w, 
     });
 }
 
+namespace {
+TrunkConfig trunk_config_of(const sepal_b200_trunk_config& config) {
+    TrunkConfig c;
+    c.layers = config.layers;
+    c.hidden = config.hidden;
+    c.intermediate = config.intermediate;
+    c.vocab = config.vocab;
+    c.attn_q = config.attn_q;
+    c.attn_kv = config.attn_kv;
+    c.dn_in = config.dn_in;
+    c.dn_v_offset = config.dn_v_offset;
+    c.dn_v = config.dn_v;
+    c.max_call_tokens = config.max_call_tokens;
+    c.mlp_int8 = config.mlp_int8;
+    c.eps = config.eps;
+    c.seed = config.seed;
+    c.attn_o = config.attn_o;
+    return c;
+}
+}  // namespace
+
+struct sepal_b200_checkpoint {
+    std::shared_ptr<const Checkpoint> checkpoint;
+    std::vector<std::string> names;  // engine names, sorted
+};
+
 int32_t sepal_b200_trunk_open(int32_t device, const sepal_b200_trunk_config* config, sepal_b200_trunk** out) {
     if (out != nullptr) *out = nullptr;
     return guarded([&] {
         require(out, "out");
         require(config, "config");
-        TrunkConfig c;
-        c.layers = config->layers;
-        c.hidden = config->hidden;
-        c.intermediate = config->intermediate;
-        c.vocab = config->vocab;
-        c.attn_q = config->attn_q;
-        c.attn_kv = config->attn_kv;
-        c.dn_in = config->dn_in;
-        c.dn_v_offset = config->dn_v_offset;
-        c.dn_v = config->dn_v;
-        c.max_call_tokens = config->max_call_tokens;
-        c.mlp_int8 = config->mlp_int8;
-        c.eps = config->eps;
-        c.seed = config->seed;
-        *out = new sepal_b200_trunk(device, c);
+        *out = new sepal_b200_trunk(device, trunk_config_of(*config), nullptr);
     });
 }
+int32_t sepal_b200_trunk_open_checkpoint(int32_t device, const sepal_b200_trunk_config* config, const sepal_b200_checkpoint* checkpoint,
+                                         sepal_b200_trunk** out) {
+    if (out != nullptr) *out = nullptr;
+    return guarded([&] {
+        require(out, "out");
+        require(config, "config");
+        require(checkpoint, "checkpoint");
+        *out = new sepal_b200_trunk(device, trunk_config_of(*config), checkpoint->checkpoint.get());
+    });
+}
+int32_t sepal_b200_trunk_save(sepal_b200_trunk* trunk, const char* path) {
+    return guarded([&] {
+        require(trunk, "trunk");
+        require(path, "path");
+        trunk->trunk.save(path);
+    });
+}
+
+int32_t sepal_b200_checkpoint_open(const char* path, sepal_b200_checkpoint** out) {
+    if (out != nullptr) *out = nullptr;
+    return guarded([&] {
+        require(out, "out");
+        require(path, "path");
+        auto handle = std::make_unique<sepal_b200_checkpoint>();
+        handle->checkpoint = Checkpoint::open(path);
+        handle->names = handle->checkpoint->names();
+        *out = handle.release();
+    });
+}
+void sepal_b200_checkpoint_close(sepal_b200_checkpoint* checkpoint) { delete checkpoint; }
+int32_t sepal_b200_checkpoint_count(const sepal_b200_checkpoint* checkpoint, uint64_t* count) {
+    return guarded([&] {
+        require(checkpoint, "checkpoint");
+        require(count, "count");
+        *count = checkpoint->names.size();
+    });
+}
+int32_t sepal_b200_checkpoint_tensor(const sepal_b200_checkpoint* checkpoint, uint64_t index, const char* name, sepal_b200_tensor_info* info) {
+    return guarded([&] {
+        require(checkpoint, "checkpoint");
+        require(info, "info");
+        const TensorView* t = nullptr;
+        if (name != nullptr) {
+            t = &checkpoint->checkpoint->at(name);
+        } else {
+            if (index >= checkpoint->names.size()) throw std::out_of_range("the checkpoint has " + std::to_string(checkpoint->names.size()) + " tensors");
+            t = &checkpoint->checkpoint->at(checkpoint->names[index]);
+        }
+        if (t->shape.size() > 8) throw std::length_error("tensor '" + t->name + "' has more than 8 dimensions");
+        std::memset(info, 0, sizeof *info);
+        const std::string& prefix = checkpoint->checkpoint->prefix();
+        const std::string engine_name = t->name.compare(0, prefix.size(), prefix) == 0 ? t->name.substr(prefix.size()) : t->name;
+        std::strncpy(info->name, engine_name.c_str(), sizeof info->name - 1);
+        info->dtype = static_cast<int32_t>(t->type);
+        info->rank = static_cast<uint32_t>(t->shape.size());
+        for (std::size_t d = 0; d < t->shape.size(); ++d) info->shape[d] = t->shape[d];
+        info->data = t->data;
+        info->bytes = t->bytes;
+    });
+}
+int32_t sepal_b200_checkpoint_metadata(const sepal_b200_checkpoint* checkpoint, const char* key, char* buffer, uint64_t capacity, uint64_t* needed) {
+    return guarded([&] {
+        require(checkpoint, "checkpoint");
+        require(key, "key");
+        const std::string value = std::string(key) == "__prefix__" ? checkpoint->checkpoint->prefix() : checkpoint->checkpoint->metadata(key);
+        if (needed != nullptr) *needed = value.size() + 1;
+        if (buffer != nullptr) {
+            if (capacity < value.size() + 1) throw std::length_error("buffer too small: " + std::to_string(value.size() + 1) + " bytes needed");
+            std::memcpy(buffer, value.c_str(), value.size() + 1);
+        }
+    });
+}
+int32_t sepal_b200_tensor_file_write(const char* path, uint64_t n, const sepal_b200_tensor_info* tensors, uint64_t n_metadata, const char* const* keys,
+                                     const char* const* values) {
+    return guarded([&] {
+        require(path, "path");
+        if (n != 0) require(tensors, "tensors");
+        std::vector<TensorToWrite> out;
+        for (uint64_t i = 0; i < n; ++i) {
+            const sepal_b200_tensor_info& t = tensors[i];
+            if (t.rank > 8 || t.dtype < 0 || t.dtype > 12) throw std::invalid_argument("tensor " + std::to_string(i) + ": bad rank or element type");
+            out.push_back(TensorToWrite{std::string(t.name), static_cast<ElementType>(t.dtype), std::vector<std::uint64_t>(t.shape, t.shape + t.rank), t.data});
+        }
+        std::map<std::string, std::string> meta;
+        for (uint64_t i = 0; i < n_metadata; ++i) meta[keys[i]] = values[i];
+        write_tensor_file(path, out, meta);
+    });
+}
+
+int32_t sepal_b200_model_preset(const char* name, sepal_b200_model* out) {
+    return guarded([&] {
+        require(name, "name");
+        require(out, "out");
+        const std::optional<ModelGeometry> g = find_model(name);
+        if (!g) throw std::invalid_argument(std::string("no model preset '") + name + "' (0.8b, 2b, 4b, 9b)");
+        out->layers = g->layers;
+        out->hidden = g->hidden;
+        out->intermediate = g->intermediate;
+        out->vocab = g->vocab;
+        out->attn_heads = g->attn_heads;
+        out->attn_kv_heads = g->attn_kv_heads;
+        out->attn_head_dim = g->attn_head_dim;
+        out->dn_key_heads = g->dn_key_heads;
+        out->dn_value_heads = g->dn_value_heads;
+        out->dn_key_head_dim = g->dn_key_head_dim;
+        out->dn_value_head_dim = g->dn_value_head_dim;
+        out->conv_kernel = g->conv_kernel;
+        out->attention_interval = g->attention_interval;
+    });
+}
+int32_t sepal_b200_plan_weight_bytes(const sepal_b200_model* model, const char* profile, uint64_t* bytes) {
+    return guarded([&] {
+        require(model, "model");
+        require(profile, "profile");
+        require(bytes, "bytes");
+        const std::optional<StorageProfile> p = find_profile(profile);
+        if (!p) throw std::invalid_argument(std::string("no storage profile '") + profile + "' (w16, w8, gpu-f16, gpu-q8w, cpu-q8, gpu-bf16, gpu-w8g)");
+        ModelGeometry g;
+        g.layers = model->layers;
+        g.hidden = model->hidden;
+        g.intermediate = model->intermediate;
+        g.vocab = model->vocab;
+        g.attn_heads = model->attn_heads;
+        g.attn_kv_heads = model->attn_kv_heads;
+        g.attn_head_dim = model->attn_head_dim;
+        g.dn_key_heads = model->dn_key_heads;
+        g.dn_value_heads = model->dn_value_heads;
+        g.dn_key_head_dim = model->dn_key_head_dim;
+        g.dn_value_head_dim = model->dn_value_head_dim;
+        g.conv_kernel = model->conv_kernel;
+        g.attention_interval = model->attention_interval;
+        *bytes = trunk_weight_bytes(g, *p);
+    });
+}
+
 void sepal_b200_trunk_close(sepal_b200_trunk* trunk) { delete trunk; }
 int32_t sepal_b200_trunk_run(sepal_b200_trunk* trunk, const uint32_t* tokens, uint64_t n, float* last_hidden, float* all_hidden, double* times_ms) {
     return guarded([&] {

@@ -191,6 +191,15 @@ void launch_fill_normal_float(float* dst, std::size_t count, std::uint64_t seed,
     count_launch();
 }
 
+void Trunk::shape_layer(std::uint32_t l) {
+    const TrunkConfig& c = cfg_;
+    Layer& L = layers_[l];
+    L.attention = l % 4 == 3;
+    L.mix_in_n = static_cast<std::uint32_t>(L.attention ? c.attn_q + 2 * c.attn_kv : c.dn_in);
+    L.mix_out_k = L.attention ? c.attn_o : c.dn_v;
+    L.band = L.attention ? 0u : c.dn_v_offset;
+}
+
 void* Trunk::alloc(std::size_t bytes) {
     void* p = nullptr;
     check(cudaMalloc(&p, bytes), "cudaMalloc(trunk)");
@@ -198,82 +207,28 @@ void* Trunk::alloc(std::size_t bytes) {
     return p;
 }
 
-Trunk::Trunk(int device, const TrunkConfig& config) : cfg_(config), ctx_(device, 0) {
-    const TrunkConfig& c = cfg_;
-    if (c.layers == 0 || c.hidden % 128 != 0 || c.intermediate % 128 != 0 || c.attn_q % 128 != 0 || c.attn_kv % 8 != 0 || c.dn_in % 8 != 0 ||
-        c.dn_v % 128 != 0 || c.dn_v_offset % 8 != 0 || c.dn_v_offset + c.dn_v > c.dn_in || c.max_call_tokens == 0 || c.vocab == 0)
-        throw std::invalid_argument("sepal_b200 trunk: widths must be multiples of 128 (k and v, the fused in-projection: of 8), the v band inside "
-                                    "the in-projection, and layers, vocabulary and call size non-zero");
+Trunk::Trunk(int device, const TrunkConfig& config, const Checkpoint* checkpoint) : cfg_(config), ctx_(device, 0) {
+    TrunkConfig& c = cfg_;
+    if (c.attn_o == 0) c.attn_o = c.attn_q;
+    if (c.layers == 0 || c.hidden % 128 != 0 || c.intermediate % 128 != 0 || c.attn_q % 128 != 0 || c.attn_o % 128 != 0 || c.attn_kv % 8 != 0 ||
+        c.dn_in % 8 != 0 || c.dn_v % 128 != 0 || c.dn_v_offset % 8 != 0 || c.dn_v_offset + c.dn_v > c.dn_in || c.attn_o > c.attn_q + 2 * c.attn_kv ||
+        c.max_call_tokens == 0 || c.vocab == 0)
+        throw std::invalid_argument("sepal_b200 trunk: widths must be multiples of 128 (k and v, the fused in-projection: of 8), the bands the "
+                                    "out-projections read inside the in-projections, and layers, vocabulary and call size non-zero");
     check(cudaSetDevice(device), "cudaSetDevice");
     check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
     for (auto& e : ev_) check(cudaEventCreate(&e), "cudaEventCreate");
     const std::size_t H = c.hidden, I = c.intermediate, T = c.max_call_tokens;
     const std::size_t attn_in = c.attn_q + 2 * static_cast<std::size_t>(c.attn_kv);
     p_width_ = static_cast<std::uint32_t>(attn_in > c.dn_in ? attn_in : c.dn_in);
-    std::uint64_t stream_seed = c.seed * 1000003ull;
-    const auto fill_half = [&](void* dst, std::size_t count) { launch_fill_normal_half(dst, count, ++stream_seed, 0.02f, stream_); };
-
-    embedding_ = alloc(static_cast<std::size_t>(c.vocab) * H * 2);
-    fill_half(embedding_, static_cast<std::size_t>(c.vocab) * H);
-    weight_bytes_ += static_cast<std::size_t>(c.vocab) * H * 2;
-
-    // scratch for building the MLP weights: the stacked [gate; up] before packing, and float32 copies for the quantiser
-    void* stacked = alloc(2 * I * H * 2);
-    float* wide = c.mlp_int8 ? static_cast<float*>(alloc(2 * I * H * 4)) : nullptr;
-    float* scales = c.mlp_int8 ? static_cast<float*>(alloc(2 * I * (H / kGroup + I / kGroup + 2) * 4)) : nullptr;
-    void* packed = c.mlp_int8 ? alloc(2 * I * H * 2) : nullptr;
-
     layers_.resize(c.layers);
-    for (std::uint32_t l = 0; l < c.layers; ++l) {
-        Layer& L = layers_[l];
-        L.attention = l % 4 == 3;
-        L.mix_in_n = static_cast<std::uint32_t>(L.attention ? attn_in : c.dn_in);
-        L.mix_out_k = L.attention ? c.attn_q : c.dn_v;
-        L.band = L.attention ? 0u : c.dn_v_offset;
-        L.norm_in = static_cast<float*>(alloc(H * 4));
-        L.norm_post = static_cast<float*>(alloc(H * 4));
-        launch_fill_normal_float(L.norm_in, H, ++stream_seed, 0.02f, stream_);
-        launch_fill_normal_float(L.norm_post, H, ++stream_seed, 0.02f, stream_);
-        L.mix_in = alloc(static_cast<std::size_t>(L.mix_in_n) * H * 2);
-        fill_half(L.mix_in, static_cast<std::size_t>(L.mix_in_n) * H);
-        L.mix_out = alloc(H * static_cast<std::size_t>(L.mix_out_k) * 2);
-        fill_half(L.mix_out, H * static_cast<std::size_t>(L.mix_out_k));
-        weight_bytes_ += (static_cast<std::size_t>(L.mix_in_n) * H + H * static_cast<std::size_t>(L.mix_out_k)) * 2 + 2 * H * 4;
-        fill_half(stacked, 2 * I * H);  // rows 0 .. I-1 gate, I .. 2I-1 up
-        if (!c.mlp_int8) {
-            L.gate_up = alloc(2 * I * H * 2);
-            launch_pack_gate_up(stacked, H * 2, L.gate_up, H * 2, I, H * 2, stream_);
-            L.down = alloc(H * I * 2);
-            fill_half(L.down, H * I);
-            weight_bytes_ += (2 * I * H + H * I) * 2;
-        } else {
-            // pack in binary16, widen, quantise per group of 128, prepare the scales (the placement of runner/cuda/src/cuda_engine.cpp:580-627)
-            launch_pack_gate_up(stacked, H * 2, packed, H * 2, I, H * 2, stream_);
-            launch_half_to_float(packed, wide, 2 * I * H, stream_);
-            std::int8_t* q = static_cast<std::int8_t*>(alloc(2 * I * H));
-            launch_quantize_group_s8(wide, H, q, H, scales, H / kGroup, 2 * I, H, stream_);
-            const std::size_t ld_st = (2 * I + 255) / 256 * 256;
-            void* st = alloc((H / kGroup) * ld_st * 2);
-            check(cudaMemsetAsync(st, 0, (H / kGroup) * ld_st * 2, stream_), "cudaMemsetAsync");
-            float* ds = static_cast<float*>(alloc(8));
-            launch_prepare_w8g_scales(scales, H / kGroup, 2 * I, H / kGroup, st, ld_st, ds, reinterpret_cast<unsigned*>(ds + 1), stream_);
-            L.gate_up_q = W8gMatrix{q, H, st, ld_st, ds};
-            L.gate_up = q;
-            // down: [H, I]
-            fill_half(stacked, H * I);
-            launch_half_to_float(stacked, wide, H * I, stream_);
-            std::int8_t* qd = static_cast<std::int8_t*>(alloc(H * I));
-            launch_quantize_group_s8(wide, I, qd, I, scales, I / kGroup, H, I, stream_);
-            const std::size_t ld_sd = (H + 255) / 256 * 256;
-            void* sd = alloc((I / kGroup) * ld_sd * 2);
-            check(cudaMemsetAsync(sd, 0, (I / kGroup) * ld_sd * 2, stream_), "cudaMemsetAsync");
-            float* dd = static_cast<float*>(alloc(8));
-            launch_prepare_w8g_scales(scales, I / kGroup, H, I / kGroup, sd, ld_sd, dd, reinterpret_cast<unsigned*>(dd + 1), stream_);
-            L.down_q = W8gMatrix{qd, I, sd, ld_sd, dd};
-            L.down = qd;
-            weight_bytes_ += 2 * I * H + H * I + ((H / kGroup) * ld_st + (I / kGroup) * ld_sd) * 2;
-        }
-    }
+    for (std::uint32_t l = 0; l < c.layers; ++l) shape_layer(l);
+    if (checkpoint == nullptr)
+        place_random();
+    else if (checkpoint->metadata("format") == kSavedFormat)
+        place_saved(*checkpoint);
+    else
+        place_checkpoint(*checkpoint);
     x_ = static_cast<float*>(alloc(T * H * 4));
     a1_ = alloc(T * H * 2);
     p_ = alloc(T * static_cast<std::size_t>(p_width_) * 2);

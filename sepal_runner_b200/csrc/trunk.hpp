@@ -21,6 +21,8 @@
 
 #include <cuda_runtime.h>
 
+#include "checkpoint.hpp"
+
 #include "gemm.hpp"
 
 namespace sepal::b200 {
@@ -33,13 +35,22 @@ struct TrunkConfig {
     std::uint32_t mlp_int8 = 0;                             // 1: gate_up and down stored as int8 groups
     float eps = 1e-6f;
     std::uint64_t seed = 1;
+    std::uint32_t attn_o = 0;                               // width the attention out-projection reads (0: attn_q); q_proj may carry a gate
+    std::uint32_t reserved = 0;
 };
+
+/// The value of the "format" metadata key of a file written by Trunk::save.
+extern const char* const kSavedFormat;
 
 enum class TrunkWeight : int { Embedding = 0, NormIn = 1, MixIn = 2, MixOut = 3, NormPost = 4, GateUp = 5, Down = 6 };
 
 class Trunk {
 public:
-    Trunk(int device, const TrunkConfig& config);
+    /// Random weights (N(0, 0.02) on the bfloat16 grid, from config.seed), or, with a checkpoint, the weights it holds: either the
+    /// reference's tensor names (embed_tokens.weight, layers.N.input_layernorm.weight, ...self_attn.{q,k,v,o}_proj.weight,
+    /// ...linear_attn.{in_proj_qkv,in_proj_z,in_proj_b,in_proj_a,out_proj}.weight, ...mlp.{gate,up,down}_proj.weight), stacked, converted,
+    /// interleaved and quantised as the reference's placement does (runner/cuda/src/cuda_engine.cpp:525-711), or a file written by save().
+    Trunk(int device, const TrunkConfig& config, const Checkpoint* checkpoint = nullptr);
     ~Trunk();
     Trunk(const Trunk&) = delete;
     Trunk& operator=(const Trunk&) = delete;
@@ -59,6 +70,10 @@ public:
     static constexpr std::size_t kMaxCallRows = 64;
     void score(std::size_t n_requests, const std::uint32_t* tokens, const std::uint64_t* offsets, float* last_hidden, double* times_s);
 
+    /// Writes the weights as they are placed on the device (stacked, interleaved, quantised) to one file in the checkpoint format, so
+    /// that the next start copies them to the device as they are. Tensors start on 256-byte boundaries of the file.
+    void save(const std::string& path);
+
     /// A weight as stored (binary16, or float32 for the norms), copied to the host: for parity checks. Returns the byte size.
     std::size_t weight(std::uint32_t layer, TrunkWeight which, void* host_out, std::size_t capacity);
 
@@ -77,8 +92,15 @@ private:
         void* gate_up = nullptr;  // binary16 packed [2 I, hidden] (mlp_int8: int8)
         void* down = nullptr;     // binary16 [hidden, I] (mlp_int8: int8)
         W8gMatrix gate_up_q, down_q;
+        float* gate_up_scales = nullptr;  // mlp_int8: the quantiser's float32 scales [2 I, hidden / 128] and [hidden, I / 128]
+        float* down_scales = nullptr;
     };
     void* alloc(std::size_t bytes);
+    void place_random();
+    void place_checkpoint(const Checkpoint& checkpoint);
+    void place_saved(const Checkpoint& checkpoint);
+    void shape_layer(std::uint32_t l);
+    void prepare_mlp_scales(Layer& L);
     void forward_call(const std::uint32_t* tokens_dev, std::size_t rows);
 
     TrunkConfig cfg_;

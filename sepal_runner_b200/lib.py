@@ -55,6 +55,16 @@ SIGNATURES = {
     "sepal_b200_trunk_open": (_i32, [_i32, _vp, C.POINTER(_vp)]),
     "sepal_b200_trunk_close": (None, [_vp]),
     "sepal_b200_set_launch_overlap": (None, [_i32]),
+    "sepal_b200_trunk_open_checkpoint": (_i32, [_i32, _vp, _vp, _vp]),
+    "sepal_b200_trunk_save": (_i32, [_vp, C.c_char_p]),
+    "sepal_b200_checkpoint_open": (_i32, [C.c_char_p, _vp]),
+    "sepal_b200_checkpoint_close": (None, [_vp]),
+    "sepal_b200_checkpoint_count": (_i32, [_vp, _vp]),
+    "sepal_b200_checkpoint_tensor": (_i32, [_vp, _u64, C.c_char_p, _vp]),
+    "sepal_b200_checkpoint_metadata": (_i32, [_vp, C.c_char_p, _vp, _u64, _vp]),
+    "sepal_b200_tensor_file_write": (_i32, [C.c_char_p, _u64, _vp, _u64, _vp, _vp]),
+    "sepal_b200_model_preset": (_i32, [C.c_char_p, _vp]),
+    "sepal_b200_plan_weight_bytes": (_i32, [_vp, C.c_char_p, _vp]),
     "sepal_b200_trunk_run": (_i32, [_vp, _vp, _u64, _vp, _vp, _vp]),
     "sepal_b200_trunk_score": (_i32, [_vp, _u64, _vp, _vp, _vp, _vp]),
     "sepal_b200_trunk_weight": (_i32, [_vp, _u32, _i32, _vp, _u64, C.POINTER(_u64)]),
@@ -274,11 +284,11 @@ class TrunkConfig(C.Structure):
 
     _fields_ = [("layers", _u32), ("hidden", _u32), ("intermediate", _u32), ("vocab", _u32), ("attn_q", _u32), ("attn_kv", _u32),
                 ("dn_in", _u32), ("dn_v_offset", _u32), ("dn_v", _u32), ("max_call_tokens", _u32), ("mlp_int8", _u32), ("eps", C.c_float),
-                ("seed", _u64)]
+                ("seed", _u64), ("attn_o", _u32), ("reserved", _u32)]
 
     def __init__(self, **kw):
         base = dict(layers=36, hidden=2560, intermediate=9728, vocab=151936, attn_q=4096, attn_kv=1024, dn_in=8192, dn_v_offset=4096, dn_v=2048,
-                    max_call_tokens=4096, mlp_int8=0, eps=1e-6, seed=1)
+                    max_call_tokens=4096, mlp_int8=0, eps=1e-6, seed=1, attn_o=0, reserved=0)
         base.update(kw)
         super().__init__(**base)
 
@@ -288,11 +298,14 @@ class Trunk:
 
     WEIGHTS = {"embedding": 0, "norm_in": 1, "mix_in": 2, "mix_out": 3, "norm_post": 4, "gate_up": 5, "down": 6}
 
-    def __init__(self, device: int = 0, config: Optional[TrunkConfig] = None) -> None:
+    def __init__(self, device: int = 0, config: Optional[TrunkConfig] = None, checkpoint: "Optional[Checkpoint]" = None) -> None:
         self._lib = library()
         self.config = config if config is not None else TrunkConfig()
         handle = _vp()
-        _check(self._lib.sepal_b200_trunk_open(device, C.addressof(self.config), C.byref(handle)))
+        if checkpoint is None:
+            _check(self._lib.sepal_b200_trunk_open(device, C.addressof(self.config), C.byref(handle)))
+        else:
+            _check(self._lib.sepal_b200_trunk_open_checkpoint(device, C.addressof(self.config), checkpoint._h, C.byref(handle)))
         self._h = handle
         flops, nbytes = _u64(), _u64()
         _check(self._lib.sepal_b200_trunk_info(self._h, C.byref(flops), C.byref(nbytes)))
@@ -309,6 +322,10 @@ class Trunk:
             self.close()
         except Exception:
             pass
+
+    def save(self, path: str) -> None:
+        """The placed weights (stacked, interleaved, quantised) as one file that Trunk(checkpoint=Checkpoint(path)) copies back as it is."""
+        _check(self._lib.sepal_b200_trunk_save(self._h, os.fsencode(path)))
 
     def run(self, tokens, want_all: bool = False):
         """tokens: uint32 numpy array. Returns (last hidden [hidden], all hidden [n, hidden] or None, device ms)."""
@@ -347,6 +364,115 @@ class Trunk:
         out = np.empty(needed.value // (4 if is_norm else 1 if int8 else 2), np.float32 if is_norm else np.int8 if int8 else np.float16)
         _check(self._lib.sepal_b200_trunk_weight(self._h, layer, code, out.ctypes.data, needed.value, C.byref(needed)))
         return out
+
+
+class TensorInfo(C.Structure):
+    """sepal_b200_tensor_info."""
+
+    _fields_ = [("name", C.c_char * 256), ("dtype", _i32), ("rank", _u32), ("shape", _u64 * 8), ("data", _vp), ("bytes", _u64)]
+
+
+# element type codes of sepal_b200_tensor_info.dtype -> numpy dtype (bfloat16 travels as its 16-bit patterns)
+ELEMENT_TYPES = {0: "float32", 1: "float16", 2: "uint16", 3: "int8", 4: "uint8", 5: "int32", 6: "int64", 7: "float64", 8: "bool", 9: "int16",
+                 10: "uint16", 11: "uint32", 12: "uint64"}
+BF16 = 2
+
+
+class Checkpoint:
+    """A safetensors file or checkpoint directory, mapped and checked (sepal_b200_checkpoint_*). Host-only: needs no GPU."""
+
+    def __init__(self, path: str) -> None:
+        self._lib = library()
+        handle = _vp()
+        _check(self._lib.sepal_b200_checkpoint_open(os.fsencode(path), C.byref(handle)))
+        self._h = handle
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.sepal_b200_checkpoint_close(self._h)
+            self._h = None
+
+    def __del__(self) -> None:  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __len__(self) -> int:
+        n = _u64()
+        _check(self._lib.sepal_b200_checkpoint_count(self._h, C.byref(n)))
+        return int(n.value)
+
+    def _info(self, index: int = 0, name: Optional[str] = None) -> TensorInfo:
+        info = TensorInfo()
+        _check(self._lib.sepal_b200_checkpoint_tensor(self._h, index, name.encode() if name is not None else None, C.byref(info)))
+        return info
+
+    def names(self):
+        return [self._info(i).name.decode() for i in range(len(self))]
+
+    def tensor(self, name: str):
+        """(numpy array copied out of the mapping, element type code)."""
+        import numpy as np
+
+        info = self._info(name=name)
+        shape = tuple(int(info.shape[d]) for d in range(info.rank))
+        dtype = np.dtype(ELEMENT_TYPES[info.dtype])
+        raw = C.string_at(info.data, info.bytes) if info.bytes else b""
+        return np.frombuffer(raw, dtype=dtype).reshape(shape).copy(), int(info.dtype)
+
+    def metadata(self, key: str) -> str:
+        needed = _u64()
+        _check(self._lib.sepal_b200_checkpoint_metadata(self._h, key.encode(), None, 0, C.byref(needed)))
+        buf = C.create_string_buffer(needed.value)
+        _check(self._lib.sepal_b200_checkpoint_metadata(self._h, key.encode(), buf, needed.value, None))
+        return buf.value.decode()
+
+    @property
+    def prefix(self) -> str:
+        return self.metadata("__prefix__")
+
+
+def write_tensor_file(path: str, tensors, metadata=None, bf16=()) -> None:
+    """tensors: dict name -> numpy array (names in `bf16` hold bfloat16 bit patterns as uint16). Written in the order of the dict."""
+    import numpy as np
+
+    codes = {"float32": 0, "float16": 1, "int8": 3, "uint8": 4, "int32": 5, "int64": 6, "float64": 7, "bool": 8, "int16": 9, "uint16": 10, "uint32": 11,
+             "uint64": 12}
+    infos = (TensorInfo * len(tensors))()
+    keep = []
+    for i, (name, value) in enumerate(tensors.items()):
+        a = np.ascontiguousarray(value)
+        keep.append(a)
+        infos[i].name = name.encode()
+        infos[i].dtype = BF16 if name in bf16 else codes[a.dtype.name]
+        infos[i].rank = a.ndim
+        for d, extent in enumerate(a.shape):
+            infos[i].shape[d] = extent
+        infos[i].data = a.ctypes.data
+        infos[i].bytes = a.nbytes
+    metadata = metadata or {}
+    keys = (C.c_char_p * len(metadata))(*[k.encode() for k in metadata])
+    values = (C.c_char_p * len(metadata))(*[v.encode() for v in metadata.values()])
+    _check(library().sepal_b200_tensor_file_write(os.fsencode(path), len(tensors), infos, len(metadata), keys, values))
+
+
+class Model(C.Structure):
+    """sepal_b200_model: the geometry of a served model (presets 0.8b, 2b, 4b, 9b)."""
+
+    _fields_ = [(f, _u64) for f in ("layers", "hidden", "intermediate", "vocab", "attn_heads", "attn_kv_heads", "attn_head_dim", "dn_key_heads",
+                                    "dn_value_heads", "dn_key_head_dim", "dn_value_head_dim", "conv_kernel", "attention_interval")]
+
+    @classmethod
+    def preset(cls, name: str) -> "Model":
+        m = cls()
+        _check(library().sepal_b200_model_preset(name.encode(), C.byref(m)))
+        return m
+
+    def weight_bytes(self, profile: str) -> int:
+        out = _u64()
+        _check(library().sepal_b200_plan_weight_bytes(C.byref(self), profile.encode(), C.byref(out)))
+        return int(out.value)
 
 
 class Provider:

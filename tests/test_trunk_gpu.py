@@ -29,7 +29,7 @@ def oracle_forward(oracle, trunk, cfg, tokens):
     for l in range(cfg.layers):
         attention = l % 4 == 3
         n_in = cfg.attn_q + 2 * cfg.attn_kv if attention else cfg.dn_in
-        k_out = cfg.attn_q if attention else cfg.dn_v
+        k_out = (cfg.attn_o or cfg.attn_q) if attention else cfg.dn_v
         off = 0 if attention else cfg.dn_v_offset
         w_in = trunk.weight("mix_in", l).reshape(n_in, H).astype(np.float32)
         w_out = trunk.weight("mix_out", l).reshape(H, k_out).astype(np.float32)
@@ -167,3 +167,131 @@ def test_score_packs_requests_into_calls_and_matches_one_by_one(oracle):
         assert trunk.score([])[0].shape == (0, cfg.hidden)
     finally:
         trunk.close()
+
+
+def to_bf16_bits(a):
+    """float32 -> bfloat16 bit patterns, round to nearest even (finite values)."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def bf16_to_f32(bits):
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def make_checkpoint(path, cfg, rng, prefix="model.language_model."):
+    """A checkpoint with the reference's tensor names for the small geometry, in mixed storage types. Returns the float32 values."""
+    import sepal_runner_b200 as sb
+
+    H, I = cfg.hidden, cfg.intermediate
+    values, stored, bf16 = {}, {}, []
+
+    def add(name, shape, kind):
+        v = (rng.standard_normal(shape) * 0.05).astype(np.float32)
+        if kind == "bf16":
+            bits = to_bf16_bits(v)
+            stored[prefix + name] = bits
+            bf16.append(prefix + name)
+            v = bf16_to_f32(bits)
+        elif kind == "f16":
+            stored[prefix + name] = v.astype(np.float16)
+            v = stored[prefix + name].astype(np.float32)
+        else:
+            stored[prefix + name] = v
+        values[name] = v
+
+    add("embed_tokens.weight", (cfg.vocab, H), "bf16")
+    add("norm.weight", (H,), "f32")  # the final norm: not part of this path, must be ignored
+    for l in range(cfg.layers):
+        pre = f"layers.{l}."
+        add(pre + "input_layernorm.weight", (H,), "bf16" if l % 2 else "f32")
+        add(pre + "post_attention_layernorm.weight", (H,), "f16" if l % 2 else "f32")
+        if l % 4 == 3:
+            add(pre + "self_attn.q_proj.weight", (cfg.attn_q, H), "bf16")
+            add(pre + "self_attn.k_proj.weight", (cfg.attn_kv, H), "f32")
+            add(pre + "self_attn.v_proj.weight", (cfg.attn_kv, H), "f16")
+            add(pre + "self_attn.o_proj.weight", (H, cfg.attn_o), "bf16")
+        else:
+            rest = cfg.dn_in - 640 - 256
+            add(pre + "linear_attn.in_proj_qkv.weight", (640, H), "bf16")
+            add(pre + "linear_attn.in_proj_z.weight", (256, H), "bf16")
+            add(pre + "linear_attn.in_proj_b.weight", (rest // 2, H), "f32")
+            add(pre + "linear_attn.in_proj_a.weight", (rest - rest // 2, H), "f32")
+            add(pre + "linear_attn.out_proj.weight", (H, cfg.dn_v), "f16")
+        add(pre + "mlp.gate_proj.weight", (I, H), "f32" if l == 0 else "bf16")
+        add(pre + "mlp.up_proj.weight", (I, H), "bf16")
+        add(pre + "mlp.down_proj.weight", (H, I), "f32" if l == 1 else "bf16")
+    sb.write_tensor_file(path, stored, {"format": "pt"}, bf16=bf16)
+    return values
+
+
+@pytest.mark.parametrize("int8", [0, 1])
+def test_placement_from_a_checkpoint_and_saved_weights(oracle, tmp_path, int8):
+    """Weights from a checkpoint with the reference's names: stacked, rounded once to binary16, [gate; up] interleaved in blocks of 64, the
+    MLP quantised from a float32 copy -- compared with a numpy restatement bit for bit; then saved in placed form and loaded back."""
+    import sepal_runner_b200 as sb
+
+    cfg = small_config(sb, attn_q=512, attn_o=256, mlp_int8=int8)
+    rng = np.random.default_rng(2024)
+    path = str(tmp_path / "model.safetensors")
+    v = make_checkpoint(path, cfg, rng)
+    ck = sb.Checkpoint(str(tmp_path))
+    trunk = sb.Trunk(0, cfg, ck)
+    H, I = cfg.hidden, cfg.intermediate
+    order = [sb.pack_gate_up_source(p, I) for p in range(2 * I)]
+    try:
+        assert np.array_equal(trunk.weight("embedding").reshape(cfg.vocab, H), v["embed_tokens.weight"].astype(np.float16))
+        for l in range(cfg.layers):
+            pre = f"layers.{l}."
+            assert np.array_equal(trunk.weight("norm_in", l), v[pre + "input_layernorm.weight"])
+            assert np.array_equal(trunk.weight("norm_post", l), v[pre + "post_attention_layernorm.weight"])
+            if l % 4 == 3:
+                stacked = np.concatenate([v[pre + f"self_attn.{n}_proj.weight"] for n in "qkv"])
+                out = v[pre + "self_attn.o_proj.weight"]
+            else:
+                stacked = np.concatenate([v[pre + f"linear_attn.in_proj_{n}.weight"] for n in ("qkv", "z", "b", "a")])
+                out = v[pre + "linear_attn.out_proj.weight"]
+            assert np.array_equal(trunk.weight("mix_in", l).reshape(stacked.shape), stacked.astype(np.float16)), l
+            assert np.array_equal(trunk.weight("mix_out", l).reshape(out.shape), out.astype(np.float16)), l
+            gate_up = np.concatenate([v[pre + "mlp.gate_proj.weight"], v[pre + "mlp.up_proj.weight"]])[order]
+            down = v[pre + "mlp.down_proj.weight"]
+            if int8:
+                assert np.array_equal(trunk.weight("gate_up", l).reshape(2 * I, H), oracle.quantize_group_s8(gate_up)[0]), l
+                assert np.array_equal(trunk.weight("down", l).reshape(H, I), oracle.quantize_group_s8(down)[0]), l
+            else:
+                assert np.array_equal(trunk.weight("gate_up", l).reshape(2 * I, H), gate_up.astype(np.float16)), l
+                assert np.array_equal(trunk.weight("down", l).reshape(H, I), down.astype(np.float16)), l
+        tokens = rng.integers(0, cfg.vocab, 333).astype(np.uint32)
+        last, allh, _ = trunk.run(tokens, want_all=True)
+        assert np.isfinite(allh).all()
+        if not int8:
+            assert rel_fro(allh, oracle_forward(oracle, trunk, cfg, tokens)) < 2e-3
+        saved = str(tmp_path / "placed.safetensors")
+        trunk.save(saved)
+        again = sb.Trunk(0, cfg, sb.Checkpoint(saved))
+        try:
+            for which in ("embedding", "mix_in", "mix_out", "norm_in", "norm_post", "gate_up", "down"):
+                for l in (0, 3, cfg.layers - 1):
+                    assert np.array_equal(again.weight(which, l), trunk.weight(which, l)), (which, l)
+            assert np.array_equal(again.run(tokens, want_all=True)[1], allh)
+            assert again.weight_bytes == trunk.weight_bytes
+        finally:
+            again.close()
+        with pytest.raises(sb.SepalB200Error, match="mlp_int8"):
+            sb.Trunk(0, small_config(sb, attn_q=512, attn_o=256, mlp_int8=1 - int8), sb.Checkpoint(saved))
+        with pytest.raises(sb.SepalB200Error, match="needs \\[256 x 128\\]|rows together"):
+            sb.Trunk(0, small_config(sb, attn_q=512, attn_o=128, mlp_int8=int8), ck)
+        with pytest.raises(sb.SepalB200Error, match="rows together"):
+            sb.Trunk(0, small_config(sb, attn_q=512, attn_o=256, dn_in=1032, mlp_int8=int8), ck)
+    finally:
+        trunk.close()
+        ck.close()
+
+
+def test_placement_reports_a_missing_tensor(tmp_path):
+    import sepal_runner_b200 as sb
+
+    cfg = small_config(sb, layers=4)
+    sb.write_tensor_file(str(tmp_path / "model.safetensors"), {"embed_tokens.weight": np.zeros((cfg.vocab, cfg.hidden), np.float16)})
+    with pytest.raises(sb.SepalB200Error, match="no tensor 'layers.0.input_layernorm.weight'"):
+        sb.Trunk(0, cfg, sb.Checkpoint(str(tmp_path)))

@@ -193,6 +193,40 @@ typedef struct sepal_b200_trunk_config {
 SEPAL_B200_API int32_t sepal_b200_trunk_open(int32_t device, const sepal_b200_trunk_config* config, sepal_b200_trunk** out);
 SEPAL_B200_API void sepal_b200_trunk_close(sepal_b200_trunk* trunk);
 
+/* ---- the full-attention core between its projections ---------------------------------------------------------------------------------
+ *
+ * Replaces launch_attention_prepare and launch_attention (runner/cuda/src/kernels_attention.hpp:154-183) for requests whose keys and
+ * values are contiguous: per-head RMSNorm of q and k ("1 + weight" form), partial RoPE (the first rotary_dims of a head, dimension i
+ * paired with i + rotary_dims / 2, angles position * theta^(-2 i / rotary_dims) in float64), keys and values appended to the request's
+ * range of the arena, causal grouped-query attention scaled by 1 / sqrt(head_dim), times sigmoid(gate)
+ * (runner/include/sepal/ref/attention.hpp:33-235). q_proj's output holds, per head, the query then its gate. A call's tokens form runs
+ * ("rows") of consecutive tokens of different requests; a row names where its request's keys start in the arena (kv_begin) and how many
+ * of the request's tokens are there already (context = the position of the row's first token). The arenas are binary16 [arena_tokens,
+ * kv_heads * head_dim] and must hold finite numbers everywhere (zero them once). head_dim 128 or 256. `rows` is a host array, sorted by
+ * q_begin. *_half: 1 = the band is binary16, 0 = float32. Both calls enqueue on `stream` and return. */
+typedef struct sepal_b200_attention_shape {
+    uint32_t heads, kv_heads, head_dim, rotary_dims;
+    double rope_theta;
+    float eps;
+    uint32_t reserved;
+} sepal_b200_attention_shape;
+typedef struct sepal_b200_attention_row {
+    uint32_t q_begin, length, kv_begin, context;
+} sepal_b200_attention_row;
+/* q_gate [N, 2 * heads * head_dim], k and v [N, kv_heads * head_dim]; q_norm, k_norm float32 [head_dim]; q_out binary16 [N, heads * head_dim]. */
+SEPAL_B200_API int32_t sepal_b200_attention_prepare(sepal_b200_ctx* ctx, const sepal_b200_attention_shape* shape, const sepal_b200_attention_row* rows,
+                                                    uint64_t n_rows, const void* q_gate, uint64_t q_gate_stride, int32_t q_gate_half, const void* k,
+                                                    uint64_t k_stride, int32_t k_half, const void* v, uint64_t v_stride, int32_t v_half,
+                                                    const float* q_norm, const float* k_norm, void* q_out, uint64_t q_stride, void* k_arena,
+                                                    void* v_arena, uint64_t arena_tokens, void* stream);
+/* q: what the prepare call wrote; gate: the q_gate band again (read at column head * 2 * head_dim + head_dim + d); out binary16
+ * [N, heads * head_dim], the operand of o_proj. Flash attention on tcgen05 (Q K^T and P V on the tensor cores, accumulators in tensor
+ * memory, float32 online softmax), one CTA per 128 queries of a row and head, keys in blocks counted from the request's first token. */
+SEPAL_B200_API int32_t sepal_b200_attention(sepal_b200_ctx* ctx, const sepal_b200_attention_shape* shape, const sepal_b200_attention_row* rows,
+                                            uint64_t n_rows, uint64_t n_tokens, const void* q, uint64_t q_stride, const void* k_arena,
+                                            const void* v_arena, uint64_t arena_tokens, const void* gate, uint64_t gate_stride, int32_t gate_half,
+                                            void* out, uint64_t out_stride, void* stream);
+
 /* ---- checkpoints and weight placement (the data format on the input side of the path) ----------------------------------------------
  *
  * The reader of the safetensors format (runner/include/sepal/safetensors.hpp:1-154) and of checkpoint directories with their name

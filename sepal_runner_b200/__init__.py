@@ -6,6 +6,10 @@ There is no CPU path: loading fails loudly when the library is missing, and `Con
 """
 from .lib import (  # noqa: F401
     ADD,
+    AttentionRow,
+    AttentionShape,
+    attention,
+    attention_prepare,
     BF16,
     Checkpoint,
     Model,

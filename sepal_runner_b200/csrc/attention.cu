@@ -1,0 +1,562 @@
+#include "attention.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include <cuda_fp16.h>
+
+#include "ptx.cuh"
+
+namespace sepal::b200 {
+
+void count_launch();
+
+namespace {
+
+constexpr int kQueries = 128;                   // queries of one CTA = lanes of tensor memory
+constexpr long long kWaitLimit = 1ll << 30;     // clock cycles before a wait gives up
+constexpr int kStatusAttention = 16;            // status codes 16 .. 23: a wait of the attention kernel ran out
+
+__device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, volatile unsigned* abort_flag, int* status, int code) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    for (;;) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 31u) == 0) {
+            if (*abort_flag != 0) return false;
+            if (clock64() - t0 > kWaitLimit) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code | (static_cast<int>(blockIdx.x) << 8));
+                return false;
+            }
+        }
+    }
+}
+
+// ---- prepare --------------------------------------------------------------------------------------------------------------------
+
+struct PrepareParams {
+    const AttentionRow* rows;
+    unsigned n_rows;
+    unsigned heads, kv_heads, head_dim, rotary_dims;
+    float eps;
+    const double* inv_freq;  // theta^(-2 i / rotary_dims), i < rotary_dims / 2
+    const void* q_gate;
+    const void* k;
+    const void* v;
+    unsigned long long q_gate_stride, k_stride, v_stride;
+    unsigned q_gate_half, k_half, v_half;
+    const float* q_norm;
+    const float* k_norm;
+    __half* q_out;
+    unsigned long long q_stride;
+    __half* k_arena;
+    __half* v_arena;
+};
+
+__device__ __forceinline__ float band_value(const void* base, unsigned long long index, unsigned half) {
+    return half != 0 ? __half2float(static_cast<const __half*>(base)[index]) : static_cast<const float*>(base)[index];
+}
+
+// One block per token; a warp takes heads in turn (query heads, then key heads, then the value heads' copy). Lane l holds dimensions
+// l, l + 32, ... of the head. Sum of squares: each lane in that order, then a butterfly: fixed, a function of the head alone. The
+// normed head goes through shared memory so that a rotated dimension can read its partner (i with i + rotary_dims / 2) from any lane.
+__global__ void __launch_bounds__(256) attention_prepare_kernel(const PrepareParams p) {
+    __shared__ float cs[256];          // cos then sin of the token's rotary_dims / 2 angles
+    __shared__ float normed[8][256];   // one head per warp
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+    const unsigned token = blockIdx.x;
+    // the run this token belongs to: the last row whose q_begin is at or before it
+    unsigned lo = 0, hi = p.n_rows;
+    while (hi - lo > 1) {
+        const unsigned mid = (lo + hi) / 2;
+        if (p.rows[mid].q_begin <= token) lo = mid; else hi = mid;
+    }
+    const AttentionRow row = p.rows[lo];
+    if (token < row.q_begin || token >= row.q_begin + row.length) return;  // a token outside every run (gaps are allowed)
+    const unsigned t = token - row.q_begin;
+    const double position = static_cast<double>(row.context + t);
+    const unsigned half_rot = p.rotary_dims / 2;
+    for (unsigned i = threadIdx.x; i < half_rot; i += blockDim.x) {
+        const double angle = position * p.inv_freq[i];  // float64: a position is a large whole number
+        cs[i] = static_cast<float>(cos(angle));
+        cs[128 + i] = static_cast<float>(sin(angle));
+    }
+    __syncthreads();
+    const unsigned warp = threadIdx.x / 32, lane = threadIdx.x % 32, warps = blockDim.x / 32;
+    const unsigned hd = p.head_dim, per_lane = hd / 32;  // 4 or 8
+    const size_t arena_row = static_cast<size_t>(row.kv_begin) + row.context + t;
+    for (unsigned job = warp; job < p.heads + 2 * p.kv_heads; job += warps) {
+        if (job >= p.heads + p.kv_heads) {  // a value head: stored as it is
+            const unsigned h = job - p.heads - p.kv_heads;
+            for (unsigned e = 0; e < per_lane; ++e) {
+                const unsigned d = lane + 32 * e;
+                p.v_arena[arena_row * (p.kv_heads * hd) + h * hd + d] = __float2half_rn(band_value(p.v, token * p.v_stride + h * hd + d, p.v_half));
+            }
+            continue;
+        }
+        const bool is_q = job < p.heads;
+        const unsigned h = is_q ? job : job - p.heads;
+        const float* w = is_q ? p.q_norm : p.k_norm;
+        float x[8];
+        float ss = 0.0f;
+        for (unsigned e = 0; e < per_lane; ++e) {
+            const unsigned d = lane + 32 * e;
+            x[e] = is_q ? band_value(p.q_gate, token * p.q_gate_stride + static_cast<size_t>(h) * 2 * hd + d, p.q_gate_half)
+                        : band_value(p.k, token * p.k_stride + h * hd + d, p.k_half);
+            ss = __fmaf_rn(x[e], x[e], ss);
+        }
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+        const float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(hd)), p.eps));
+        __syncwarp();  // the previous head's readers are done with the buffer
+        for (unsigned e = 0; e < per_lane; ++e) normed[warp][lane + 32 * e] = __fmul_rn(__fdiv_rn(x[e], rms), __fadd_rn(1.0f, w[lane + 32 * e]));
+        __syncwarp();
+        __half* dst = is_q ? p.q_out + token * p.q_stride + static_cast<size_t>(h) * hd : p.k_arena + arena_row * (p.kv_heads * hd) + h * hd;
+        for (unsigned e = 0; e < per_lane; ++e) {
+            const unsigned d = lane + 32 * e;
+            float y = normed[warp][d];
+            if (d < half_rot) {  // (a, b) -> (a cos - b sin, b cos + a sin) for a = dimension i, b = dimension i + rotary_dims / 2
+                y = __fsub_rn(__fmul_rn(y, cs[d]), __fmul_rn(normed[warp][d + half_rot], cs[128 + d]));
+            } else if (d < 2 * half_rot) {
+                const unsigned i = d - half_rot;
+                y = __fadd_rn(__fmul_rn(y, cs[i]), __fmul_rn(normed[warp][i], cs[128 + i]));
+            }
+            dst[d] = __float2half_rn(y);
+        }
+    }
+}
+
+// ---- attention -------------------------------------------------------------------------------------------------------------------
+
+struct AttentionParams {
+    const AttentionRow* rows;
+    const unsigned* blocks;  // (row, query block) pairs, heaviest first
+    unsigned heads, group;   // query heads; heads / kv_heads
+    float scale_log2;        // log2(e) / sqrt(head_dim)
+    const void* gate;
+    unsigned long long gate_stride;
+    unsigned gate_half;
+    __half* out;
+    unsigned long long out_stride;
+    int* status;
+};
+
+template <int D>
+struct AttentionTile {
+    static constexpr int kKeys = D == 128 ? 128 : 64;         // keys per block
+    static constexpr int kBoxes = D / 64;                      // 64-column boxes of a Q, K or V tile
+    static constexpr int kQBytes = kQueries * D * 2;
+    static constexpr int kKvBytes = kKeys * D * 2;             // one K tile or one V tile
+    static constexpr int kPBytes = kQueries * kKeys * 2;
+    static constexpr int kStages = 2;
+    static constexpr int kSmem = 1024 + kQBytes + kStages * 2 * kKvBytes + kPBytes + 256;
+    static constexpr int kSCols = kKeys;                       // tensor-memory columns of one score buffer
+    static constexpr int kOCol = 2 * kKeys;                    // where the output accumulator starts
+};
+
+// Warp 0: TMA (Q once, then K and V blocks into a ring of two). Warp 1: MMA issuer: S_j = Q K_j^T into one of two score buffers (S_{j+1}
+// is issued before P_j V_j, so the tensor core has work while the softmax of block j runs), then O += P_j V_j. Warps 2-5: one query per
+// thread: scores from tensor memory, masked, running maximum and sum in the base-2 domain, P_j as binary16 into shared memory in the
+// layout the MMA reads, O rescaled in tensor memory when the maximum moved; at the end O / l * sigmoid(gate).
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                 const AttentionParams p) {
+    using T = AttentionTile<D>;
+    constexpr int kKeys = T::kKeys;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_addr(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* const smem = smem_raw + (base - raw_addr);
+    const uint32_t q_addr = base;
+    const uint32_t kv_addr = base + T::kQBytes;  // stage s: K at kv_addr + s * 2 * kKvBytes, V right after it
+    const uint32_t p_addr = kv_addr + T::kStages * 2 * T::kKvBytes;
+    uint8_t* const p_smem = smem + (p_addr - base);
+    uint8_t* const tail = smem + (p_addr - base) + T::kPBytes;
+    const uint32_t bars = ptx::smem_addr(tail);
+    const uint32_t q_full = bars, p_full = bars + 8, pv_done = bars + 16;
+    const auto kv_full = [&](int s) { return bars + 24u + 8u * s; };
+    const auto kv_empty = [&](int s) { return bars + 40u + 8u * s; };
+    const auto s_full = [&](int b) { return bars + 56u + 8u * b; };
+    const auto s_free = [&](int b) { return bars + 72u + 8u * b; };
+    unsigned* const words = reinterpret_cast<unsigned*>(tail + 96);
+    unsigned* const tmem_slot = words;
+    volatile unsigned* const abort_flag = words + 1;
+
+    const unsigned warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const unsigned head = blockIdx.y, kv_head = head / p.group;
+    const AttentionRow row = p.rows[p.blocks[2 * blockIdx.x]];
+    const unsigned qb = p.blocks[2 * blockIdx.x + 1];
+    const unsigned q0 = qb * kQueries;                                  // first query of the block inside the run
+    const unsigned valid = min(static_cast<unsigned>(kQueries), row.length - q0);
+    // keys the block's last valid query sees, and the blocks that hold them
+    const unsigned n_keys = row.context + q0 + valid;
+    const unsigned n_blocks = (n_keys + kKeys - 1) / kKeys;
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(q_full, 1);
+        ptx::mbar_init(p_full, 128);
+        ptx::mbar_init(pv_done, 1);
+        for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(kv_full(s), 1);
+            ptx::mbar_init(kv_empty(s), 1);
+            ptx::mbar_init(s_full(s), 1);
+            ptx::mbar_init(s_free(s), 128);
+        }
+        words[1] = 0;
+        ptx::fence_barrier_init();
+        ptx::tma_prefetch_descriptor(&map_q);
+        ptx::tma_prefetch_descriptor(&map_k);
+        ptx::tma_prefetch_descriptor(&map_v);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_addr(tmem_slot), 512);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            ptx::mbar_arrive_expect_tx(q_full, T::kQBytes);
+            for (int b = 0; b < T::kBoxes; ++b)
+                ptx::tma_load_2d(q_addr + b * (kQueries * 128), &map_q, q_full, static_cast<int>(head * D + 64 * b), static_cast<int>(row.q_begin + q0));
+            for (unsigned j = 0; j < n_blocks; ++j) {
+                const int s = static_cast<int>(j & 1u);
+                if (j >= 2 && !wait_barrier(kv_empty(s), ((j >> 1) - 1) & 1u, abort_flag, p.status, kStatusAttention + 0)) break;
+                const uint32_t k_dst = kv_addr + s * 2 * T::kKvBytes, v_dst = k_dst + T::kKvBytes;
+                const int key_row = static_cast<int>(row.kv_begin + j * kKeys);
+                ptx::mbar_arrive_expect_tx(kv_full(s), 2 * T::kKvBytes);
+                for (int b = 0; b < T::kBoxes; ++b) {
+                    ptx::tma_load_2d(k_dst + b * (kKeys * 128), &map_k, kv_full(s), static_cast<int>(kv_head * D + 64 * b), key_row);
+                    ptx::tma_load_2d(v_dst + b * (kKeys * 128), &map_v, kv_full(s), static_cast<int>(kv_head * D + 64 * b), key_row);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_s = ptx::instr_desc_f16_f32acc(kQueries, kKeys);
+            const uint32_t idesc_o = ptx::instr_desc_f16_f32acc_b_mn(kQueries, D);
+            const uint32_t o_tmem = tmem_base + T::kOCol;
+            const auto issue_scores = [&](unsigned j) {  // S_j = Q K_j^T into score buffer j & 1
+                const int s = static_cast<int>(j & 1u);
+                const uint32_t k_tile = kv_addr + s * 2 * T::kKvBytes;
+#pragma unroll
+                for (int b = 0; b < T::kBoxes; ++b) {
+                    const uint64_t dq = ptx::smem_desc_k_major_sw128(q_addr + b * (kQueries * 128));
+                    const uint64_t dk = ptx::smem_desc_k_major_sw128(k_tile + b * (kKeys * 128));
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) ptx::mma_f16_ss(tmem_base + s * T::kSCols, dq + 2u * kk, dk + 2u * kk, idesc_s, (b | kk) != 0 ? 1u : 0u);
+                }
+                ptx::mma_commit(s_full(s));
+            };
+            bool ok = wait_barrier(q_full, 0, abort_flag, p.status, kStatusAttention + 1) && wait_barrier(kv_full(0), 0, abort_flag, p.status, kStatusAttention + 1);
+            if (ok) {
+                ptx::tc_fence_after_sync();
+                issue_scores(0);
+            }
+            for (unsigned j = 0; ok && j < n_blocks; ++j) {
+                const int s = static_cast<int>(j & 1u);
+                if (j + 1 < n_blocks) {
+                    const unsigned n = j + 1;
+                    ok = wait_barrier(kv_full(n & 1u), (n >> 1) & 1u, abort_flag, p.status, kStatusAttention + 2);
+                    if (ok && n >= 2) ok = wait_barrier(s_free(n & 1u), ((n >> 1) - 1) & 1u, abort_flag, p.status, kStatusAttention + 3);
+                    if (!ok) break;
+                    ptx::tc_fence_after_sync();
+                    issue_scores(n);
+                }
+                ok = wait_barrier(p_full, j & 1u, abort_flag, p.status, kStatusAttention + 4);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t v_tile = kv_addr + s * 2 * T::kKvBytes + T::kKvBytes;
+#pragma unroll
+                for (int kb = 0; kb < kKeys / 16; ++kb) {
+                    const uint64_t dp = ptx::smem_desc_k_major_sw128(p_addr + (kb / 4) * (kQueries * 128)) + 2u * (kb % 4);
+                    const uint64_t dv = ptx::smem_desc_mn_major_sw128(v_tile + kb * 2048, kKeys * 128);
+                    ptx::mma_f16_ss(o_tmem, dp, dv, idesc_o, (j > 0 || kb > 0) ? 1u : 0u);
+                }
+                ptx::mma_commit(kv_empty(s));
+                ptx::mma_commit(pv_done);
+            }
+        }
+        __syncwarp();
+    } else {
+        const unsigned quarter = warp % 4;
+        const unsigned r = quarter * 32 + lane;  // this thread's query inside the block
+        const uint32_t lane_base = tmem_base + ((quarter * 32u) << 16);
+        const unsigned q_index = row.context + q0 + r;  // the last key this query sees
+        float m = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (unsigned j = 0; j < n_blocks; ++j) {
+            const int s = static_cast<int>(j & 1u);
+            ok = wait_barrier(s_full(s), (j >> 1) & 1u, abort_flag, p.status, kStatusAttention + 5);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t s_tmem = lane_base + s * T::kSCols;
+            const unsigned key0 = j * kKeys;
+            const bool diagonal = key0 + kKeys - 1 > row.context + q0;  // some key of the block is hidden from some query
+            // pass 1: the block's maximum for this query
+            float block_max = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < kKeys; c += 32) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(s_tmem + c, v);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float t = __uint_as_float(v[i]) * p.scale_log2;
+                    if (!diagonal || key0 + c + i <= q_index) block_max = fmaxf(block_max, t);
+                }
+            }
+            const float m_new = fmaxf(m, block_max);
+            const float alpha = exp2f(m - m_new);  // 0 at the first block (m = -inf), 1 when the maximum did not move
+            // P_j may be written and O rescaled only when P_{j-1} V_{j-1} has finished
+            if (j > 0) {
+                ok = wait_barrier(pv_done, (j - 1) & 1u, abort_flag, p.status, kStatusAttention + 6);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+            }
+            // pass 2: probabilities, their sum, P as binary16 in the swizzled K-major layout (row r, 16-byte chunk c8 of box c8 / 8)
+            float sum = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < kKeys; c += 32) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(s_tmem + c, v);
+                ptx::tmem_ld_wait();
+                unsigned packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float e0 = exp2f(__uint_as_float(v[i]) * p.scale_log2 - m_new);
+                    float e1 = exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - m_new);
+                    if (diagonal) {
+                        if (key0 + c + i > q_index) e0 = 0.0f;
+                        if (key0 + c + i + 1 > q_index) e1 = 0.0f;
+                    }
+                    const __half2 h = __floats2half2_rn(e0, e1);
+                    // the sum is taken over what the tensor core will multiply: the rounded probabilities
+                    const float2 back = __half22float2(h);
+                    sum += back.x + back.y;
+                    packed[i / 2] = *reinterpret_cast<const unsigned*>(&h);
+                }
+                uint8_t* box = p_smem + (c / 64) * (kQueries * 128) + r * 128;
+                const unsigned chunk0 = (c % 64) / 8;
+#pragma unroll
+                for (unsigned q = 0; q < 4; ++q)
+                    *reinterpret_cast<uint4*>(box + (((chunk0 + q) ^ (r & 7u)) * 16)) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            }
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(s_free(s));  // the scores of this buffer have been read twice: it may be overwritten
+            // rescale O where the maximum moved (a warp's loads and stores of tensor memory are collective: all lanes go together)
+            if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
+#pragma unroll 1
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32(lane_base + T::kOCol + c, v);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    ptx::tmem_st_32x32(lane_base + T::kOCol + c, v);
+                }
+                ptx::tmem_st_wait();
+            }
+            l = l * alpha + sum;
+            m = m_new;
+            ptx::fence_proxy_async_smem();  // P was written with ordinary stores; the MMA reads it through the async proxy
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive(p_full);
+        }
+        if (ok && n_blocks > 0) ok = wait_barrier(pv_done, (n_blocks - 1) & 1u, abort_flag, p.status, kStatusAttention + 7);
+        // every lane takes part in the loads; only valid queries store
+        if (ok) {
+            ptx::tc_fence_after_sync();
+            const float inv_l = 1.0f / l;
+            const size_t token = static_cast<size_t>(row.q_begin) + q0 + r;
+            __half* dst = p.out + token * p.out_stride + static_cast<size_t>(head) * D;
+#pragma unroll 1
+            for (int c = 0; c < D; c += 32) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(lane_base + T::kOCol + c, v);
+                ptx::tmem_ld_wait();
+                if (r < valid) {
+                    unsigned packed[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const size_t g = token * p.gate_stride + static_cast<size_t>(head) * 2 * D + D + c + i;
+                        const float g0 = band_value(p.gate, g, p.gate_half), g1 = band_value(p.gate, g + 1, p.gate_half);
+                        const float o0 = __uint_as_float(v[i]) * inv_l * (1.0f / (1.0f + expf(-g0)));
+                        const float o1 = __uint_as_float(v[i + 1]) * inv_l * (1.0f / (1.0f + expf(-g1)));
+                        const __half2 h = __floats2half2_rn(o0, o1);
+                        packed[i / 2] = *reinterpret_cast<const unsigned*>(&h);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        *reinterpret_cast<uint4*>(dst + c + 8 * q) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+            }
+        }
+    }
+
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, 512);
+    }
+}
+
+void check_shape(const AttentionShape& s) {
+    if (!attention_supports(s))
+        throw std::invalid_argument("sepal_b200 attention: head_dim must be 128 or 256, heads a multiple of kv_heads, rotary_dims even and at most head_dim");
+}
+
+// The rows and, after them, what else a launch needs, copied to the context's table. Returns the device address of the rows.
+const AttentionRow* upload_rows(Context& ctx, const AttentionRow* rows, std::size_t n_rows, const void* extra, std::size_t extra_bytes, const void** extra_dev,
+                                cudaStream_t stream) {
+    if (ctx.table == nullptr) throw std::invalid_argument("sepal_b200 attention: this context has no table memory");
+    const std::size_t row_bytes = n_rows * sizeof(AttentionRow);
+    const std::size_t need = (row_bytes + 15) / 16 * 16 + extra_bytes;
+    if (need > ctx.table_bytes / 2) throw std::invalid_argument("sepal_b200 attention: " + std::to_string(n_rows) + " rows are more than the context's table holds");
+    // two halves used in turn, so that the table of the launch before this one is not overwritten while it may still run
+    char* base = static_cast<char*>(ctx.table) + (ctx.table_turn++ & 1u) * (ctx.table_bytes / 2);
+    check(cudaMemcpyAsync(base, rows, row_bytes, cudaMemcpyHostToDevice, stream), "cudaMemcpyAsync(rows)");
+    if (extra_bytes != 0) {
+        check(cudaMemcpyAsync(base + (row_bytes + 15) / 16 * 16, extra, extra_bytes, cudaMemcpyHostToDevice, stream), "cudaMemcpyAsync(table)");
+        *extra_dev = base + (row_bytes + 15) / 16 * 16;
+    }
+    return reinterpret_cast<const AttentionRow*>(base);
+}
+
+void check_rows(const AttentionRow* rows, std::size_t n_rows, std::size_t n_tokens, std::size_t arena_tokens) {
+    for (std::size_t i = 0; i < n_rows; ++i) {
+        const AttentionRow& r = rows[i];
+        if (r.length == 0) throw std::invalid_argument("sepal_b200 attention: row " + std::to_string(i) + " is empty");
+        if (i > 0 && r.q_begin < rows[i - 1].q_begin + rows[i - 1].length) throw std::invalid_argument("sepal_b200 attention: rows must be sorted by their first token and must not overlap");
+        if (n_tokens != 0 && static_cast<std::size_t>(r.q_begin) + r.length > n_tokens) throw std::invalid_argument("sepal_b200 attention: row " + std::to_string(i) + " ends past the call's tokens");
+        if (static_cast<std::size_t>(r.kv_begin) + r.context + r.length > arena_tokens)
+            throw std::invalid_argument("sepal_b200 attention: row " + std::to_string(i) + " ends past the key/value arena");
+    }
+}
+
+}  // namespace
+
+bool attention_supports(const AttentionShape& s) {
+    return (s.head_dim == 128 || s.head_dim == 256) && s.kv_heads != 0 && s.heads != 0 && s.heads % s.kv_heads == 0 && s.rotary_dims % 2 == 0 &&
+           s.rotary_dims <= s.head_dim;
+}
+
+void launch_attention_prepare(Context& ctx, const AttentionShape& shape, const AttentionRow* rows, std::size_t n_rows, Band q_gate, Band k, Band v,
+                              const float* q_norm, const float* k_norm, void* q_out, std::size_t q_stride, void* k_arena, void* v_arena,
+                              std::size_t arena_tokens, cudaStream_t stream) {
+    check_shape(shape);
+    if (n_rows == 0) return;
+    if (rows == nullptr || q_gate.data == nullptr || k.data == nullptr || v.data == nullptr || q_norm == nullptr || k_norm == nullptr || q_out == nullptr ||
+        k_arena == nullptr || v_arena == nullptr)
+        throw std::invalid_argument("sepal_b200 attention: null pointer");
+    check_rows(rows, n_rows, 0, arena_tokens);
+    check(cudaSetDevice(ctx.device), "cudaSetDevice");
+    std::vector<double> inv_freq(shape.rotary_dims / 2);
+    for (std::size_t i = 0; i < inv_freq.size(); ++i) inv_freq[i] = std::pow(shape.rope_theta, -static_cast<double>(2 * i) / static_cast<double>(shape.rotary_dims));
+    const void* inv_dev = nullptr;
+    PrepareParams p{};
+    p.rows = upload_rows(ctx, rows, n_rows, inv_freq.data(), inv_freq.size() * sizeof(double), &inv_dev, stream);
+    p.n_rows = static_cast<unsigned>(n_rows);
+    p.heads = shape.heads;
+    p.kv_heads = shape.kv_heads;
+    p.head_dim = shape.head_dim;
+    p.rotary_dims = shape.rotary_dims;
+    p.eps = shape.eps;
+    p.inv_freq = static_cast<const double*>(inv_dev);
+    p.q_gate = q_gate.data;
+    p.k = k.data;
+    p.v = v.data;
+    p.q_gate_stride = q_gate.stride;
+    p.k_stride = k.stride;
+    p.v_stride = v.stride;
+    p.q_gate_half = q_gate.half ? 1u : 0u;
+    p.k_half = k.half ? 1u : 0u;
+    p.v_half = v.half ? 1u : 0u;
+    p.q_norm = q_norm;
+    p.k_norm = k_norm;
+    p.q_out = static_cast<__half*>(q_out);
+    p.q_stride = q_stride;
+    p.k_arena = static_cast<__half*>(k_arena);
+    p.v_arena = static_cast<__half*>(v_arena);
+    const unsigned first = rows[0].q_begin, last = rows[n_rows - 1].q_begin + rows[n_rows - 1].length;
+    (void)first;
+    launch_kernel(attention_prepare_kernel, dim3(last), dim3(256), 0, stream, "attention_prepare_kernel launch", p);
+    count_launch();
+}
+
+void launch_attention(Context& ctx, const AttentionShape& shape, const AttentionRow* rows, std::size_t n_rows, std::size_t n_tokens, const void* q,
+                      std::size_t q_stride, const void* k_arena, const void* v_arena, std::size_t arena_tokens, Band gate, void* out,
+                      std::size_t out_stride, cudaStream_t stream) {
+    check_shape(shape);
+    if (n_rows == 0) return;
+    if (rows == nullptr || q == nullptr || k_arena == nullptr || v_arena == nullptr || gate.data == nullptr || out == nullptr)
+        throw std::invalid_argument("sepal_b200 attention: null pointer");
+    if (q_stride % 8 != 0 || out_stride % 8 != 0 || reinterpret_cast<std::uintptr_t>(q) % 16 != 0 || reinterpret_cast<std::uintptr_t>(out) % 16 != 0 ||
+        reinterpret_cast<std::uintptr_t>(k_arena) % 16 != 0 || reinterpret_cast<std::uintptr_t>(v_arena) % 16 != 0)
+        throw std::invalid_argument("sepal_b200 attention: q, out and the arenas must be 16-byte aligned with row strides that are multiples of 8");
+    check_rows(rows, n_rows, n_tokens, arena_tokens);
+    check(cudaSetDevice(ctx.device), "cudaSetDevice");
+    const unsigned D = shape.head_dim;
+    const unsigned keys = D == 128 ? 128u : 64u;
+    // (row, query block) pairs, the ones with the most keys first: they take longest
+    struct Block {
+        unsigned row, qb, work;
+    };
+    std::vector<Block> blocks;
+    for (std::size_t i = 0; i < n_rows; ++i)
+        for (unsigned qb = 0; qb * kQueries < rows[i].length; ++qb) blocks.push_back({static_cast<unsigned>(i), qb, rows[i].context + (qb + 1) * kQueries});
+    std::stable_sort(blocks.begin(), blocks.end(), [](const Block& a, const Block& b) { return a.work > b.work; });
+    std::vector<unsigned> table(2 * blocks.size());
+    for (std::size_t i = 0; i < blocks.size(); ++i) {
+        table[2 * i] = blocks[i].row;
+        table[2 * i + 1] = blocks[i].qb;
+    }
+    const void* table_dev = nullptr;
+    AttentionParams p{};
+    p.rows = upload_rows(ctx, rows, n_rows, table.data(), table.size() * sizeof(unsigned), &table_dev, stream);
+    p.blocks = static_cast<const unsigned*>(table_dev);
+    p.heads = shape.heads;
+    p.group = shape.heads / shape.kv_heads;
+    p.scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(D)));
+    p.gate = gate.data;
+    p.gate_stride = gate.stride;
+    p.gate_half = gate.half ? 1u : 0u;
+    p.out = static_cast<__half*>(out);
+    p.out_stride = out_stride;
+    p.status = ctx.status;
+    const std::size_t kv_cols = static_cast<std::size_t>(shape.kv_heads) * D;
+    const CUtensorMap map_q = make_tensor_map_2d(ctx, q, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_tokens, static_cast<std::size_t>(shape.heads) * D, q_stride, kQueries, 64, true);
+    const CUtensorMap map_k = make_tensor_map_2d(ctx, k_arena, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, arena_tokens, kv_cols, kv_cols, keys, 64, true);
+    const CUtensorMap map_v = make_tensor_map_2d(ctx, v_arena, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, arena_tokens, kv_cols, kv_cols, keys, 64, true);
+    const dim3 grid(static_cast<unsigned>(blocks.size()), shape.heads);
+    if (D == 128) {
+        static bool configured[64] = {};
+        if (ctx.device >= 64 || !configured[ctx.device]) {
+            check(cudaFuncSetAttribute(attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttentionTile<128>::kSmem), "cudaFuncSetAttribute");
+            if (ctx.device < 64) configured[ctx.device] = true;
+        }
+        launch_kernel(attention_kernel<128>, grid, dim3(192), AttentionTile<128>::kSmem, stream, "attention_kernel launch", map_q, map_k, map_v, p);
+    } else {
+        static bool configured[64] = {};
+        if (ctx.device >= 64 || !configured[ctx.device]) {
+            check(cudaFuncSetAttribute(attention_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttentionTile<256>::kSmem), "cudaFuncSetAttribute");
+            if (ctx.device < 64) configured[ctx.device] = true;
+        }
+        launch_kernel(attention_kernel<256>, grid, dim3(192), AttentionTile<256>::kSmem, stream, "attention_kernel launch", map_q, map_k, map_v, p);
+    }
+    count_launch();
+}
+
+}  // namespace sepal::b200

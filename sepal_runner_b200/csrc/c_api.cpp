@@ -12,6 +12,7 @@
 #include <string>
 #include <vector>
 
+#include "attention.hpp"
 #include "checkpoint.hpp"
 #include "gemm.hpp"
 #include "model.hpp"
@@ -250,6 +251,43 @@ struct sepal_b200_checkpoint {
     std::shared_ptr<const Checkpoint> checkpoint;
     std::vector<std::string> names;  // engine names, sorted
 };
+
+namespace {
+AttentionShape attention_shape_of(const sepal_b200_attention_shape& s) {
+    AttentionShape a;
+    a.heads = s.heads;
+    a.kv_heads = s.kv_heads;
+    a.head_dim = s.head_dim;
+    a.rotary_dims = s.rotary_dims;
+    a.rope_theta = s.rope_theta;
+    a.eps = s.eps;
+    return a;
+}
+static_assert(sizeof(sepal_b200_attention_row) == sizeof(AttentionRow), "the row tables must have one layout");
+}  // namespace
+
+int32_t sepal_b200_attention_prepare(sepal_b200_ctx* ctx, const sepal_b200_attention_shape* shape, const sepal_b200_attention_row* rows, uint64_t n_rows,
+                                     const void* q_gate, uint64_t q_gate_stride, int32_t q_gate_half, const void* k, uint64_t k_stride, int32_t k_half,
+                                     const void* v, uint64_t v_stride, int32_t v_half, const float* q_norm, const float* k_norm, void* q_out,
+                                     uint64_t q_stride, void* k_arena, void* v_arena, uint64_t arena_tokens, void* stream) {
+    return guarded([&] {
+        require(ctx, "ctx");
+        require(shape, "shape");
+        launch_attention_prepare(ctx->ctx, attention_shape_of(*shape), reinterpret_cast<const AttentionRow*>(rows), n_rows, Band{q_gate, q_gate_stride, q_gate_half != 0},
+                                 Band{k, k_stride, k_half != 0}, Band{v, v_stride, v_half != 0}, q_norm, k_norm, q_out, q_stride, k_arena, v_arena, arena_tokens,
+                                 static_cast<cudaStream_t>(stream));
+    });
+}
+int32_t sepal_b200_attention(sepal_b200_ctx* ctx, const sepal_b200_attention_shape* shape, const sepal_b200_attention_row* rows, uint64_t n_rows,
+                             uint64_t n_tokens, const void* q, uint64_t q_stride, const void* k_arena, const void* v_arena, uint64_t arena_tokens,
+                             const void* gate, uint64_t gate_stride, int32_t gate_half, void* out, uint64_t out_stride, void* stream) {
+    return guarded([&] {
+        require(ctx, "ctx");
+        require(shape, "shape");
+        launch_attention(ctx->ctx, attention_shape_of(*shape), reinterpret_cast<const AttentionRow*>(rows), n_rows, n_tokens, q, q_stride, k_arena, v_arena,
+                         arena_tokens, Band{gate, gate_stride, gate_half != 0}, out, out_stride, static_cast<cudaStream_t>(stream));
+    });
+}
 
 int32_t sepal_b200_trunk_open(int32_t device, const sepal_b200_trunk_config* config, sepal_b200_trunk** out) {
     if (out != nullptr) *out = nullptr;

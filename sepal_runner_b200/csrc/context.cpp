@@ -55,6 +55,8 @@ Context::Context(int device_, std::size_t workspace_bytes) : device(device_) {
         const float one = 1.0f;
         check(cudaMemcpy(unit_scales, ones.data(), kUnitScales * 2, cudaMemcpyHostToDevice), "cudaMemcpy(unit scales)");
         check(cudaMemcpy(unit, &one, sizeof one, cudaMemcpyHostToDevice), "cudaMemcpy(unit)");
+        table_bytes = std::size_t{4} << 20;
+        check(cudaMalloc(&table, table_bytes), "cudaMalloc(table)");
     }
     check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
 }
@@ -89,6 +91,7 @@ Context::~Context() {
     if (status != nullptr) cudaFree(status);
     if (unit_scales != nullptr) cudaFree(unit_scales);
     if (unit != nullptr) cudaFree(unit);
+    if (table != nullptr) cudaFree(table);
     if (status_host != nullptr) cudaFreeHost(status_host);
 }
 

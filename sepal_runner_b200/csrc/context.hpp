@@ -44,6 +44,9 @@ struct Context {
     void* unit_scales = nullptr;  // kUnitScales binary16 ones: the scale table of an int8 multiply whose scales are applied per output column
     float* unit = nullptr;        // device float 1.0
     static constexpr std::size_t kUnitScales = 1u << 16;
+    void* table = nullptr;        // device memory for the small per-launch tables of the attention kernels (rows, block lists)
+    std::size_t table_bytes = 0;
+    unsigned table_turn = 0;
 
     Context(int device, std::size_t workspace_bytes);
     /// A context over device memory that somebody else owns: nothing is allocated here, and such a context must never be destroyed

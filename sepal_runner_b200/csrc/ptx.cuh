@@ -120,6 +120,18 @@ __device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
                  : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The store that mirrors tmem_ld_32x32: register j of thread i goes to lane (base lane + i), column (base column + j).
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+          "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+          "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- MMA ---------------------------------------------------------------------------------------------------------------
 
@@ -147,6 +159,24 @@ __host__ __device__ constexpr uint32_t instr_desc_f16_f32acc(uint32_t m, uint32_
            | (0u << 16)         // B K-major
            | ((n >> 3) << 17)   // N / 8
            | ((m >> 4) << 24);  // M / 16
+}
+
+// The descriptor of an MN-major operand tile with the 128-byte swizzle: what TMA loads of [k rows, 64 x 2-byte] boxes leave when the
+// matrix in memory has the operand's k as its rows (V [keys, head_dim] as the B operand of P V). A row of k is 128 bytes = 64 values
+// along n; 8 rows of k are one 1024-byte swizzle atom (stride byte offset between atoms along k: 1024); the next 64 values along n are
+// the next box, `n_group_bytes` further (leading byte offset). A step of 16 along k is +2048 bytes on the start address.
+__device__ __forceinline__ uint64_t smem_desc_mn_major_sw128(uint32_t addr, uint32_t n_group_bytes) {
+    uint64_t desc = 0;
+    desc |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+    desc |= static_cast<uint64_t>((n_group_bytes >> 4) & 0x3FFFu) << 16;
+    desc |= static_cast<uint64_t>(1024 >> 4) << 32;
+    desc |= static_cast<uint64_t>(1) << 46;
+    desc |= static_cast<uint64_t>(2) << 61;
+    return desc;
+}
+// instr_desc_f16_f32acc with the B operand MN-major (bit 16).
+__host__ __device__ constexpr uint32_t instr_desc_f16_f32acc_b_mn(uint32_t m, uint32_t n) {
+    return (1u << 4) | (1u << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 // D[tmem] (+)= A[smem] B[smem]^T, issued by ONE thread. `accumulate` == 0 overwrites D.

@@ -55,6 +55,8 @@ SIGNATURES = {
     "sepal_b200_trunk_open": (_i32, [_i32, _vp, C.POINTER(_vp)]),
     "sepal_b200_trunk_close": (None, [_vp]),
     "sepal_b200_set_launch_overlap": (None, [_i32]),
+    "sepal_b200_attention_prepare": (_i32, [_vp, _vp, _vp, _u64, _vp, _u64, _i32, _vp, _u64, _i32, _vp, _u64, _i32, _vp, _vp, _vp, _u64, _vp, _vp, _u64, _vp]),
+    "sepal_b200_attention": (_i32, [_vp, _vp, _vp, _u64, _u64, _vp, _u64, _vp, _vp, _u64, _vp, _u64, _i32, _vp, _u64, _vp]),
     "sepal_b200_trunk_open_checkpoint": (_i32, [_i32, _vp, _vp, _vp]),
     "sepal_b200_trunk_save": (_i32, [_vp, C.c_char_p]),
     "sepal_b200_checkpoint_open": (_i32, [C.c_char_p, _vp]),
@@ -277,6 +279,40 @@ class Context:
     @staticmethod
     def take_launch_count() -> int:
         return int(library().sepal_b200_take_launch_count())
+
+
+class AttentionShape(C.Structure):
+    """sepal_b200_attention_shape."""
+
+    _fields_ = [("heads", _u32), ("kv_heads", _u32), ("head_dim", _u32), ("rotary_dims", _u32), ("rope_theta", C.c_double), ("eps", C.c_float),
+                ("reserved", _u32)]
+
+
+class AttentionRow(C.Structure):
+    """sepal_b200_attention_row."""
+
+    _fields_ = [("q_begin", _u32), ("length", _u32), ("kv_begin", _u32), ("context", _u32)]
+
+
+def attention_prepare(ctx, shape, rows, q_gate, k, v, q_norm, k_norm, q_out, k_arena, v_arena, stream=None):
+    """Norm, RoPE and cache append (sepal_b200_attention_prepare). rows: list of (q_begin, length, kv_begin, context); torch tensors."""
+    import torch
+
+    table = (AttentionRow * len(rows))(*[AttentionRow(*r) for r in rows])
+    half = lambda t: 1 if t.dtype == torch.float16 else 0  # noqa: E731
+    _check(ctx._lib.sepal_b200_attention_prepare(ctx._h, C.byref(shape), table, len(rows), q_gate.data_ptr(), q_gate.stride(0), half(q_gate), k.data_ptr(),
+                                                 k.stride(0), half(k), v.data_ptr(), v.stride(0), half(v), q_norm.data_ptr(), k_norm.data_ptr(),
+                                                 q_out.data_ptr(), q_out.stride(0), k_arena.data_ptr(), v_arena.data_ptr(), k_arena.shape[0], _stream_ptr(stream)))
+
+
+def attention(ctx, shape, rows, q, k_arena, v_arena, gate, out, stream=None):
+    """Causal grouped-query flash attention times sigmoid(gate) (sepal_b200_attention)."""
+    import torch
+
+    table = (AttentionRow * len(rows))(*[AttentionRow(*r) for r in rows])
+    _check(ctx._lib.sepal_b200_attention(ctx._h, C.byref(shape), table, len(rows), q.shape[0], q.data_ptr(), q.stride(0), k_arena.data_ptr(), v_arena.data_ptr(),
+                                         k_arena.shape[0], gate.data_ptr(), gate.stride(0), 1 if gate.dtype == torch.float16 else 0, out.data_ptr(),
+                                         out.stride(0), _stream_ptr(stream)))
 
 
 class TrunkConfig(C.Structure):

@@ -133,6 +133,13 @@ __global__ void __launch_bounds__(256) attention_prepare_kernel(const PreparePar
 
 // ---- attention -------------------------------------------------------------------------------------------------------------------
 
+// 2^x by the special-function unit (two units in the last place; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 struct AttentionParams {
     const AttentionRow* rows;
     const unsigned* blocks;  // (row, query block) pairs, heaviest first
@@ -154,17 +161,17 @@ struct AttentionTile {
     static constexpr int kKvBytes = kKeys * D * 2;             // one K tile or one V tile
     static constexpr int kPBytes = kQueries * kKeys * 2;
     static constexpr int kStages = 2;
-    static constexpr int kSmem = 1024 + kQBytes + kStages * 2 * kKvBytes + kPBytes + 256;
+    static constexpr int kSmem = 1024 + kQBytes + kStages * 2 * kKvBytes + 2 * kPBytes + 256 + 1024;  // two P buffers; barriers; the halves' exchange
     static constexpr int kSCols = kKeys;                       // tensor-memory columns of one score buffer
     static constexpr int kOCol = 2 * kKeys;                    // where the output accumulator starts
 };
 
 // Warp 0: TMA (Q once, then K and V blocks into a ring of two). Warp 1: MMA issuer: S_j = Q K_j^T into one of two score buffers (S_{j+1}
-// is issued before P_j V_j, so the tensor core has work while the softmax of block j runs), then O += P_j V_j. Warps 2-5: one query per
-// thread: scores from tensor memory, masked, running maximum and sum in the base-2 domain, P_j as binary16 into shared memory in the
+// is issued before P_j V_j, so the tensor core has work while the softmax of block j runs), then O += P_j V_j. Warps 2-9: one query per
+// thread pair: scores from tensor memory, masked, running maximum and sum in the base-2 domain, P_j as binary16 into shared memory in the
 // layout the MMA reads, O rescaled in tensor memory when the maximum moved; at the end O / l * sigmoid(gate).
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                  const AttentionParams p) {
     using T = AttentionTile<D>;
@@ -177,16 +184,19 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const uint32_t kv_addr = base + T::kQBytes;  // stage s: K at kv_addr + s * 2 * kKvBytes, V right after it
     const uint32_t p_addr = kv_addr + T::kStages * 2 * T::kKvBytes;
     uint8_t* const p_smem = smem + (p_addr - base);
-    uint8_t* const tail = smem + (p_addr - base) + T::kPBytes;
+    uint8_t* const tail = smem + (p_addr - base) + 2 * T::kPBytes;
     const uint32_t bars = ptx::smem_addr(tail);
-    const uint32_t q_full = bars, p_full = bars + 8, pv_done = bars + 16;
+    const uint32_t q_full = bars;
+    const auto p_full = [&](int b) { return bars + 8u + 8u * b; };    // P_j is written (j & 1 picks the buffer)
     const auto kv_full = [&](int s) { return bars + 24u + 8u * s; };
     const auto kv_empty = [&](int s) { return bars + 40u + 8u * s; };
     const auto s_full = [&](int b) { return bars + 56u + 8u * b; };
     const auto s_free = [&](int b) { return bars + 72u + 8u * b; };
-    unsigned* const words = reinterpret_cast<unsigned*>(tail + 96);
+    const auto p_free = [&](int b) { return bars + 88u + 8u * b; };   // P_j V_j has finished: buffer j & 1 is free, and O holds blocks 0 .. j
+    unsigned* const words = reinterpret_cast<unsigned*>(tail + 112);
     unsigned* const tmem_slot = words;
     volatile unsigned* const abort_flag = words + 1;
+    float* const exchange = reinterpret_cast<float*>(tail + 256);  // 2 x 128 floats: what the two halves of a query tell each other
 
     const unsigned warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const unsigned head = blockIdx.y, kv_head = head / p.group;
@@ -200,13 +210,13 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(q_full, 1);
-        ptx::mbar_init(p_full, 128);
-        ptx::mbar_init(pv_done, 1);
         for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(p_full(s), 256);
+            ptx::mbar_init(p_free(s), 1);
             ptx::mbar_init(kv_full(s), 1);
             ptx::mbar_init(kv_empty(s), 1);
             ptx::mbar_init(s_full(s), 1);
-            ptx::mbar_init(s_free(s), 128);
+            ptx::mbar_init(s_free(s), 256);
         }
         words[1] = 0;
         ptx::fence_barrier_init();
@@ -274,26 +284,35 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     ptx::tc_fence_after_sync();
                     issue_scores(n);
                 }
-                ok = wait_barrier(p_full, j & 1u, abort_flag, p.status, kStatusAttention + 4);
+                ok = wait_barrier(p_full(s), (j >> 1) & 1u, abort_flag, p.status, kStatusAttention + 4);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 const uint32_t v_tile = kv_addr + s * 2 * T::kKvBytes + T::kKvBytes;
 #pragma unroll
                 for (int kb = 0; kb < kKeys / 16; ++kb) {
-                    const uint64_t dp = ptx::smem_desc_k_major_sw128(p_addr + (kb / 4) * (kQueries * 128)) + 2u * (kb % 4);
+                    const uint64_t dp = ptx::smem_desc_k_major_sw128(p_addr + s * T::kPBytes + (kb / 4) * (kQueries * 128)) + 2u * (kb % 4);
                     const uint64_t dv = ptx::smem_desc_mn_major_sw128(v_tile + kb * 2048, kKeys * 128);
                     ptx::mma_f16_ss(o_tmem, dp, dv, idesc_o, (j > 0 || kb > 0) ? 1u : 0u);
                 }
                 ptx::mma_commit(kv_empty(s));
-                ptx::mma_commit(pv_done);
+                ptx::mma_commit(p_free(s));
             }
         }
         __syncwarp();
     } else {
+        // Eight warps: warps w and w + 4 share the 32 queries of tensor-memory lanes 32 (w % 4) ..., each taking half of a block's keys
+        // (and later half of the head's dimensions), so that two warps per scheduler hide each other's latencies.
+        constexpr int kW = kKeys / 2;                 // keys of a block per thread
+        constexpr int kDh = D / 2;                    // output dimensions per thread
         const unsigned quarter = warp % 4;
-        const unsigned r = quarter * 32 + lane;  // this thread's query inside the block
+        const unsigned side = (warp - 2) / 4;         // which half
+        const unsigned r = quarter * 32 + lane;       // this thread's query inside the block
         const uint32_t lane_base = tmem_base + ((quarter * 32u) << 16);
         const unsigned q_index = row.context + q0 + r;  // the last key this query sees
+        const auto pair_sync = [&] { asm volatile("bar.sync %0, 64;" ::"r"(2u + quarter) : "memory"); };
+        // Running state in the base-2 domain: the reference maximum m (the row's probabilities are exp2(t - m)) and the sum l of this
+        // thread's half of them. m follows the true maximum lazily: it moves only when the maximum has grown by more than 8, so a
+        // probability is at most 2^8 (binary16 holds it with its full relative precision) and O is rescaled only then. O / l does not care.
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
         for (unsigned j = 0; j < n_blocks; ++j) {
@@ -301,97 +320,105 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             ok = wait_barrier(s_full(s), (j >> 1) & 1u, abort_flag, p.status, kStatusAttention + 5);
             if (!ok) break;
             ptx::tc_fence_after_sync();
-            const uint32_t s_tmem = lane_base + s * T::kSCols;
-            const unsigned key0 = j * kKeys;
-            const bool diagonal = key0 + kKeys - 1 > row.context + q0;  // some key of the block is hidden from some query
-            // pass 1: the block's maximum for this query
-            float block_max = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < kKeys; c += 32) {
+            const unsigned key0 = j * kKeys + side * kW;  // this thread's first key of the block
+            const bool diagonal = j * kKeys + kKeys - 1 > row.context + q0;  // some key of the block is hidden from some query
+            float t[kW];
+#pragma unroll
+            for (int c = 0; c < kW; c += 32) {
                 uint32_t v[32];
-                ptx::tmem_ld_32x32(s_tmem + c, v);
+                ptx::tmem_ld_32x32(lane_base + s * T::kSCols + side * kW + c, v);
                 ptx::tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float t = __uint_as_float(v[i]) * p.scale_log2;
-                    if (!diagonal || key0 + c + i <= q_index) block_max = fmaxf(block_max, t);
-                }
-            }
-            const float m_new = fmaxf(m, block_max);
-            const float alpha = exp2f(m - m_new);  // 0 at the first block (m = -inf), 1 when the maximum did not move
-            // P_j may be written and O rescaled only when P_{j-1} V_{j-1} has finished
-            if (j > 0) {
-                ok = wait_barrier(pv_done, (j - 1) & 1u, abort_flag, p.status, kStatusAttention + 6);
-                if (!ok) break;
-                ptx::tc_fence_after_sync();
-            }
-            // pass 2: probabilities, their sum, P as binary16 in the swizzled K-major layout (row r, 16-byte chunk c8 of box c8 / 8)
-            float sum = 0.0f;
-#pragma unroll 1
-            for (int c = 0; c < kKeys; c += 32) {
-                uint32_t v[32];
-                ptx::tmem_ld_32x32(s_tmem + c, v);
-                ptx::tmem_ld_wait();
-                unsigned packed[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float e0 = exp2f(__uint_as_float(v[i]) * p.scale_log2 - m_new);
-                    float e1 = exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - m_new);
-                    if (diagonal) {
-                        if (key0 + c + i > q_index) e0 = 0.0f;
-                        if (key0 + c + i + 1 > q_index) e1 = 0.0f;
-                    }
-                    const __half2 h = __floats2half2_rn(e0, e1);
-                    // the sum is taken over what the tensor core will multiply: the rounded probabilities
-                    const float2 back = __half22float2(h);
-                    sum += back.x + back.y;
-                    packed[i / 2] = *reinterpret_cast<const unsigned*>(&h);
-                }
-                uint8_t* box = p_smem + (c / 64) * (kQueries * 128) + r * 128;
-                const unsigned chunk0 = (c % 64) / 8;
-#pragma unroll
-                for (unsigned q = 0; q < 4; ++q)
-                    *reinterpret_cast<uint4*>(box + (((chunk0 + q) ^ (r & 7u)) * 16)) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                for (int i = 0; i < 32; ++i) t[c + i] = __uint_as_float(v[i]);
             }
             ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(s_free(s));  // the scores of this buffer have been read twice: it may be overwritten
-            // rescale O where the maximum moved (a warp's loads and stores of tensor memory are collective: all lanes go together)
+            ptx::mbar_arrive(s_free(s));  // the scores are in registers: the buffer may be overwritten
+            if (diagonal) {
+#pragma unroll
+                for (int i = 0; i < kW; ++i)
+                    if (key0 + i > q_index) t[i] = -INFINITY;
+            }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < kW; ++i) mx[i & 3] = fmaxf(mx[i & 3], t[i]);
+            const float mine = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            exchange[side * 128 + r] = mine;
+            pair_sync();
+            const float block_max = fmaxf(mine, exchange[(side ^ 1u) * 128 + r]) * p.scale_log2;
+            pair_sync();  // both have read: the next block may overwrite
+            float alpha = 1.0f;
+            if (block_max > m + 8.0f) {  // also the first block (m = -inf), where alpha is 0 and O is not touched
+                alpha = fast_exp2(m - block_max);
+                m = block_max;
+            }
+            // P buffer j & 1 was last read by P_{j-2} V_{j-2}
+            if (j >= 2) {
+                ok = wait_barrier(p_free(s), ((j >> 1) - 1) & 1u, abort_flag, p.status, kStatusAttention + 6);
+                if (!ok) break;
+            }
+            // probabilities (a hidden key: exp2(-inf) = 0), their sum, P as binary16 in the swizzled K-major layout
+            float sum[2] = {0.0f, 0.0f};
+            uint8_t* const p_row = p_smem + s * T::kPBytes + r * 128;
+#pragma unroll
+            for (int c = 0; c < kW; c += 8) {
+                unsigned packed[4];
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    const float e0 = fast_exp2(__fmaf_rn(t[c + i], p.scale_log2, -m));
+                    const float e1 = fast_exp2(__fmaf_rn(t[c + i + 1], p.scale_log2, -m));
+                    sum[0] += e0;
+                    sum[1] += e1;
+                    const __half2 h = __floats2half2_rn(e0, e1);
+                    packed[i / 2] = *reinterpret_cast<const unsigned*>(&h);
+                }
+                const unsigned col = side * kW + c;  // column of the block: box col / 64, 16-byte chunk (col % 64) / 8
+                *reinterpret_cast<uint4*>(p_row + (col / 64) * (kQueries * 128) + ((((col % 64) / 8) ^ (r & 7u)) * 16)) =
+                    make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            // rescale this thread's half of O where the reference maximum moved (a warp's loads and stores of tensor memory are
+            // collective: all lanes go together); O must hold P_{j-1} V_{j-1} first
             if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
+                ok = wait_barrier(p_free(s ^ 1), ((j - 1) >> 1) & 1u, abort_flag, p.status, kStatusAttention + 6);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
 #pragma unroll 1
-                for (int c = 0; c < D; c += 32) {
+                for (int c = 0; c < kDh; c += 32) {
                     uint32_t v[32];
-                    ptx::tmem_ld_32x32(lane_base + T::kOCol + c, v);
+                    ptx::tmem_ld_32x32(lane_base + T::kOCol + side * kDh + c, v);
                     ptx::tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                    ptx::tmem_st_32x32(lane_base + T::kOCol + c, v);
+                    ptx::tmem_st_32x32(lane_base + T::kOCol + side * kDh + c, v);
                 }
                 ptx::tmem_st_wait();
             }
-            l = l * alpha + sum;
-            m = m_new;
+            l = l * alpha + (sum[0] + sum[1]);
             ptx::fence_proxy_async_smem();  // P was written with ordinary stores; the MMA reads it through the async proxy
             ptx::tc_fence_before_sync();
-            ptx::mbar_arrive(p_full);
+            ptx::mbar_arrive(p_full(s));
         }
-        if (ok && n_blocks > 0) ok = wait_barrier(pv_done, (n_blocks - 1) & 1u, abort_flag, p.status, kStatusAttention + 7);
+        if (ok && n_blocks > 0) ok = wait_barrier(p_free((n_blocks - 1) & 1u), ((n_blocks - 1) >> 1) & 1u, abort_flag, p.status, kStatusAttention + 7);
+        // the row's sum: the first half's plus the second half's
+        exchange[side * 128 + r] = l;
+        pair_sync();
+        const float total = exchange[r] + exchange[128 + r];
         // every lane takes part in the loads; only valid queries store
         if (ok) {
             ptx::tc_fence_after_sync();
-            const float inv_l = 1.0f / l;
+            const float inv_l = 1.0f / total;
             const size_t token = static_cast<size_t>(row.q_begin) + q0 + r;
-            __half* dst = p.out + token * p.out_stride + static_cast<size_t>(head) * D;
+            __half* dst = p.out + token * p.out_stride + static_cast<size_t>(head) * D + side * kDh;
+            const size_t gate0 = token * p.gate_stride + static_cast<size_t>(head) * 2 * D + D + side * kDh;
 #pragma unroll 1
-            for (int c = 0; c < D; c += 32) {
+            for (int c = 0; c < kDh; c += 32) {
                 uint32_t v[32];
-                ptx::tmem_ld_32x32(lane_base + T::kOCol + c, v);
+                ptx::tmem_ld_32x32(lane_base + T::kOCol + side * kDh + c, v);
                 ptx::tmem_ld_wait();
                 if (r < valid) {
                     unsigned packed[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        const size_t g = token * p.gate_stride + static_cast<size_t>(head) * 2 * D + D + c + i;
-                        const float g0 = band_value(p.gate, g, p.gate_half), g1 = band_value(p.gate, g + 1, p.gate_half);
+                        const float g0 = band_value(p.gate, gate0 + c + i, p.gate_half), g1 = band_value(p.gate, gate0 + c + i + 1, p.gate_half);
                         const float o0 = __uint_as_float(v[i]) * inv_l * (1.0f / (1.0f + expf(-g0)));
                         const float o1 = __uint_as_float(v[i + 1]) * inv_l * (1.0f / (1.0f + expf(-g1)));
                         const __half2 h = __floats2half2_rn(o0, o1);
@@ -547,14 +574,14 @@ void launch_attention(Context& ctx, const AttentionShape& shape, const Attention
             check(cudaFuncSetAttribute(attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttentionTile<128>::kSmem), "cudaFuncSetAttribute");
             if (ctx.device < 64) configured[ctx.device] = true;
         }
-        launch_kernel(attention_kernel<128>, grid, dim3(192), AttentionTile<128>::kSmem, stream, "attention_kernel launch", map_q, map_k, map_v, p);
+        launch_kernel(attention_kernel<128>, grid, dim3(320), AttentionTile<128>::kSmem, stream, "attention_kernel launch", map_q, map_k, map_v, p);
     } else {
         static bool configured[64] = {};
         if (ctx.device >= 64 || !configured[ctx.device]) {
             check(cudaFuncSetAttribute(attention_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttentionTile<256>::kSmem), "cudaFuncSetAttribute");
             if (ctx.device < 64) configured[ctx.device] = true;
         }
-        launch_kernel(attention_kernel<256>, grid, dim3(192), AttentionTile<256>::kSmem, stream, "attention_kernel launch", map_q, map_k, map_v, p);
+        launch_kernel(attention_kernel<256>, grid, dim3(320), AttentionTile<256>::kSmem, stream, "attention_kernel launch", map_q, map_k, map_v, p);
     }
     count_launch();
 }

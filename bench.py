@@ -462,6 +462,152 @@ def run_serve(args):
         dist.destroy_process_group()
 
 
+def run_attention(args):
+    """The full-attention core of one layer over the 15,900-token log (BASELINE configs[3]'s request) as four chained calls of 4096 / 4096 /
+    4096 / 3612 tokens: norm + RoPE + cache append, then causal grouped-query flash attention times the output gate. A step is the four
+    calls. Heads: 16 query / 4 key-value heads of 256 (the served models' attention geometry); --heads128 runs 32 / 8 heads of 128."""
+    import torch
+
+    import sepal_runner_b200 as sb
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    heads, kvh, hd, rot = (32, 8, 128, 32) if args.heads128 else (16, 4, 256, 64)
+    shape = sb.AttentionShape(heads=heads, kv_heads=kvh, head_dim=hd, rotary_dims=rot, rope_theta=1.0e7, eps=1e-6)
+    ctx = sb.Context(local)
+    total, chunk = 15900, 4096
+    gen = torch.Generator(device=device).manual_seed(4004 + rank)
+    qg = (torch.randn((total, 2 * heads * hd), generator=gen, device=device) * 1.0).half()
+    k = torch.randn((total, kvh * hd), generator=gen, device=device).half()
+    v = torch.randn((total, kvh * hd), generator=gen, device=device).half()
+    w = (torch.randn(hd, generator=gen, device=device) * 0.1).float()
+    k_arena = torch.zeros((total, kvh * hd), dtype=torch.float16, device=device)
+    v_arena = torch.zeros_like(k_arena)
+    q_out = torch.empty((chunk, heads * hd), dtype=torch.float16, device=device)
+    out = torch.empty((total, heads * hd), dtype=torch.float16, device=device)
+    calls = [(at, min(chunk, total - at)) for at in range(0, total, chunk)]
+    pairs = sum(n * at + n * (n + 1) // 2 for at, n in calls)
+    flops = 4.0 * hd * pairs * heads  # Q K^T and P V over the visible (query, key) pairs
+
+    def step():
+        for at, n in calls:
+            rows = [(0, n, 0, at)]
+            sb.attention_prepare(ctx, shape, rows, qg[at:at + n], k[at:at + n], v[at:at + n], w, w, q_out[:n], k_arena, v_arena)
+            sb.attention(ctx, shape, rows, q_out[:n], k_arena, v_arena, qg[at:at + n], out[at:at + n])
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for _ in range(args.warmup):
+        step()
+    ctx.check_status()
+    ctx.take_launch_count()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    elapsed_ms = e0.elapsed_time(e1)
+    launches = ctx.take_launch_count()
+    ctx.check_status()
+    # the attention launches alone (the number the roofline is about)
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    attn_ms = 0.0
+    for at, n in calls:
+        rows = [(0, n, 0, at)]
+        sb.attention_prepare(ctx, shape, rows, qg[at:at + n], k[at:at + n], v[at:at + n], w, w, q_out[:n], k_arena, v_arena)
+        a0.record()
+        for _ in range(3):
+            sb.attention(ctx, shape, rows, q_out[:n], k_arena, v_arena, qg[at:at + n], out[at:at + n])
+        a1.record()
+        torch.cuda.synchronize()
+        attn_ms += a0.elapsed_time(a1) / 3
+    # end to end: the projections' outputs in pinned host memory in, the o_proj operand back out, copies inside the timed region
+    h_qg, h_k, h_v = qg.cpu().pin_memory(), k.cpu().pin_memory(), v.cpu().pin_memory()
+    h_out = torch.empty((total, heads * hd), dtype=torch.float16).pin_memory()
+    d_qg, d_k, d_v = torch.empty_like(qg[:chunk]), torch.empty_like(k[:chunk]), torch.empty_like(v[:chunk])
+
+    def e2e_step():
+        for at, n in calls:
+            d_qg[:n].copy_(h_qg[at:at + n], non_blocking=True)
+            d_k[:n].copy_(h_k[at:at + n], non_blocking=True)
+            d_v[:n].copy_(h_v[at:at + n], non_blocking=True)
+            rows = [(0, n, 0, at)]
+            sb.attention_prepare(ctx, shape, rows, d_qg[:n], d_k[:n], d_v[:n], w, w, q_out[:n], k_arena, v_arena)
+            sb.attention(ctx, shape, rows, q_out[:n], k_arena, v_arena, d_qg[:n], out[at:at + n])
+            h_out[at:at + n].copy_(out[at:at + n], non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e2e_steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    sampler.stop_flag.set()
+    sampler.join(timeout=2)
+    times = torch.tensor([elapsed_ms, e2e_s * 1e3, attn_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms, attn_ms = float(times[0]), float(times[1]), float(times[2])
+    if rank == 0:
+        peaks, peak_kind = measured_peaks()
+        peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+        step_ms = elapsed_ms / args.steps
+        kernel_tf = flops / (attn_ms * 1e-3) / 1e12
+        line = {
+            "metric": "attention core TFLOP/s (causal grouped-query, 15,900-token log in four chained calls)",
+            "value": round(flops / (step_ms * 1e-3) / 1e12 * world, 2),
+            "unit": "TFLOP/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": round(step_ms, 4),
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "f16 x f16 -> f32 accumulate, f32 softmax",
+            "data": "synthetic",
+            "config": {"workload": f"attention: {heads} query / {kvh} key-value heads of {hd}, rotary {rot}, calls of 4096/4096/4096/3612 tokens of one request",
+                       "tokens_per_s": round(total / (step_ms * 1e-3) * world, 1),
+                       "l2": "q, k, v and the cache of a call are 180 to 400 MB: larger than the 126 MiB L2",
+                       "parallelism": f"one request per GPU x{world}, no collective"},
+            "roofline": {"bound": "tensor", "achieved": round(kernel_tf, 2), "peak": peak_tf, "unit": "TFLOP/s", "frac": round(kernel_tf / peak_tf, 4),
+                         "peak_source": f"bf16_tflops of MEASURED_PEAKS.json ({peak_kind}; burst)", "traffic": None,
+                         "kernel": "attention_kernel: algorithmic flops = 4 x head_dim x visible (query, key) pairs x heads; the four launches of a step by CUDA events",
+                         "ms_attention_launches": round(attn_ms, 4)},
+            "e2e": {"value": round(flops / (e2e_ms * 1e-3) / 1e12 * world, 2), "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": total * (2 * heads * hd + 2 * kvh * hd) * 2, "d2h_bytes_per_step": total * heads * hd * 2,
+                    "note": "sepal_b200_attention_prepare + sepal_b200_attention per call, q_gate / k / v from pinned host memory, the gated output back to it"},
+            "gpu_launches": int(launches),
+            "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    ctx.close()
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
 def cpu_baseline(kind, m, n, k, reps: int = 5):
     """The reference's cpu-bf16 packed GEMM on this host's cores, on the same product (int8 weights dequantised to float32 first:
     the reference has no group-128 CPU kernel), weights packed once, best of `reps` (runner/tools/sepal_cpu_gemm_bench.cpp:153-201)."""
@@ -542,7 +688,8 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="w8g_down_m900", choices=sorted(WORKLOADS) + ["serve"])
+    ap.add_argument("--workload", default="w8g_down_m900", choices=sorted(WORKLOADS) + ["serve", "attention"])
+    ap.add_argument("--heads128", action="store_true", help="attention: 32 / 8 heads of 128 instead of 16 / 4 heads of 256")
     ap.add_argument("--int8", action="store_true", help="serve: store the MLP weights as int8 groups")
     ap.add_argument("--no-trunk", dest="trunk", action="store_false", help="skip the whole-trunk passes")
     ap.add_argument("--calls-per-step", type=int, default=32)
@@ -552,11 +699,13 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
-        if args.workload == "serve":
+        if args.workload in ("serve", "attention"):
             args.workload = "w8g_down_m900"
         run_reference(args)
     elif args.workload == "serve":
         run_serve(args)
+    elif args.workload == "attention":
+        run_attention(args)
     else:
         run_ours(args)
 

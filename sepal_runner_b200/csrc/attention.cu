@@ -440,6 +440,299 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
 }
 
+// ---- the same on CTA pairs ---------------------------------------------------------------------------------------------------------
+//
+// One CTA keeps two key/value blocks in flight and needs a new one every thousand cycles of tensor work: the loads do not arrive in
+// time. A pair of CTAs (tcgen05.mma.cta_group::2) takes 256 queries of one head against each block of 128 keys: every CTA holds its own
+// 128 queries, scores and output rows, and loads HALF of the block: 64 of the 128 keys for S = Q K^T (the B operand is split along its
+// rows) and half of the head's dimensions of all 128 values for O += P V (split along the output columns). Twice the work per loaded
+// byte and per stage. The first CTA's MMA thread issues for both; its commits reach both CTAs; arrivals of the second CTA's warps go to
+// the first CTA's barriers.
+template <int D>
+struct AttentionPairTile {
+    static constexpr int kKeys = 128;
+    static constexpr int kStages = D == 128 ? 4 : 2;
+    static constexpr int kPBuffers = D == 128 ? 2 : 1;
+    static constexpr int kQBytes = kQueries * D * 2;
+    static constexpr int kHalfBytes = 128 * D;                 // 64 keys x D, and 128 values x D / 2, in binary16
+    static constexpr int kStageBytes = 2 * kHalfBytes;
+    static constexpr int kPBytes = kQueries * kKeys * 2;
+    static constexpr int kSmem = 1024 + kQBytes + kStages * kStageBytes + kPBuffers * kPBytes + 256 + 1024;
+    static constexpr int kOCol = 256;
+};
+
+template <int D>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
+attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                      const AttentionParams p) {
+    using T = AttentionPairTile<D>;
+    constexpr int kKeys = T::kKeys, kStages = T::kStages, kPBuffers = T::kPBuffers;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_addr(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* const smem = smem_raw + (base - raw_addr);
+    const uint32_t q_addr = base;
+    const uint32_t kv_addr = base + T::kQBytes;  // stage s: this CTA's 64 keys at kv_addr + s * kStageBytes, its half of the values after them
+    const uint32_t p_addr = kv_addr + kStages * T::kStageBytes;
+    uint8_t* const p_smem = smem + (p_addr - base);
+    uint8_t* const tail = smem + (p_addr - base) + kPBuffers * T::kPBytes;
+    const uint32_t bars = ptx::smem_addr(tail);
+    const uint32_t q_full = bars;
+    const auto kv_full = [&](int s) { return bars + 8u + 8u * s; };
+    const auto kv_empty = [&](int s) { return bars + 40u + 8u * s; };
+    const auto s_full = [&](int b) { return bars + 72u + 8u * b; };
+    const auto s_free = [&](int b) { return bars + 88u + 8u * b; };
+    const auto p_full = [&](int b) { return bars + 104u + 8u * b; };
+    const auto p_free = [&](int b) { return bars + 120u + 8u * b; };
+    unsigned* const words = reinterpret_cast<unsigned*>(tail + 136);
+    unsigned* const tmem_slot = words;
+    volatile unsigned* const abort_flag = words + 1;
+    float* const exchange = reinterpret_cast<float*>(tail + 256);
+
+    const unsigned warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const unsigned rank = ptx::cluster_ctarank();
+    const unsigned head = blockIdx.y, kv_head = head / p.group;
+    const unsigned block = blockIdx.x / 2;
+    const AttentionRow row = p.rows[p.blocks[2 * block]];
+    const unsigned qb = p.blocks[2 * block + 1];
+    const unsigned pair_q0 = qb * 2 * kQueries;                         // first query of the pair inside the run
+    const unsigned q0 = pair_q0 + rank * kQueries;                      // and of this CTA
+    const unsigned pair_valid = min(2u * kQueries, row.length - pair_q0);
+    const unsigned valid = pair_valid > rank * kQueries ? min(static_cast<unsigned>(kQueries), pair_valid - rank * kQueries) : 0u;
+    const unsigned n_keys = row.context + pair_q0 + pair_valid;         // keys the pair's last valid query sees
+    const unsigned n_blocks = (n_keys + kKeys - 1) / kKeys;
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(q_full, 1);
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(kv_full(s), 1);
+            ptx::mbar_init(kv_empty(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(s_full(b), 1);
+            ptx::mbar_init(s_free(b), 512);  // the softmax threads of both CTAs (used in the first CTA only)
+            ptx::mbar_init(p_full(b), 512);
+            ptx::mbar_init(p_free(b), 1);
+        }
+        words[1] = 0;
+        ptx::fence_barrier_init();
+        ptx::tma_prefetch_descriptor(&map_q);
+        ptx::tma_prefetch_descriptor(&map_k);
+        ptx::tma_prefetch_descriptor(&map_v);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_addr(tmem_slot), 512);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();  // the partner's barriers exist before anything signals them
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t q_first = ptx::map_to_cta(q_full, 0);
+            if (rank == 0) ptx::mbar_arrive_expect_tx(q_full, 2 * T::kQBytes);
+            for (int b = 0; b < D / 64; ++b)
+                ptx::tma_load_2d_pair(q_addr + b * (kQueries * 128), &map_q, q_first, static_cast<int>(head * D + 64 * b), static_cast<int>(row.q_begin + q0));
+            for (unsigned j = 0; j < n_blocks; ++j) {
+                const int s = static_cast<int>(j % kStages);
+                if (j >= static_cast<unsigned>(kStages) && !wait_barrier(kv_empty(s), ((j / kStages) - 1) & 1u, abort_flag, p.status, kStatusAttention + 0)) break;
+                const uint32_t k_dst = kv_addr + s * T::kStageBytes, v_dst = k_dst + T::kHalfBytes;
+                const uint32_t full_first = ptx::map_to_cta(kv_full(s), 0);
+                if (rank == 0) ptx::mbar_arrive_expect_tx(kv_full(s), 2 * T::kStageBytes);
+                const int key_row = static_cast<int>(row.kv_begin + j * kKeys);
+                for (int b = 0; b < D / 64; ++b)  // this CTA's 64 keys: boxes of [64 keys x 64 dimensions]
+                    ptx::tma_load_2d_pair(k_dst + b * (64 * 128), &map_k, full_first, static_cast<int>(kv_head * D + 64 * b), key_row + static_cast<int>(rank * 64));
+                for (int b = 0; b < D / 128; ++b)  // this CTA's half of the dimensions of all 128 values: boxes of [128 values x 64 dimensions]
+                    ptx::tma_load_2d_pair(v_dst + b * (kKeys * 128), &map_v, full_first, static_cast<int>(kv_head * D + rank * (D / 2) + 64 * b), key_row);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc_s = ptx::instr_desc_f16_f32acc(2 * kQueries, kKeys);
+            const uint32_t idesc_o = ptx::instr_desc_f16_f32acc_b_mn(2 * kQueries, D);
+            const uint32_t o_tmem = tmem_base + T::kOCol;
+            const auto issue_scores = [&](unsigned j) {
+                const int s = static_cast<int>(j % kStages), sb = static_cast<int>(j & 1u);
+                const uint32_t k_tile = kv_addr + s * T::kStageBytes;
+#pragma unroll
+                for (int b = 0; b < D / 64; ++b) {
+                    const uint64_t dq = ptx::smem_desc_k_major_sw128(q_addr + b * (kQueries * 128));
+                    const uint64_t dk = ptx::smem_desc_k_major_sw128(k_tile + b * (64 * 128));
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) ptx::mma_f16_ss_pair(tmem_base + sb * kKeys, dq + 2u * kk, dk + 2u * kk, idesc_s, (b | kk) != 0 ? 1u : 0u);
+                }
+                ptx::mma_commit_pair(s_full(sb), 3);
+            };
+            bool ok = wait_barrier(q_full, 0, abort_flag, p.status, kStatusAttention + 1) && wait_barrier(kv_full(0), 0, abort_flag, p.status, kStatusAttention + 1);
+            if (ok) {
+                ptx::tc_fence_after_sync();
+                issue_scores(0);
+            }
+            for (unsigned j = 0; ok && j < n_blocks; ++j) {
+                const int s = static_cast<int>(j % kStages), pb = static_cast<int>(j % kPBuffers);
+                if (j + 1 < n_blocks) {
+                    const unsigned n = j + 1;
+                    ok = wait_barrier(kv_full(n % kStages), (n / kStages) & 1u, abort_flag, p.status, kStatusAttention + 2);
+                    if (ok && n >= 2) ok = wait_barrier(s_free(n & 1u), ((n >> 1) - 1) & 1u, abort_flag, p.status, kStatusAttention + 3);
+                    if (!ok) break;
+                    ptx::tc_fence_after_sync();
+                    issue_scores(n);
+                }
+                ok = wait_barrier(p_full(pb), (j / kPBuffers) & 1u, abort_flag, p.status, kStatusAttention + 4);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t v_tile = kv_addr + s * T::kStageBytes + T::kHalfBytes;
+#pragma unroll
+                for (int kb = 0; kb < kKeys / 16; ++kb) {
+                    const uint64_t dp = ptx::smem_desc_k_major_sw128(p_addr + pb * T::kPBytes + (kb / 4) * (kQueries * 128)) + 2u * (kb % 4);
+                    const uint64_t dv = ptx::smem_desc_mn_major_sw128(v_tile + kb * 2048, kKeys * 128);
+                    ptx::mma_f16_ss_pair(o_tmem, dp, dv, idesc_o, (j > 0 || kb > 0) ? 1u : 0u);
+                }
+                ptx::mma_commit_pair(kv_empty(s), 3);
+                ptx::mma_commit_pair(p_free(pb), 3);
+            }
+        }
+        __syncwarp();
+    } else {
+        constexpr int kW = kKeys / 2;
+        constexpr int kDh = D / 2;
+        const unsigned quarter = warp % 4;
+        const unsigned side = (warp - 2) / 4;
+        const unsigned r = quarter * 32 + lane;
+        const uint32_t lane_base = tmem_base + ((quarter * 32u) << 16);
+        const unsigned q_index = row.context + q0 + r;
+        const auto pair_sync = [&] { asm volatile("bar.sync %0, 64;" ::"r"(2u + quarter) : "memory"); };
+        float m = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (unsigned j = 0; j < n_blocks; ++j) {
+            const int sb = static_cast<int>(j & 1u), pb = static_cast<int>(j % kPBuffers);
+            ok = wait_barrier(s_full(sb), (j >> 1) & 1u, abort_flag, p.status, kStatusAttention + 5);
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            const unsigned key0 = j * kKeys + side * kW;
+            const bool diagonal = j * kKeys + kKeys - 1 > row.context + q0;
+            float t[kW];
+#pragma unroll
+            for (int c = 0; c < kW; c += 32) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(lane_base + sb * kKeys + side * kW + c, v);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) t[c + i] = __uint_as_float(v[i]);
+            }
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive_cluster(ptx::map_to_cta(s_free(sb), 0));
+            if (diagonal) {
+#pragma unroll
+                for (int i = 0; i < kW; ++i)
+                    if (key0 + i > q_index) t[i] = -INFINITY;
+            }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < kW; ++i) mx[i & 3] = fmaxf(mx[i & 3], t[i]);
+            const float mine = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            exchange[side * 128 + r] = mine;
+            pair_sync();
+            const float block_max = fmaxf(mine, exchange[(side ^ 1u) * 128 + r]) * p.scale_log2;
+            pair_sync();
+            float alpha = 1.0f;
+            if (block_max > m + 8.0f) {
+                alpha = fast_exp2(m - block_max);
+                m = block_max;
+            }
+            if (j >= static_cast<unsigned>(kPBuffers)) {  // the buffer was last read by P V of block j - kPBuffers
+                ok = wait_barrier(p_free(pb), ((j / kPBuffers) - 1) & 1u, abort_flag, p.status, kStatusAttention + 6);
+                if (!ok) break;
+            }
+            float sum[2] = {0.0f, 0.0f};
+            uint8_t* const p_row = p_smem + pb * T::kPBytes + r * 128;
+#pragma unroll
+            for (int c = 0; c < kW; c += 8) {
+                unsigned packed[4];
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    const float e0 = fast_exp2(__fmaf_rn(t[c + i], p.scale_log2, -m));
+                    const float e1 = fast_exp2(__fmaf_rn(t[c + i + 1], p.scale_log2, -m));
+                    sum[0] += e0;
+                    sum[1] += e1;
+                    const __half2 h = __floats2half2_rn(e0, e1);
+                    packed[i / 2] = *reinterpret_cast<const unsigned*>(&h);
+                }
+                const unsigned col = side * kW + c;
+                *reinterpret_cast<uint4*>(p_row + (col / 64) * (kQueries * 128) + ((((col % 64) / 8) ^ (r & 7u)) * 16)) =
+                    make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // O must hold P V of block j - 1 first
+                const unsigned before = j - 1;
+                ok = wait_barrier(p_free(before % kPBuffers), (before / kPBuffers) & 1u, abort_flag, p.status, kStatusAttention + 6);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+#pragma unroll 1
+                for (int c = 0; c < kDh; c += 32) {
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32(lane_base + T::kOCol + side * kDh + c, v);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    ptx::tmem_st_32x32(lane_base + T::kOCol + side * kDh + c, v);
+                }
+                ptx::tmem_st_wait();
+            }
+            l = l * alpha + (sum[0] + sum[1]);
+            ptx::fence_proxy_async_smem();
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive_cluster(ptx::map_to_cta(p_full(pb), 0));
+        }
+        if (ok && n_blocks > 0) {
+            const unsigned last = n_blocks - 1;
+            ok = wait_barrier(p_free(last % kPBuffers), (last / kPBuffers) & 1u, abort_flag, p.status, kStatusAttention + 7);
+        }
+        exchange[side * 128 + r] = l;
+        pair_sync();
+        const float total = exchange[r] + exchange[128 + r];
+        if (ok) {
+            ptx::tc_fence_after_sync();
+            const float inv_l = 1.0f / total;
+            const size_t token = static_cast<size_t>(row.q_begin) + q0 + r;
+            __half* dst = p.out + token * p.out_stride + static_cast<size_t>(head) * D + side * kDh;
+            const size_t gate0 = token * p.gate_stride + static_cast<size_t>(head) * 2 * D + D + side * kDh;
+#pragma unroll 1
+            for (int c = 0; c < kDh; c += 32) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(lane_base + T::kOCol + side * kDh + c, v);
+                ptx::tmem_ld_wait();
+                if (r < valid) {
+                    unsigned packed[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float g0 = band_value(p.gate, gate0 + c + i, p.gate_half), g1 = band_value(p.gate, gate0 + c + i + 1, p.gate_half);
+                        const float o0 = __uint_as_float(v[i]) * inv_l * (1.0f / (1.0f + expf(-g0)));
+                        const float o1 = __uint_as_float(v[i + 1]) * inv_l * (1.0f / (1.0f + expf(-g1)));
+                        const __half2 h = __floats2half2_rn(o0, o1);
+                        packed[i / 2] = *reinterpret_cast<const unsigned*>(&h);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        *reinterpret_cast<uint4*>(dst + c + 8 * q) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+            }
+        }
+    }
+
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();  // neither CTA leaves while the other may still signal its barriers or read its shared memory
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
 void check_shape(const AttentionShape& s) {
     if (!attention_supports(s))
         throw std::invalid_argument("sepal_b200 attention: head_dim must be 128 or 256, heads a multiple of kv_heads, rotary_dims even and at most head_dim");
@@ -536,14 +829,18 @@ void launch_attention(Context& ctx, const AttentionShape& shape, const Attention
     check_rows(rows, n_rows, n_tokens, arena_tokens);
     check(cudaSetDevice(ctx.device), "cudaSetDevice");
     const unsigned D = shape.head_dim;
-    const unsigned keys = D == 128 ? 128u : 64u;
+    unsigned longest = 0;
+    for (std::size_t i = 0; i < n_rows; ++i) longest = std::max(longest, rows[i].length);
+    const bool pair = longest > static_cast<unsigned>(kQueries);  // CTA pairs take 256 queries at a time
+    const unsigned per_block = pair ? 2u * kQueries : static_cast<unsigned>(kQueries);
+    const unsigned keys = pair ? 128u : (D == 128 ? 128u : 64u);
     // (row, query block) pairs, the ones with the most keys first: they take longest
     struct Block {
         unsigned row, qb, work;
     };
     std::vector<Block> blocks;
     for (std::size_t i = 0; i < n_rows; ++i)
-        for (unsigned qb = 0; qb * kQueries < rows[i].length; ++qb) blocks.push_back({static_cast<unsigned>(i), qb, rows[i].context + (qb + 1) * kQueries});
+        for (unsigned qb = 0; qb * per_block < rows[i].length; ++qb) blocks.push_back({static_cast<unsigned>(i), qb, rows[i].context + (qb + 1) * per_block});
     std::stable_sort(blocks.begin(), blocks.end(), [](const Block& a, const Block& b) { return a.work > b.work; });
     std::vector<unsigned> table(2 * blocks.size());
     for (std::size_t i = 0; i < blocks.size(); ++i) {
@@ -565,24 +862,23 @@ void launch_attention(Context& ctx, const AttentionShape& shape, const Attention
     p.status = ctx.status;
     const std::size_t kv_cols = static_cast<std::size_t>(shape.kv_heads) * D;
     const CUtensorMap map_q = make_tensor_map_2d(ctx, q, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_tokens, static_cast<std::size_t>(shape.heads) * D, q_stride, kQueries, 64, true);
-    const CUtensorMap map_k = make_tensor_map_2d(ctx, k_arena, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, arena_tokens, kv_cols, kv_cols, keys, 64, true);
+    // a CTA of a pair loads 64 of a block's 128 keys, and all 128 values (half of their dimensions)
+    const CUtensorMap map_k = make_tensor_map_2d(ctx, k_arena, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, arena_tokens, kv_cols, kv_cols, pair ? 64u : keys, 64, true);
     const CUtensorMap map_v = make_tensor_map_2d(ctx, v_arena, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, arena_tokens, kv_cols, kv_cols, keys, 64, true);
-    const dim3 grid(static_cast<unsigned>(blocks.size()), shape.heads);
-    if (D == 128) {
-        static bool configured[64] = {};
-        if (ctx.device >= 64 || !configured[ctx.device]) {
-            check(cudaFuncSetAttribute(attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttentionTile<128>::kSmem), "cudaFuncSetAttribute");
-            if (ctx.device < 64) configured[ctx.device] = true;
+    const auto launch = [&](auto kernel, int smem, unsigned ctas_per_block, const char* what) {
+        static bool configured[4][64] = {};
+        const int which = (pair ? 2 : 0) + (D == 256 ? 1 : 0);
+        if (ctx.device >= 64 || !configured[which][ctx.device]) {
+            check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute");
+            if (ctx.device < 64) configured[which][ctx.device] = true;
         }
-        launch_kernel(attention_kernel<128>, grid, dim3(320), AttentionTile<128>::kSmem, stream, "attention_kernel launch", map_q, map_k, map_v, p);
-    } else {
-        static bool configured[64] = {};
-        if (ctx.device >= 64 || !configured[ctx.device]) {
-            check(cudaFuncSetAttribute(attention_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttentionTile<256>::kSmem), "cudaFuncSetAttribute");
-            if (ctx.device < 64) configured[ctx.device] = true;
-        }
-        launch_kernel(attention_kernel<256>, grid, dim3(320), AttentionTile<256>::kSmem, stream, "attention_kernel launch", map_q, map_k, map_v, p);
-    }
+        launch_kernel(kernel, dim3(static_cast<unsigned>(blocks.size()) * ctas_per_block, shape.heads), dim3(320), static_cast<std::size_t>(smem), stream, what, map_q,
+                      map_k, map_v, p);
+    };
+    if (pair && D == 128) launch(attention_pair_kernel<128>, AttentionPairTile<128>::kSmem, 2, "attention_pair_kernel launch");
+    else if (pair) launch(attention_pair_kernel<256>, AttentionPairTile<256>::kSmem, 2, "attention_pair_kernel launch");
+    else if (D == 128) launch(attention_kernel<128>, AttentionTile<128>::kSmem, 1, "attention_kernel launch");
+    else launch(attention_kernel<256>, AttentionTile<256>::kSmem, 1, "attention_kernel launch");
     count_launch();
 }
 

@@ -188,7 +188,12 @@ typedef struct sepal_b200_trunk_config {
     float eps;
     uint64_t seed;
     uint32_t attn_o;                      /* width the attention out-projection reads; 0: attn_q (a real q_proj also carries the output gate) */
+    /* attn_heads > 0: the attention layers run the real core between their projections (sepal_b200_attention_prepare / _attention on
+     * the in-projection's bands, key/value caches per layer) instead of the fixed wiring. Then attn_q = 2 * heads * head_dim,
+     * attn_kv = kv_heads * head_dim, attn_o = heads * head_dim, head_dim 128 or 256. */
+    uint32_t attn_heads, attn_kv_heads, attn_head_dim, attn_rotary_dims;
     uint32_t reserved;
+    double rope_theta;                    /* 0: 1e7 */
 } sepal_b200_trunk_config;
 SEPAL_B200_API int32_t sepal_b200_trunk_open(int32_t device, const sepal_b200_trunk_config* config, sepal_b200_trunk** out);
 SEPAL_B200_API void sepal_b200_trunk_close(sepal_b200_trunk* trunk);
@@ -289,7 +294,7 @@ SEPAL_B200_API int32_t sepal_b200_trunk_run(sepal_b200_trunk* trunk, const uint3
 SEPAL_B200_API int32_t sepal_b200_trunk_score(sepal_b200_trunk* trunk, uint64_t n_requests, const uint32_t* tokens, const uint64_t* offsets,
                                               float* last_hidden, double* times_s);
 /* Copies a stored weight to the host (size-query protocol: host_out NULL only reports *needed). which: 0 embedding, 1 input norm,
- * 2 mixer in-projection, 3 mixer out-projection, 4 post norm, 5 packed [gate; up], 6 down. */
+ * 2 mixer in-projection, 3 mixer out-projection, 4 post norm, 5 packed [gate; up], 6 down, 7 / 8 the attention core's q / k head norms. */
 SEPAL_B200_API int32_t sepal_b200_trunk_weight(sepal_b200_trunk* trunk, uint32_t layer, int32_t which, void* host_out, uint64_t capacity,
                                                uint64_t* needed);
 SEPAL_B200_API int32_t sepal_b200_trunk_info(sepal_b200_trunk* trunk, uint64_t* gemm_flops_per_token, uint64_t* weight_bytes);

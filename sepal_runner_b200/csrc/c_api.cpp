@@ -243,6 +243,11 @@ TrunkConfig trunk_config_of(const sepal_b200_trunk_config& config) {
     c.eps = config.eps;
     c.seed = config.seed;
     c.attn_o = config.attn_o;
+    c.attn_heads = config.attn_heads;
+    c.attn_kv_heads = config.attn_kv_heads;
+    c.attn_head_dim = config.attn_head_dim;
+    c.attn_rotary_dims = config.attn_rotary_dims;
+    if (config.rope_theta > 0.0) c.rope_theta = config.rope_theta;
     return c;
 }
 }  // namespace
@@ -449,7 +454,7 @@ int32_t sepal_b200_trunk_score(sepal_b200_trunk* trunk, uint64_t n_requests, con
 int32_t sepal_b200_trunk_weight(sepal_b200_trunk* trunk, uint32_t layer, int32_t which, void* host_out, uint64_t capacity, uint64_t* needed) {
     return guarded([&] {
         require(trunk, "trunk");
-        if (which < 0 || which > 6) throw std::invalid_argument("which must be 0 .. 6");
+        if (which < 0 || which > 8) throw std::invalid_argument("which must be 0 .. 8");
         const std::size_t bytes = trunk->trunk.weight(layer, static_cast<TrunkWeight>(which), host_out, capacity);
         if (needed != nullptr) *needed = bytes;
     });

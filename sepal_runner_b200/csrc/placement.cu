@@ -192,6 +192,13 @@ void Trunk::place_random() {
         L.norm_post = static_cast<float*>(alloc(H * 4));
         launch_fill_normal_float(L.norm_in, H, ++stream_seed, 0.02f, stream_);
         launch_fill_normal_float(L.norm_post, H, ++stream_seed, 0.02f, stream_);
+        if (L.attention && real_attention()) {
+            L.q_norm = static_cast<float*>(alloc(c.attn_head_dim * 4));
+            L.k_norm = static_cast<float*>(alloc(c.attn_head_dim * 4));
+            launch_fill_normal_float(L.q_norm, c.attn_head_dim, ++stream_seed, 0.02f, stream_);
+            launch_fill_normal_float(L.k_norm, c.attn_head_dim, ++stream_seed, 0.02f, stream_);
+            weight_bytes_ += 2 * c.attn_head_dim * 4;
+        }
         L.mix_in = alloc(static_cast<std::size_t>(L.mix_in_n) * H * 2);
         fill_half(L.mix_in, static_cast<std::size_t>(L.mix_in_n) * H);
         L.mix_out = alloc(H * static_cast<std::size_t>(L.mix_out_k) * 2);
@@ -272,6 +279,13 @@ void Trunk::place_checkpoint(const Checkpoint& ck) {
             const std::string a = pre + "self_attn.";
             stack({a + "q_proj.weight", a + "k_proj.weight", a + "v_proj.weight"}, L.mix_in_n, H, ElementType::F16, L.mix_in);
             up.put(need(ck, a + "o_proj.weight", H, L.mix_out_k), ElementType::F16, L.mix_out);
+            if (real_attention()) {
+                L.q_norm = static_cast<float*>(alloc(c.attn_head_dim * 4));
+                L.k_norm = static_cast<float*>(alloc(c.attn_head_dim * 4));
+                up.put(need(ck, a + "q_norm.weight", c.attn_head_dim, 0), ElementType::F32, L.q_norm);
+                up.put(need(ck, a + "k_norm.weight", c.attn_head_dim, 0), ElementType::F32, L.k_norm);
+                weight_bytes_ += 2 * c.attn_head_dim * 4;
+            }
         } else {
             const std::string d = pre + "linear_attn.";
             stack({d + "in_proj_qkv.weight", d + "in_proj_z.weight", d + "in_proj_b.weight", d + "in_proj_a.weight"}, L.mix_in_n, H, ElementType::F16, L.mix_in);
@@ -331,6 +345,13 @@ void Trunk::place_saved(const Checkpoint& ck) {
         up.put(same_type(need(ck, pre + "norm_post", H, 0), ElementType::F32), ElementType::F32, L.norm_post);
         L.mix_in = alloc(static_cast<std::size_t>(L.mix_in_n) * H * 2);
         L.mix_out = alloc(H * static_cast<std::size_t>(L.mix_out_k) * 2);
+        if (L.attention && real_attention()) {
+            L.q_norm = static_cast<float*>(alloc(c.attn_head_dim * 4));
+            L.k_norm = static_cast<float*>(alloc(c.attn_head_dim * 4));
+            up.put(same_type(need(ck, pre + "q_norm", c.attn_head_dim, 0), ElementType::F32), ElementType::F32, L.q_norm);
+            up.put(same_type(need(ck, pre + "k_norm", c.attn_head_dim, 0), ElementType::F32), ElementType::F32, L.k_norm);
+            weight_bytes_ += 2 * c.attn_head_dim * 4;
+        }
         up.put(same_type(need(ck, pre + "mix_in", L.mix_in_n, H), ElementType::F16), ElementType::F16, L.mix_in);
         up.put(same_type(need(ck, pre + "mix_out", H, L.mix_out_k), ElementType::F16), ElementType::F16, L.mix_out);
         weight_bytes_ += (static_cast<std::size_t>(L.mix_in_n) * H + H * static_cast<std::size_t>(L.mix_out_k)) * 2 + 2 * H * 4;
@@ -377,6 +398,10 @@ void Trunk::save(const std::string& path) {
         add(pre + "mix_in", ElementType::F16, {L.mix_in_n, H}, L.mix_in);
         add(pre + "mix_out", ElementType::F16, {H, L.mix_out_k}, L.mix_out);
         add(pre + "norm_post", ElementType::F32, {H}, L.norm_post);
+        if (L.q_norm != nullptr) {
+            add(pre + "q_norm", ElementType::F32, {c.attn_head_dim}, L.q_norm);
+            add(pre + "k_norm", ElementType::F32, {c.attn_head_dim}, L.k_norm);
+        }
         if (!c.mlp_int8) {
             add(pre + "gate_up", ElementType::F16, {2 * I, H}, L.gate_up);
             add(pre + "down", ElementType::F16, {H, I}, L.down);

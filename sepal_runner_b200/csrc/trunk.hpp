@@ -21,6 +21,7 @@
 
 #include <cuda_runtime.h>
 
+#include "attention.hpp"
 #include "checkpoint.hpp"
 
 #include "gemm.hpp"
@@ -36,13 +37,18 @@ struct TrunkConfig {
     float eps = 1e-6f;
     std::uint64_t seed = 1;
     std::uint32_t attn_o = 0;                               // width the attention out-projection reads (0: attn_q); q_proj may carry a gate
+    // attn_heads > 0: the attention layers run the real core between their projections (norm, RoPE, cache, causal grouped-query
+    // attention, output gate) instead of the fixed wiring; then attn_q = 2 * heads * head_dim (query and gate), attn_kv = kv_heads *
+    // head_dim, attn_o = heads * head_dim.
+    std::uint32_t attn_heads = 0, attn_kv_heads = 0, attn_head_dim = 0, attn_rotary_dims = 0;
     std::uint32_t reserved = 0;
+    double rope_theta = 1.0e7;
 };
 
 /// The value of the "format" metadata key of a file written by Trunk::save.
 extern const char* const kSavedFormat;
 
-enum class TrunkWeight : int { Embedding = 0, NormIn = 1, MixIn = 2, MixOut = 3, NormPost = 4, GateUp = 5, Down = 6 };
+enum class TrunkWeight : int { Embedding = 0, NormIn = 1, MixIn = 2, MixOut = 3, NormPost = 4, GateUp = 5, Down = 6, QNorm = 7, KNorm = 8 };
 
 class Trunk {
 public:
@@ -92,6 +98,10 @@ private:
         void* gate_up = nullptr;  // binary16 packed [2 I, hidden] (mlp_int8: int8)
         void* down = nullptr;     // binary16 [hidden, I] (mlp_int8: int8)
         W8gMatrix gate_up_q, down_q;
+        float* q_norm = nullptr;  // attention layers with the real core: per-head norm weights [head_dim]
+        float* k_norm = nullptr;
+        void* k_cache = nullptr;  // binary16 [arena tokens, kv width]: the keys (normed, rotated) and values of the requests being served
+        void* v_cache = nullptr;
         float* gate_up_scales = nullptr;  // mlp_int8: the quantiser's float32 scales [2 I, hidden / 128] and [hidden, I / 128]
         float* down_scales = nullptr;
     };
@@ -101,7 +111,9 @@ private:
     void place_saved(const Checkpoint& checkpoint);
     void shape_layer(std::uint32_t l);
     void prepare_mlp_scales(Layer& L);
-    void forward_call(const std::uint32_t* tokens_dev, std::size_t rows);
+    void forward_call(const std::uint32_t* tokens_dev, std::size_t rows, const std::vector<AttentionRow>& runs);
+    void reserve_cache(std::size_t tokens);
+    bool real_attention() const { return cfg_.attn_heads != 0; }
 
     TrunkConfig cfg_;
     Context ctx_;
@@ -114,6 +126,9 @@ private:
     void* a1_ = nullptr;         // binary16 [max_call_tokens, hidden]
     void* p_ = nullptr;          // binary16 [max_call_tokens, p_width]
     void* a3_ = nullptr;         // binary16 [max_call_tokens, intermediate]
+    void* q_ = nullptr;          // binary16 [max_call_tokens, attn_o]: normed, rotated queries
+    void* a2_ = nullptr;         // binary16 [max_call_tokens, attn_o]: the attention output, o_proj's operand
+    std::size_t cache_tokens_ = 0;
     std::uint32_t* tokens_dev_ = nullptr;     // two buffers of max_call_tokens: a call's ids are copied while the call before it runs
     std::uint32_t* tokens_pinned_ = nullptr;  // likewise
     float* out_pinned_ = nullptr;             // kMaxCallRows rows of hidden floats, twice

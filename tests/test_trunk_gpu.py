@@ -37,7 +37,19 @@ def oracle_forward(oracle, trunk, cfg, tokens):
         down = trunk.weight("down", l).reshape(H, I).astype(np.float32)
         a1 = f16(oracle.rmsnorm(x, trunk.weight("norm_in", l), cfg.eps))
         p = f16(oracle.gemm(a1, w_in))
-        x = oracle.add(x, oracle.gemm(np.ascontiguousarray(p[:, off:off + k_out]), w_out))
+        if attention and cfg.attn_heads:
+            # the real core on the in-projection's bands: one request, positions 0 .. n - 1; the device keeps q, k, v and the result in binary16
+            from oracle import attention_oracle as ao
+
+            hd, heads, kvh = cfg.attn_head_dim, cfg.attn_heads, cfg.attn_kv_heads
+            q, gate, kk, vv = ao.prepare(p[:, :cfg.attn_q], p[:, cfg.attn_q:cfg.attn_q + cfg.attn_kv], p[:, cfg.attn_q + cfg.attn_kv:n_in],
+                                         trunk.weight("q_norm", l), trunk.weight("k_norm", l), np.arange(len(tokens)), heads, kvh, hd,
+                                         cfg.attn_rotary_dims, cfg.rope_theta, cfg.eps)
+            attended = ao.gated(ao.attend(f16(q.astype(np.float32)).astype(np.float64), f16(kk.astype(np.float32)).astype(np.float64), vv, 0), gate)
+            a2 = f16(attended.reshape(len(tokens), heads * hd).astype(np.float32))
+            x = oracle.add(x, oracle.gemm(a2, w_out))
+        else:
+            x = oracle.add(x, oracle.gemm(np.ascontiguousarray(p[:, off:off + k_out]), w_out))
         a1 = f16(oracle.rmsnorm(x, trunk.weight("norm_post", l), cfg.eps))
         a3 = f16(oracle.swiglu_packed(oracle.gemm(a1, gate_up), I))
         x = oracle.add(x, oracle.gemm(a3, down))
@@ -295,3 +307,42 @@ def test_placement_reports_a_missing_tensor(tmp_path):
     sb.write_tensor_file(str(tmp_path / "model.safetensors"), {"embed_tokens.weight": np.zeros((cfg.vocab, cfg.hidden), np.float16)})
     with pytest.raises(sb.SepalB200Error, match="no tensor 'layers.0.input_layernorm.weight'"):
         sb.Trunk(0, cfg, sb.Checkpoint(str(tmp_path)))
+
+
+def test_trunk_with_the_real_attention_core(oracle, tmp_path):
+    """attn_heads > 0: the attention layers run norm, RoPE, cache and causal grouped-query attention between their projections. One request cut
+    into three calls (the later calls attend to the earlier ones' keys), against the CPU composition; several requests packed into calls give
+    what each gives alone; the head norms travel through a saved file."""
+    import sepal_runner_b200 as sb
+
+    cfg = small_config(sb, attn_q=512, attn_kv=128, attn_o=256, attn_heads=2, attn_kv_heads=1, attn_head_dim=128, attn_rotary_dims=32, rope_theta=1.0e4)
+    trunk = sb.Trunk(0, cfg)
+    try:
+        rng = np.random.default_rng(31)
+        tokens = rng.integers(0, cfg.vocab, 700).astype(np.uint32)
+        last, allh, _ = trunk.run(tokens, want_all=True)
+        assert np.isfinite(allh).all()
+        want = oracle_forward(oracle, trunk, cfg, tokens)
+        assert rel_fro(allh, want) < 3e-3
+        assert rel_fro(allh[-50:], want[-50:]) < 3e-3  # the last call's tokens see all 700 keys
+        # unlike the wired trunk, a token now depends on the tokens before it
+        other = tokens.copy()
+        other[0] = (other[0] + 1) % cfg.vocab
+        assert not np.array_equal(trunk.run(other)[0], last)
+        requests = [tokens[:130], tokens, tokens[100:101], tokens[:555]]
+        hidden, _ = trunk.score(requests)
+        for i, r in enumerate(requests):
+            assert rel_fro(hidden[i], trunk.run(r)[0]) < 1e-5, i
+        assert rel_fro(hidden[1], last) < 1e-5
+        saved = str(tmp_path / "placed.safetensors")
+        trunk.save(saved)
+        again = sb.Trunk(0, cfg, sb.Checkpoint(saved))
+        try:
+            assert np.array_equal(again.weight("q_norm", 3), trunk.weight("q_norm", 3)) and np.array_equal(again.weight("k_norm", 7), trunk.weight("k_norm", 7))
+            assert np.array_equal(again.run(tokens)[0], last)
+        finally:
+            again.close()
+        with pytest.raises(sb.SepalB200Error, match="attn_q = 2 heads"):
+            sb.Trunk(0, small_config(sb, attn_q=256, attn_kv=128, attn_o=256, attn_heads=2, attn_kv_heads=1, attn_head_dim=128))
+    finally:
+        trunk.close()

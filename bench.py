@@ -341,8 +341,11 @@ def trunk_numbers(local, peak_tf):
 
     out = {}
     rng = np.random.default_rng(4004)
-    for name, int8 in (("f16", 0), ("mlp_int8", 1)):
-        trunk = sb.Trunk(local, sb.TrunkConfig(mlp_int8=int8))
+    # "attention": the nine attention layers run the real core (16 query / 4 key-value heads of 256, q_proj carrying the output gate:
+    # 8192 rows instead of 4096) instead of the fixed wiring; the DeltaNet layers stay wired.
+    real = dict(attn_q=8192, attn_kv=1024, attn_o=4096, attn_heads=16, attn_kv_heads=4, attn_head_dim=256, attn_rotary_dims=64)
+    for name, int8, extra in (("f16", 0, {}), ("mlp_int8", 1, {}), ("f16_attention", 0, real)):
+        trunk = sb.Trunk(local, sb.TrunkConfig(mlp_int8=int8, **extra))
         flops_tok = trunk.gemm_flops_per_token
         row = {"weight_gb": round(trunk.weight_bytes / 1e9, 2), "gemm_gflop_per_token": round(flops_tok / 1e9, 3)}
         for label, n in (("alert_900", 900), ("log_15900", 15900)):

@@ -452,16 +452,16 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 template <int D>
 struct AttentionPairTile {
     static constexpr int kKeys = 128;
-    static constexpr int kStages = D == 128 ? 6 : 2;
+    static constexpr int kStages = D == 128 ? 5 : 2;
     static constexpr int kQBytes = kQueries * D * 2;
     static constexpr int kHalfBytes = 128 * D;                 // 64 keys x D, and 128 values x D / 2, in binary16
     static constexpr int kStageBytes = 2 * kHalfBytes;
-    static constexpr int kSmem = 1024 + kQBytes + kStages * kStageBytes + 256 + 1024;
+    static constexpr int kSmem = 1024 + kQBytes + kStages * kStageBytes + 256 + 2048;  // barriers; 4 x 128 floats the warps of a query exchange
     static constexpr int kOCol = 256;
 };
 
 template <int D>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(576, 1)
 attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const AttentionParams p) {
     using T = AttentionPairTile<D>;
@@ -506,7 +506,7 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(s_full(b), 1);
-            ptx::mbar_init(p_full(b), 512);  // the softmax threads of both CTAs (used in the first CTA only)
+            ptx::mbar_init(p_full(b), 32);  // one arrival from each softmax warp of both CTAs (used in the first CTA only)
             ptx::mbar_init(p_free(b), 1);
         }
         words[1] = 0;
@@ -551,16 +551,19 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const uint32_t idesc_s = ptx::instr_desc_f16_f32acc(2 * kQueries, kKeys);
             const uint32_t idesc_o = ptx::instr_desc_f16_f32acc_b_mn(2 * kQueries, D);
             const uint32_t o_tmem = tmem_base + T::kOCol;
+            // The descriptors are made once: an MMA of 256 x 128 x 16 is 64 cycles of tensor work, and building two descriptors for each
+            // would take the issuing thread about as long.
+            uint64_t dq[D / 16];
+#pragma unroll
+            for (int i = 0; i < D / 16; ++i) dq[i] = ptx::smem_desc_k_major_sw128(q_addr + (i / 4) * (kQueries * 128)) + 2u * (i % 4);
+            const uint64_t dk_base = ptx::smem_desc_k_major_sw128(kv_addr);
+            const uint64_t dv_base = ptx::smem_desc_mn_major_sw128(kv_addr + T::kHalfBytes, kKeys * 128);
             const auto issue_scores = [&](unsigned j) {
                 const int s = static_cast<int>(j % kStages), sb = static_cast<int>(j & 1u);
-                const uint32_t k_tile = kv_addr + s * T::kStageBytes;
+                const uint64_t dk = dk_base + static_cast<uint64_t>((s * T::kStageBytes) >> 4);
 #pragma unroll
-                for (int b = 0; b < D / 64; ++b) {
-                    const uint64_t dq = ptx::smem_desc_k_major_sw128(q_addr + b * (kQueries * 128));
-                    const uint64_t dk = ptx::smem_desc_k_major_sw128(k_tile + b * (64 * 128));
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) ptx::mma_f16_ss_pair(tmem_base + sb * kKeys, dq + 2u * kk, dk + 2u * kk, idesc_s, (b | kk) != 0 ? 1u : 0u);
-                }
+                for (int i = 0; i < D / 16; ++i)  // box i / 4 of 64 dimensions (8 KB of this CTA's 64 keys), 16 dimensions i % 4 inside it
+                    ptx::mma_f16_ss_pair(tmem_base + sb * kKeys, dq[i], dk + static_cast<uint64_t>((i / 4) * 512 + (i % 4) * 2), idesc_s, i != 0 ? 1u : 0u);
                 ptx::mma_commit_pair(s_full(sb), 3);
             };
             bool ok = wait_barrier(q_full, 0, abort_flag, p.status, kStatusAttention + 1) && wait_barrier(kv_full(0), 0, abort_flag, p.status, kStatusAttention + 1);
@@ -581,43 +584,45 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 ok = wait_barrier(p_full(sb), (j >> 1) & 1u, abort_flag, p.status, kStatusAttention + 4);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
-                const uint32_t v_tile = kv_addr + s * T::kStageBytes + T::kHalfBytes;
+                const uint64_t dv = dv_base + static_cast<uint64_t>((s * T::kStageBytes) >> 4);
 #pragma unroll
-                for (int kb = 0; kb < kKeys / 16; ++kb) {  // P_j from tensor memory: 16 keys are 8 columns
-                    const uint64_t dv = ptx::smem_desc_mn_major_sw128(v_tile + kb * 2048, kKeys * 128);
-                    ptx::mma_f16_ts_pair(o_tmem, tmem_base + sb * kKeys + kb * 8, dv, idesc_o, (j > 0 || kb > 0) ? 1u : 0u);
-                }
+                for (int kb = 0; kb < kKeys / 16; ++kb)  // P_j from tensor memory: 16 keys are 8 columns; 16 values are 2048 bytes further
+                    ptx::mma_f16_ts_pair(o_tmem, tmem_base + sb * kKeys + kb * 8, dv + static_cast<uint64_t>(kb * 128), idesc_o, (j > 0 || kb > 0) ? 1u : 0u);
                 ptx::mma_commit_pair(kv_empty(s), 3);
                 ptx::mma_commit_pair(p_free(sb), 3);
             }
         }
         __syncwarp();
     } else {
-        constexpr int kW = kKeys / 2;
-        constexpr int kDh = D / 2;
+        // Sixteen warps: the four warps w, w + 4, w + 8, w + 12 share the 32 queries of tensor-memory lanes 32 (w % 4) ..., each taking a
+        // quarter of a block's keys (and later of the head's dimensions): four warps per scheduler hide each other's latencies (with two,
+        // the schedulers issued one cycle in three).
+        constexpr int kSplit = 4;
+        constexpr int kW = kKeys / kSplit;            // keys of a block per thread: 32
+        constexpr int kDq = D / kSplit;               // output dimensions per thread: 32 or 64
         const unsigned quarter = warp % 4;
-        const unsigned side = (warp - 2) / 4;
+        const unsigned side = (warp - 2) / 4;         // which quarter of the keys
         const unsigned r = quarter * 32 + lane;
         const uint32_t lane_base = tmem_base + ((quarter * 32u) << 16);
         const unsigned q_index = row.context + q0 + r;
-        const auto pair_sync = [&] { asm volatile("bar.sync %0, 64;" ::"r"(2u + quarter) : "memory"); };
+        const auto row_sync = [&] { asm volatile("bar.sync %0, 128;" ::"r"(2u + quarter) : "memory"); };  // the four warps of these rows
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
         for (unsigned j = 0; j < n_blocks; ++j) {
             const int sb = static_cast<int>(j & 1u);
-            ok = wait_barrier(s_full(sb), (j >> 1) & 1u, abort_flag, p.status, kStatusAttention + 5);
-            if (!ok) break;
+            // (once a wait has given up, the waits return at once and the loop runs on over garbage: the warps of a quarter must keep
+            // meeting at their named barrier, which has no time limit)
+            if (ok) ok = wait_barrier(s_full(sb), (j >> 1) & 1u, abort_flag, p.status, kStatusAttention + 5);
             ptx::tc_fence_after_sync();
             const unsigned key0 = j * kKeys + side * kW;
             const bool diagonal = j * kKeys + kKeys - 1 > row.context + q0;
             float t[kW];
-#pragma unroll
-            for (int c = 0; c < kW; c += 32) {
+            {
                 uint32_t v[32];
-                ptx::tmem_ld_32x32(lane_base + sb * kKeys + side * kW + c, v);
+                ptx::tmem_ld_32x32(lane_base + sb * kKeys + side * kW, v);
                 ptx::tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) t[c + i] = __uint_as_float(v[i]);
+                for (int i = 0; i < 32; ++i) t[i] = __uint_as_float(v[i]);
             }
             if (diagonal) {
 #pragma unroll
@@ -627,17 +632,16 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int i = 0; i < kW; ++i) mx[i & 3] = fmaxf(mx[i & 3], t[i]);
-            const float mine = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            exchange[side * 128 + r] = mine;
-            pair_sync();
-            const float block_max = fmaxf(mine, exchange[(side ^ 1u) * 128 + r]) * p.scale_log2;
-            pair_sync();
+            exchange[side * 128 + r] = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            row_sync();
+            const float block_max = fmaxf(fmaxf(exchange[r], exchange[128 + r]), fmaxf(exchange[256 + r], exchange[384 + r])) * p.scale_log2;
+            row_sync();  // all four have read: the next block may overwrite
             float alpha = 1.0f;
-            if (block_max > m + 8.0f) {
+            if (block_max > m + 8.0f) {  // also the first block (m = -inf), where alpha is 0 and O is not touched
                 alpha = fast_exp2(m - block_max);
                 m = block_max;
             }
-            // Probabilities as binary16, two keys to a 32-bit column, over the scores they came from: both halves of the query have
+            // Probabilities as binary16, two keys to a 32-bit column, over the scores they came from: all four parts of the query have
             // their scores in registers (the exchange above saw to that), and the next S into this buffer is issued after P_j V_j.
             float sum[2] = {0.0f, 0.0f};
             uint32_t packed[kW / 2];
@@ -650,44 +654,44 @@ attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const __half2 h = __floats2half2_rn(e0, e1);
                 packed[i / 2] = *reinterpret_cast<const unsigned*>(&h);
             }
-            ptx::tmem_st_32x32(lane_base + sb * kKeys + side * (kW / 2), packed);
+            ptx::tmem_st_32x16(lane_base + sb * kKeys + side * (kW / 2), packed);
             if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // O must hold P V of block j - 1 first
                 const unsigned before = j - 1;
-                ok = wait_barrier(p_free(before & 1u), (before >> 1) & 1u, abort_flag, p.status, kStatusAttention + 6);
-                if (!ok) break;
+                if (ok) ok = wait_barrier(p_free(before & 1u), (before >> 1) & 1u, abort_flag, p.status, kStatusAttention + 6);
                 ptx::tc_fence_after_sync();
 #pragma unroll 1
-                for (int c = 0; c < kDh; c += 32) {
+                for (int c = 0; c < kDq; c += 32) {
                     uint32_t v[32];
-                    ptx::tmem_ld_32x32(lane_base + T::kOCol + side * kDh + c, v);
+                    ptx::tmem_ld_32x32(lane_base + T::kOCol + side * kDq + c, v);
                     ptx::tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                    ptx::tmem_st_32x32(lane_base + T::kOCol + side * kDh + c, v);
+                    ptx::tmem_st_32x32(lane_base + T::kOCol + side * kDq + c, v);
                 }
             }
             ptx::tmem_st_wait();
             l = l * alpha + (sum[0] + sum[1]);
             ptx::tc_fence_before_sync();
-            ptx::mbar_arrive_cluster(ptx::map_to_cta(p_full(sb), 0));
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(p_full(sb), 0));  // one arrival for the warp
         }
         if (ok && n_blocks > 0) {
             const unsigned last = n_blocks - 1;
             ok = wait_barrier(p_free(last & 1u), (last >> 1) & 1u, abort_flag, p.status, kStatusAttention + 7);
         }
         exchange[side * 128 + r] = l;
-        pair_sync();
-        const float total = exchange[r] + exchange[128 + r];
+        row_sync();
+        const float total = (exchange[r] + exchange[128 + r]) + (exchange[256 + r] + exchange[384 + r]);
         if (ok) {
             ptx::tc_fence_after_sync();
             const float inv_l = 1.0f / total;
             const size_t token = static_cast<size_t>(row.q_begin) + q0 + r;
-            __half* dst = p.out + token * p.out_stride + static_cast<size_t>(head) * D + side * kDh;
-            const size_t gate0 = token * p.gate_stride + static_cast<size_t>(head) * 2 * D + D + side * kDh;
+            __half* dst = p.out + token * p.out_stride + static_cast<size_t>(head) * D + side * kDq;
+            const size_t gate0 = token * p.gate_stride + static_cast<size_t>(head) * 2 * D + D + side * kDq;
 #pragma unroll 1
-            for (int c = 0; c < kDh; c += 32) {
+            for (int c = 0; c < kDq; c += 32) {
                 uint32_t v[32];
-                ptx::tmem_ld_32x32(lane_base + T::kOCol + side * kDh + c, v);
+                ptx::tmem_ld_32x32(lane_base + T::kOCol + side * kDq + c, v);
                 ptx::tmem_ld_wait();
                 if (r < valid) {
                     unsigned packed[16];
@@ -855,8 +859,8 @@ void launch_attention(Context& ctx, const AttentionShape& shape, const Attention
             check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute");
             if (ctx.device < 64) configured[which][ctx.device] = true;
         }
-        launch_kernel(kernel, dim3(static_cast<unsigned>(blocks.size()) * ctas_per_block, shape.heads), dim3(320), static_cast<std::size_t>(smem), stream, what, map_q,
-                      map_k, map_v, p);
+        launch_kernel(kernel, dim3(static_cast<unsigned>(blocks.size()) * ctas_per_block, shape.heads), dim3(pair ? 576 : 320), static_cast<std::size_t>(smem), stream,
+                      what, map_q, map_k, map_v, p);
     };
     if (pair && D == 128) launch(attention_pair_kernel<128>, AttentionPairTile<128>::kSmem, 2, "attention_pair_kernel launch");
     else if (pair) launch(attention_pair_kernel<256>, AttentionPairTile<256>::kSmem, 2, "attention_pair_kernel launch");

@@ -232,6 +232,33 @@ SEPAL_B200_API int32_t sepal_b200_attention(sepal_b200_ctx* ctx, const sepal_b20
                                             const void* v_arena, uint64_t arena_tokens, const void* gate, uint64_t gate_stride, int32_t gate_half,
                                             void* out, uint64_t out_stride, void* stream);
 
+/* ---- the Gated DeltaNet core between its projections ---------------------------------------------------------------------------------
+ *
+ * Replaces the DeltaNet launches of the reference's layer loop (runner/cuda/src/cuda_engine.cpp:1827-1857; contract
+ * runner/cuda/src/kernels_deltanet.hpp; math runner/include/sepal/ref/deltanet.hpp:33-330): causal depthwise convolution over `mixed`
+ * (K taps, the last on the current token, continued from the request's previous K - 1 rows), SiLU, q / k / v split, q and k L2-normalised
+ * per head, value head h on key head h / (value_heads / key_heads), the gated delta rule on a float32 state per value head
+ * (S <- decay S; S <- S + k (x) beta (v - k . S); read = S^T q / sqrt(dk); decay = exp(-exp(A_log) softplus(a + dt_bias)), beta =
+ * sigmoid(b)), the head-wise RMSNorm of the read with the norm weight itself and the silu(z) gate, binary16 out for out_proj.
+ * mixed [N, 2 key_dim + value_dim], z [N, value_dim], b and a [N, value_heads] are bands of the in-projection (all binary16 or all
+ * float32); conv float32 [conv_dim, K], a_log and dt_bias [value_heads], norm [head_dim]; scratch: N * (2 key_dim + value_dim + 2
+ * value_heads) floats; states float32 [slots, value_heads, 128, 128] and tails float32 [slots, K - 1, conv_dim] persist between calls
+ * (a row with fresh = 1 starts from zero whatever its slot holds); a row is {first token, length, slot, fresh}; rows: host array sorted
+ * by first token, one row per slot in a call. head_dim 128. The scan is token-sequential (one CTA per row and value head). */
+typedef struct sepal_b200_deltanet_shape {
+    uint32_t key_heads, value_heads, head_dim, conv_kernel;
+    float eps;
+    uint32_t reserved;
+} sepal_b200_deltanet_shape;
+typedef struct sepal_b200_deltanet_row {
+    uint32_t q_begin, length, slot, fresh;
+} sepal_b200_deltanet_row;
+SEPAL_B200_API int32_t sepal_b200_deltanet(sepal_b200_ctx* ctx, const sepal_b200_deltanet_shape* shape, const sepal_b200_deltanet_row* rows,
+                                           uint64_t n_rows, const void* mixed, uint64_t mixed_stride, const void* z, uint64_t z_stride, const void* b,
+                                           uint64_t b_stride, const void* a, uint64_t a_stride, int32_t bands_half, const float* conv,
+                                           const float* a_log, const float* dt_bias, const float* norm, float* scratch, float* states, float* tails,
+                                           uint64_t slots, void* out, uint64_t out_stride, void* stream);
+
 /* ---- checkpoints and weight placement (the data format on the input side of the path) ----------------------------------------------
  *
  * The reader of the safetensors format (runner/include/sepal/safetensors.hpp:1-154) and of checkpoint directories with their name

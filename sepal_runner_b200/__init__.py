@@ -16,6 +16,9 @@ from .lib import (  # noqa: F401
     STORE,
     SWIGLU,
     Context,
+    DeltaNetRow,
+    DeltaNetShape,
+    deltanet,
     Provider,
     SepalB200Error,
     Trunk,

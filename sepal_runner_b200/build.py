@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsepal_b200.so")
-SOURCES = ["gemm_tc.cu", "quant.cu", "provider.cu", "trunk.cu", "placement.cu", "attention.cu", "context.cpp", "model.cpp", "checkpoint.cpp", "c_api.cpp"]
+SOURCES = ["gemm_tc.cu", "quant.cu", "provider.cu", "trunk.cu", "placement.cu", "attention.cu", "deltanet.cu", "context.cpp", "model.cpp", "checkpoint.cpp", "c_api.cpp"]
 NVCC_FLAGS = [
     "-std=c++20", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "-x", "cu", "--shared", "-cudart", "static",

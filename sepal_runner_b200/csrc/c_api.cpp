@@ -14,6 +14,7 @@
 
 #include "attention.hpp"
 #include "checkpoint.hpp"
+#include "deltanet.hpp"
 #include "gemm.hpp"
 #include "model.hpp"
 #include "provider.hpp"
@@ -291,6 +292,40 @@ int32_t sepal_b200_attention(sepal_b200_ctx* ctx, const sepal_b200_attention_sha
         require(shape, "shape");
         launch_attention(ctx->ctx, attention_shape_of(*shape), reinterpret_cast<const AttentionRow*>(rows), n_rows, n_tokens, q, q_stride, k_arena, v_arena,
                          arena_tokens, Band{gate, gate_stride, gate_half != 0}, out, out_stride, static_cast<cudaStream_t>(stream));
+    });
+}
+
+static_assert(sizeof(sepal_b200_deltanet_row) == sizeof(DeltaNetRow), "the row tables must have one layout");
+
+int32_t sepal_b200_deltanet(sepal_b200_ctx* ctx, const sepal_b200_deltanet_shape* shape, const sepal_b200_deltanet_row* rows, uint64_t n_rows,
+                            const void* mixed, uint64_t mixed_stride, const void* z, uint64_t z_stride, const void* b, uint64_t b_stride, const void* a,
+                            uint64_t a_stride, int32_t bands_half, const float* conv, const float* a_log, const float* dt_bias, const float* norm,
+                            float* scratch, float* states, float* tails, uint64_t slots, void* out, uint64_t out_stride, void* stream) {
+    return guarded([&] {
+        require(ctx, "ctx");
+        require(shape, "shape");
+        DeltaNetShape s;
+        s.key_heads = shape->key_heads;
+        s.value_heads = shape->value_heads;
+        s.head_dim = shape->head_dim;
+        s.conv_kernel = shape->conv_kernel;
+        s.eps = shape->eps;
+        if (n_rows != 0) {
+            require(rows, "rows");
+            require(scratch, "scratch");
+        }
+        std::size_t tokens = 0;
+        if (n_rows != 0) tokens = static_cast<std::size_t>(rows[n_rows - 1].q_begin) + rows[n_rows - 1].length;
+        DeltaNetScratch sc;  // q, k, v, decay, beta one after the other
+        sc.q = scratch;
+        sc.k = sc.q + tokens * s.key_dim();
+        sc.v = sc.k + tokens * s.key_dim();
+        sc.decay = sc.v + tokens * s.value_dim();
+        sc.beta = sc.decay + tokens * s.value_heads;
+        const bool half = bands_half != 0;
+        launch_deltanet(ctx->ctx, s, reinterpret_cast<const DeltaNetRow*>(rows), n_rows, Band{mixed, mixed_stride, half}, Band{z, z_stride, half},
+                        Band{b, b_stride, half}, Band{a, a_stride, half}, DeltaNetWeights{conv, a_log, dt_bias, norm}, sc, states, tails, nullptr, slots, out,
+                        out_stride, static_cast<cudaStream_t>(stream));
     });
 }
 

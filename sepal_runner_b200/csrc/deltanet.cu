@@ -1,0 +1,284 @@
+#include "deltanet.hpp"
+
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include <cuda_fp16.h>
+
+#include "ptx.cuh"
+
+namespace sepal::b200 {
+
+void count_launch();
+
+namespace {
+
+constexpr int kDim = 128;  // dk = dv
+
+struct DeltaParams {
+    const DeltaNetRow* rows;
+    unsigned n_rows;
+    unsigned key_heads, value_heads, taps;
+    unsigned key_dim, value_dim, conv_dim;
+    float eps;
+    const void* mixed;
+    const void* z;
+    const void* b;
+    const void* a;
+    unsigned long long mixed_stride, z_stride, b_stride, a_stride;
+    unsigned mixed_half, z_half, b_half, a_half;
+    const float* conv;
+    const float* a_log;
+    const float* dt_bias;
+    const float* norm;
+    float* q;
+    float* k;
+    float* v;
+    float* decay;
+    float* beta;
+    float* states;
+    float* tails;  // [slots, taps - 1, conv_dim]
+    __half* out;
+    unsigned long long out_stride;
+};
+
+__device__ __forceinline__ float value_of(const void* base, unsigned long long index, unsigned half) {
+    return half != 0 ? __half2float(static_cast<const __half*>(base)[index]) : static_cast<const float*>(base)[index];
+}
+// softplus, sigmoid and silu in the reference's forms (runner/include/sepal/ref/primitives.hpp:25-40).
+__device__ __forceinline__ float softplus(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); }
+__device__ __forceinline__ float sigmoid(float x) { return expf(-softplus(-x)); }
+__device__ __forceinline__ float silu(float x) { return __fmul_rn(x, sigmoid(x)); }
+
+__device__ __forceinline__ unsigned row_of(const DeltaNetRow* rows, unsigned n_rows, unsigned token) {
+    unsigned lo = 0, hi = n_rows;
+    while (hi - lo > 1) {
+        const unsigned mid = (lo + hi) / 2;
+        if (rows[mid].q_begin <= token) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+// One block per token: the convolution (taps in ascending order, the last on the token itself; inputs before the run come from the
+// slot's tail, zeros for a fresh request), SiLU, q and k normalised per head, v as it is; the token's decay and beta per value head.
+__global__ void __launch_bounds__(256) deltanet_prepare_kernel(const DeltaParams p) {
+    extern __shared__ float activated[];  // [conv_dim]
+    __shared__ float head_sums[64];
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+    const unsigned token = blockIdx.x;
+    const DeltaNetRow row = p.rows[row_of(p.rows, p.n_rows, token)];
+    if (token < row.q_begin || token >= row.q_begin + row.length) return;
+    const unsigned t = token - row.q_begin;
+    const unsigned history = p.taps - 1;
+    const float* tail = p.tails + static_cast<size_t>(row.slot) * history * p.conv_dim;
+    for (unsigned c = threadIdx.x; c < p.conv_dim; c += blockDim.x) {
+        float acc = 0.0f;
+        for (unsigned j = 0; j < p.taps; ++j) {
+            // window index t + j over (tail, then the run's inputs): the input of token t + j - history, or tail row t + j
+            float x;
+            if (t + j >= history) x = value_of(p.mixed, (static_cast<size_t>(token) + j - history) * p.mixed_stride + c, p.mixed_half);
+            else x = row.fresh != 0 ? 0.0f : tail[static_cast<size_t>(t + j) * p.conv_dim + c];
+            acc = __fadd_rn(acc, __fmul_rn(p.conv[static_cast<size_t>(c) * p.taps + j], x));
+        }
+        activated[c] = silu(acc);
+    }
+    __syncthreads();
+    // q and k heads: 2 * key_heads vectors of 128; one warp per head in turn
+    const unsigned warp = threadIdx.x / 32, lane = threadIdx.x % 32, warps = blockDim.x / 32;
+    for (unsigned h = warp; h < 2 * p.key_heads; h += warps) {
+        const float* x = activated + h * kDim;
+        float ss = 0.0f;
+        for (int e = 0; e < 4; ++e) ss = __fmaf_rn(x[lane + 32 * e], x[lane + 32 * e], ss);
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+        if (lane == 0) head_sums[h] = ss;
+    }
+    __syncthreads();
+    for (unsigned c = threadIdx.x; c < p.conv_dim; c += blockDim.x) {
+        if (c < 2 * p.key_dim) {
+            const float value = __fdiv_rn(activated[c], __fsqrt_rn(__fadd_rn(head_sums[c / kDim], 1.0e-6f)));
+            if (c < p.key_dim) p.q[static_cast<size_t>(token) * p.key_dim + c] = value;
+            else p.k[static_cast<size_t>(token) * p.key_dim + (c - p.key_dim)] = value;
+        } else {
+            p.v[static_cast<size_t>(token) * p.value_dim + (c - 2 * p.key_dim)] = activated[c];
+        }
+    }
+    for (unsigned h = threadIdx.x; h < p.value_heads; h += blockDim.x) {
+        const float a = value_of(p.a, static_cast<size_t>(token) * p.a_stride + h, p.a_half);
+        const float b = value_of(p.b, static_cast<size_t>(token) * p.b_stride + h, p.b_half);
+        p.decay[static_cast<size_t>(token) * p.value_heads + h] = expf(-expf(p.a_log[h]) * softplus(a + p.dt_bias[h]));
+        p.beta[static_cast<size_t>(token) * p.value_heads + h] = sigmoid(b);
+    }
+}
+
+// After the prepare launch: the slot's tail becomes the last K - 1 rows of (old tail, then the run's inputs). One block per run.
+__global__ void deltanet_tail_kernel(const DeltaParams p) {
+    const DeltaNetRow row = p.rows[blockIdx.x];
+    const unsigned history = p.taps - 1;
+    float* tail = p.tails + static_cast<size_t>(row.slot) * history * p.conv_dim;
+    for (unsigned c = threadIdx.x; c < p.conv_dim; c += blockDim.x) {
+        for (unsigned i = 0; i < history; ++i) {  // ascending: row length + i of the window is read before row i is written (length >= 1)
+            const unsigned w = row.length + i;
+            float x;
+            if (w >= history) x = value_of(p.mixed, (static_cast<size_t>(row.q_begin) + w - history) * p.mixed_stride + c, p.mixed_half);
+            else x = row.fresh != 0 ? 0.0f : tail[static_cast<size_t>(w) * p.conv_dim + c];
+            tail[static_cast<size_t>(i) * p.conv_dim + c] = x;
+        }
+    }
+}
+
+// One CTA per run and value head, 256 threads: thread (half, j) holds rows 64 half .. 64 half + 63 of column j of the state. Per
+// token: the state decays; each column's recall k . S[:, j] is summed in two halves (rows in order, the first half then the second);
+// the column takes its correction; the read q . S[:, j] likewise; then the head's RMS over the 128 reads (a butterfly over each warp,
+// the four warp sums in order), the norm weight and the silu(z) gate, and the binary16 store. The next token's k, q, v, z are fetched
+// while the current one is worked on.
+__global__ void __launch_bounds__(256) deltanet_scan_kernel(const DeltaParams p) {
+    __shared__ float k_sh[2][kDim], q_sh[2][kDim];
+    __shared__ float part[2][kDim];
+    __shared__ float warp_sums[4];
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+    const DeltaNetRow row = p.rows[blockIdx.x];
+    const unsigned head = blockIdx.y, key_head = head / (p.value_heads / p.key_heads);
+    const unsigned j = threadIdx.x % kDim, half = threadIdx.x / kDim;
+    float s[64];
+    float* state = p.states + (static_cast<size_t>(row.slot) * p.value_heads + head) * kDim * kDim;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) s[i] = row.fresh != 0 ? 0.0f : state[static_cast<size_t>(64 * half + i) * kDim + j];
+    const float scale = rsqrtf(static_cast<float>(kDim));  // 1 / sqrt(128): computed once; the exact value 2^-3.5 rounded
+    const float w_norm = p.norm[j];
+    const auto fetch = [&](unsigned t, float& kq, float& vv, float& zz, float& dd, float& bb) {
+        const size_t token = static_cast<size_t>(row.q_begin) + t;
+        kq = half == 0 ? p.k[token * p.key_dim + key_head * kDim + j] : p.q[token * p.key_dim + key_head * kDim + j];
+        vv = p.v[token * p.value_dim + head * kDim + j];
+        zz = value_of(p.z, token * p.z_stride + head * kDim + j, p.z_half);
+        dd = p.decay[token * p.value_heads + head];
+        bb = p.beta[token * p.value_heads + head];
+    };
+    float kq_next, v_next, z_next, decay_next, beta_next;
+    fetch(0, kq_next, v_next, z_next, decay_next, beta_next);
+    for (unsigned t = 0; t < row.length; ++t) {
+        const unsigned buf = t & 1u;
+        const float v = v_next, z = z_next, decay = decay_next, beta = beta_next;
+        if (half == 0) k_sh[buf][j] = kq_next; else q_sh[buf][j] = kq_next;
+        const size_t token = static_cast<size_t>(row.q_begin) + t;
+        if (t + 1 < row.length) fetch(t + 1, kq_next, v_next, z_next, decay_next, beta_next);
+        __syncthreads();  // k and q of this token are in shared memory (the buffers alternate, so the next token may already be written)
+        float rec[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+            s[i] = __fmul_rn(s[i], decay);
+            rec[i & 3] = __fmaf_rn(k_sh[buf][64 * half + i], s[i], rec[i & 3]);
+        }
+        part[half][j] = (rec[0] + rec[1]) + (rec[2] + rec[3]);
+        __syncthreads();
+        const float correction = __fmul_rn(beta, __fsub_rn(v, part[0][j] + part[1][j]));
+        __syncthreads();  // both halves have read the recall before the reads overwrite the slots
+        float rd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+            s[i] = __fmaf_rn(k_sh[buf][64 * half + i], correction, s[i]);
+            rd[i & 3] = __fmaf_rn(q_sh[buf][64 * half + i], s[i], rd[i & 3]);
+        }
+        part[half][j] = (rd[0] + rd[1]) + (rd[2] + rd[3]);
+        __syncthreads();
+        if (half == 0) {
+            const float read = __fmul_rn(part[0][j] + part[1][j], scale);
+            float ss = __fmul_rn(read, read);
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+            if (j % 32 == 0) warp_sums[j / 32] = ss;
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // the first four warps
+            const float total = ((warp_sums[0] + warp_sums[1]) + warp_sums[2]) + warp_sums[3];
+            const float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(kDim)), p.eps));
+            p.out[token * p.out_stride + head * kDim + j] = __float2half_rn(__fmul_rn(__fmul_rn(__fdiv_rn(read, rms), w_norm), silu(z)));
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // warp_sums may be rewritten
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 64; ++i) state[static_cast<size_t>(64 * half + i) * kDim + j] = s[i];
+}
+
+}  // namespace
+
+bool deltanet_supports(const DeltaNetShape& s) {
+    return s.head_dim == 128 && s.key_heads != 0 && s.value_heads != 0 && s.value_heads % s.key_heads == 0 && s.key_heads <= 32 && s.conv_kernel >= 1 &&
+           s.conv_kernel <= 8;
+}
+
+void launch_deltanet(Context& ctx, const DeltaNetShape& shape, const DeltaNetRow* rows, std::size_t n_rows, Band mixed, Band z, Band b, Band a,
+                     const DeltaNetWeights& weights, const DeltaNetScratch& scratch, float* states, float* tails, float* /*unused*/, std::size_t slots,
+                     void* out, std::size_t out_stride, cudaStream_t stream) {
+    if (!deltanet_supports(shape))
+        throw std::invalid_argument("sepal_b200 deltanet: head_dim must be 128, value_heads a multiple of key_heads (at most 32 key heads), 1 to 8 conv taps");
+    if (n_rows == 0) return;
+    if (rows == nullptr || mixed.data == nullptr || z.data == nullptr || b.data == nullptr || a.data == nullptr || weights.conv == nullptr ||
+        weights.a_log == nullptr || weights.dt_bias == nullptr || weights.norm == nullptr || scratch.q == nullptr || scratch.k == nullptr ||
+        scratch.v == nullptr || scratch.decay == nullptr || scratch.beta == nullptr || states == nullptr || tails == nullptr || out == nullptr)
+        throw std::invalid_argument("sepal_b200 deltanet: null pointer");
+    for (std::size_t i = 0; i < n_rows; ++i) {
+        if (rows[i].length == 0) throw std::invalid_argument("sepal_b200 deltanet: row " + std::to_string(i) + " is empty");
+        if (i > 0 && rows[i].q_begin < rows[i - 1].q_begin + rows[i - 1].length) throw std::invalid_argument("sepal_b200 deltanet: rows must be sorted by their first token and must not overlap");
+        if (rows[i].slot >= slots) throw std::invalid_argument("sepal_b200 deltanet: row " + std::to_string(i) + " names a state slot that does not exist");
+        for (std::size_t o = 0; o < i; ++o)
+            if (rows[o].slot == rows[i].slot) throw std::invalid_argument("sepal_b200 deltanet: two rows of one call share a state slot");
+    }
+    check(cudaSetDevice(ctx.device), "cudaSetDevice");
+    if (ctx.table == nullptr || n_rows * sizeof(DeltaNetRow) > ctx.table_bytes / 2) throw std::invalid_argument("sepal_b200 deltanet: too many rows for the context's table");
+    char* table = static_cast<char*>(ctx.table) + (ctx.table_turn++ & 1u) * (ctx.table_bytes / 2);
+    check(cudaMemcpyAsync(table, rows, n_rows * sizeof(DeltaNetRow), cudaMemcpyHostToDevice, stream), "cudaMemcpyAsync(rows)");
+    DeltaParams p{};
+    p.rows = reinterpret_cast<const DeltaNetRow*>(table);
+    p.n_rows = static_cast<unsigned>(n_rows);
+    p.key_heads = shape.key_heads;
+    p.value_heads = shape.value_heads;
+    p.taps = shape.conv_kernel;
+    p.key_dim = shape.key_dim();
+    p.value_dim = shape.value_dim();
+    p.conv_dim = shape.conv_dim();
+    p.eps = shape.eps;
+    p.mixed = mixed.data;
+    p.z = z.data;
+    p.b = b.data;
+    p.a = a.data;
+    p.mixed_stride = mixed.stride;
+    p.z_stride = z.stride;
+    p.b_stride = b.stride;
+    p.a_stride = a.stride;
+    p.mixed_half = mixed.half ? 1u : 0u;
+    p.z_half = z.half ? 1u : 0u;
+    p.b_half = b.half ? 1u : 0u;
+    p.a_half = a.half ? 1u : 0u;
+    p.conv = weights.conv;
+    p.a_log = weights.a_log;
+    p.dt_bias = weights.dt_bias;
+    p.norm = weights.norm;
+    p.q = scratch.q;
+    p.k = scratch.k;
+    p.v = scratch.v;
+    p.decay = scratch.decay;
+    p.beta = scratch.beta;
+    p.states = states;
+    p.tails = tails;
+    p.out = static_cast<__half*>(out);
+    p.out_stride = out_stride;
+    const unsigned last = rows[n_rows - 1].q_begin + rows[n_rows - 1].length;
+    const std::size_t prepare_smem = static_cast<std::size_t>(p.conv_dim) * sizeof(float);
+    if (prepare_smem > 160 * 1024) throw std::invalid_argument("sepal_b200 deltanet: the convolution is wider than the prepare kernel's shared memory");
+    static bool configured[64] = {};
+    if (ctx.device >= 64 || !configured[ctx.device]) {
+        check(cudaFuncSetAttribute(deltanet_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024), "cudaFuncSetAttribute");
+        if (ctx.device < 64) configured[ctx.device] = true;
+    }
+    launch_kernel(deltanet_prepare_kernel, dim3(last), dim3(256), prepare_smem, stream, "deltanet_prepare_kernel launch", p);
+    count_launch();
+    if (shape.conv_kernel > 1) {
+        deltanet_tail_kernel<<<static_cast<unsigned>(n_rows), 256, 0, stream>>>(p);
+        check(cudaGetLastError(), "deltanet_tail_kernel launch");
+        count_launch();
+    }
+    launch_kernel(deltanet_scan_kernel, dim3(static_cast<unsigned>(n_rows), shape.value_heads), dim3(256), 0, stream, "deltanet_scan_kernel launch", p);
+    count_launch();
+}
+
+}  // namespace sepal::b200

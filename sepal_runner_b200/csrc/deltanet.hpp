@@ -1,0 +1,70 @@
+// The core of the Gated DeltaNet mixer between its projections, with the reference's arithmetic
+// (runner/include/sepal/ref/deltanet.hpp:33-330; docs/RUNNER.md:350-361): a depthwise causal convolution over the in-projection's
+// `mixed` band (K taps, the LAST tap on the current token, continued from the request's previous K - 1 inputs), SiLU, the split into
+// q, k (key heads) and v (value heads), L2 normalisation of q and k per head (x / sqrt(sum x^2 + 1e-6)), value head h reading key head
+// h / (value heads / key heads); per token and value head the gated delta rule on a float32 state S [dk, dv]:
+//     S <- decay * S;   S <- S + k (x) beta (v - k . S);   read = S^T q / sqrt(dk)
+// with decay = exp(-exp(A_log) softplus(a + dt_bias)) and beta = sigmoid(b) (a token reads the state after its own update); then the
+// RMSNorm of each head's read scaled by the norm weight itself (not 1 + w) and gated by silu(z), rounded to binary16 for out_proj.
+//
+// State. A request owns a slot: its recurrent state [value heads, dk, dv] float32 and the last K - 1 rows of `mixed`. A call holds runs
+// of consecutive tokens of different requests; a run continues its slot's state and leaves it updated, so a request cut into several
+// calls gives what it gives in one. The scan walks a run token by token (one CTA per run and value head, the state in registers): the
+// chunked form on the tensor cores is the next step for this row of the scope table.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+#include <cuda_runtime.h>
+
+#include "attention.hpp"
+#include "context.hpp"
+
+namespace sepal::b200 {
+
+struct DeltaNetShape {
+    std::uint32_t key_heads = 0, value_heads = 0;  // value_heads a multiple of key_heads
+    std::uint32_t head_dim = 128;                  // dk = dv = 128
+    std::uint32_t conv_kernel = 4;
+    float eps = 1.0e-6f;                           // of the gated norm
+    std::uint32_t key_dim() const { return key_heads * head_dim; }
+    std::uint32_t value_dim() const { return value_heads * head_dim; }
+    std::uint32_t conv_dim() const { return 2 * key_dim() + value_dim(); }
+};
+
+struct DeltaNetRow {
+    std::uint32_t q_begin;  // the run's first token in the flat list of the call
+    std::uint32_t length;
+    std::uint32_t slot;     // the request's state
+    std::uint32_t fresh;    // 1: the request starts here: its state and conv tail count as zero whatever the slot holds
+};
+
+/// The per-layer weights of the core (device, float32): conv [conv_dim, K]; a_log, dt_bias [value_heads]; norm [head_dim].
+struct DeltaNetWeights {
+    const float* conv = nullptr;
+    const float* a_log = nullptr;
+    const float* dt_bias = nullptr;
+    const float* norm = nullptr;
+};
+
+/// Scratch of one call (device, float32), sized for the call's tokens N: q, k [N, key_dim]; v [N, value_dim]; decay, beta [N, value_heads].
+struct DeltaNetScratch {
+    float* q = nullptr;
+    float* k = nullptr;
+    float* v = nullptr;
+    float* decay = nullptr;
+    float* beta = nullptr;
+};
+
+/// Both launches of a layer. mixed [N, conv_dim], z [N, value_dim], b and a [N, value_heads] are bands of the in-projection's output;
+/// states float32 [slots, value_heads, head_dim, head_dim]; tails float32 [2][slots, K - 1, conv_dim] (read from tails[turn], written
+/// to tails[turn ^ 1]; the caller flips `turn` after every call); out binary16 [N, value_dim] with row stride out_stride.
+/// `rows` is a HOST array sorted by q_begin.
+void launch_deltanet(Context& ctx, const DeltaNetShape& shape, const DeltaNetRow* rows, std::size_t n_rows, Band mixed, Band z, Band b, Band a,
+                     const DeltaNetWeights& weights, const DeltaNetScratch& scratch, float* states, float* tails_in, float* tails_out, std::size_t slots,
+                     void* out, std::size_t out_stride, cudaStream_t stream);
+
+bool deltanet_supports(const DeltaNetShape& shape);
+
+}  // namespace sepal::b200

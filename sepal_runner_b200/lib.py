@@ -57,6 +57,7 @@ SIGNATURES = {
     "sepal_b200_set_launch_overlap": (None, [_i32]),
     "sepal_b200_attention_prepare": (_i32, [_vp, _vp, _vp, _u64, _vp, _u64, _i32, _vp, _u64, _i32, _vp, _u64, _i32, _vp, _vp, _vp, _u64, _vp, _vp, _u64, _vp]),
     "sepal_b200_attention": (_i32, [_vp, _vp, _vp, _u64, _u64, _vp, _u64, _vp, _vp, _u64, _vp, _u64, _i32, _vp, _u64, _vp]),
+    "sepal_b200_deltanet": (_i32, [_vp, _vp, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _vp]),
     "sepal_b200_trunk_open_checkpoint": (_i32, [_i32, _vp, _vp, _vp]),
     "sepal_b200_trunk_save": (_i32, [_vp, C.c_char_p]),
     "sepal_b200_checkpoint_open": (_i32, [C.c_char_p, _vp]),
@@ -313,6 +314,35 @@ def attention(ctx, shape, rows, q, k_arena, v_arena, gate, out, stream=None):
     _check(ctx._lib.sepal_b200_attention(ctx._h, C.byref(shape), table, len(rows), q.shape[0], q.data_ptr(), q.stride(0), k_arena.data_ptr(), v_arena.data_ptr(),
                                          k_arena.shape[0], gate.data_ptr(), gate.stride(0), 1 if gate.dtype == torch.float16 else 0, out.data_ptr(),
                                          out.stride(0), _stream_ptr(stream)))
+
+
+class DeltaNetShape(C.Structure):
+    """sepal_b200_deltanet_shape."""
+
+    _fields_ = [("key_heads", _u32), ("value_heads", _u32), ("head_dim", _u32), ("conv_kernel", _u32), ("eps", C.c_float), ("reserved", _u32)]
+
+
+class DeltaNetRow(C.Structure):
+    """sepal_b200_deltanet_row."""
+
+    _fields_ = [("q_begin", _u32), ("length", _u32), ("slot", _u32), ("fresh", _u32)]
+
+
+def deltanet(ctx, shape, rows, mixed, z, b, a, conv, a_log, dt_bias, norm, states, tails, out, stream=None):
+    """The Gated DeltaNet core (sepal_b200_deltanet). rows: list of (q_begin, length, slot, fresh); mixed, z, b, a: torch bands of one
+    dtype (float16 or float32); states [slots, value_heads, 128, 128] and tails [slots, K - 1, conv_dim] float32, updated in place."""
+    import torch
+
+    table = (DeltaNetRow * len(rows))(*[DeltaNetRow(*r) for r in rows])
+    n = max((r[0] + r[1] for r in rows), default=0)
+    kd, vd = shape.key_heads * shape.head_dim, shape.value_heads * shape.head_dim
+    scratch = torch.empty(max(1, n * (2 * kd + vd + 2 * shape.value_heads)), dtype=torch.float32, device=out.device)
+    assert mixed.dtype == z.dtype == b.dtype == a.dtype
+    _check(ctx._lib.sepal_b200_deltanet(ctx._h, C.byref(shape), table, len(rows), mixed.data_ptr(), mixed.stride(0), z.data_ptr(), z.stride(0), b.data_ptr(),
+                                        b.stride(0), a.data_ptr(), a.stride(0), 1 if mixed.dtype == torch.float16 else 0, conv.data_ptr(), a_log.data_ptr(),
+                                        dt_bias.data_ptr(), norm.data_ptr(), scratch.data_ptr(), states.data_ptr(), tails.data_ptr(), states.shape[0],
+                                        out.data_ptr(), out.stride(0), _stream_ptr(stream)))
+    return scratch  # kept alive by the caller until the stream has run
 
 
 class TrunkConfig(C.Structure):

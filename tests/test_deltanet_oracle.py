@@ -1,0 +1,44 @@
+"""The DeltaNet oracle against hand-checkable cases (no GPU): the restated rules of runner/include/sepal/ref/deltanet.hpp."""
+import numpy as np
+
+from oracle import deltanet_oracle as do
+
+
+def test_causal_conv_puts_the_last_tap_on_the_current_token_and_keeps_a_tail():
+    x = np.arange(1, 7, dtype=np.float64).reshape(3, 2)  # tokens [1, 2], [3, 4], [5, 6]
+    kernel = np.array([[10.0, 100.0, 1000.0], [1.0, 0.0, 0.0]])
+    out, tail = do.causal_conv(x, kernel, np.array([[7.0, 8.0], [9.0, 11.0]]))
+    # channel 0 at token 0: 10 * tail[0] + 100 * tail[1] + 1000 * x[0]
+    assert out[0, 0] == 10 * 7 + 100 * 9 + 1000 * 1 and out[1, 0] == 10 * 9 + 100 * 1 + 1000 * 3 and out[2, 0] == 10 * 1 + 100 * 3 + 1000 * 5
+    assert out[0, 1] == 8 and out[1, 1] == 11 and out[2, 1] == 2  # the first tap reads two tokens back
+    assert np.array_equal(tail, x[1:])
+    out2, tail2 = do.causal_conv(x[:1], kernel, np.array([[7.0, 8.0], [9.0, 11.0]]))
+    assert np.array_equal(tail2, [[9.0, 11.0], [1.0, 2.0]]) and out2[0, 0] == out[0, 0]  # a run shorter than the tail shifts it
+
+
+def test_delta_rule_one_head_by_hand_and_continuation():
+    rng = np.random.default_rng(0)
+    dim, kh, vh, t = 4, 1, 2, 5
+    conv_dim = 2 * kh * dim + vh * dim
+    mixed = rng.standard_normal((t, conv_dim))
+    z = rng.standard_normal((t, vh * dim))
+    b = rng.standard_normal((t, vh))
+    a = rng.standard_normal((t, vh))
+    conv = rng.standard_normal((conv_dim, 4)) * 0.5
+    a_log, dt_bias, norm = rng.standard_normal(vh) * 0.1, rng.standard_normal(vh) * 0.1, rng.standard_normal(dim)
+    out, state, tail = do.core(mixed, z, b, a, conv, a_log, dt_bias, norm, kh, vh, dim, 1e-6)
+    # by hand for token 0 of value head 1: S = k (x) beta v after one step; read = S^T q / 2
+    act = do.silu(mixed[0] * conv[:, 3])  # the tail is zero: only the last tap sees the token
+    q, k, v = act[:4], act[4:8], act[12:16]
+    q, k = q / np.sqrt(q @ q + 1e-6), k / np.sqrt(k @ k + 1e-6)
+    beta = do.sigmoid(b[0, 1])
+    read = np.outer(k, beta * v).T @ q / 2.0
+    want = read / np.sqrt((read * read).mean() + 1e-6) * norm * do.silu(z[0, 4:8])
+    assert np.allclose(out[0, 4:8], want)
+    # two runs give what one gives
+    o1, s1, t1 = do.core(mixed[:2], z[:2], b[:2], a[:2], conv, a_log, dt_bias, norm, kh, vh, dim, 1e-6)
+    o2, s2, t2 = do.core(mixed[2:], z[2:], b[2:], a[2:], conv, a_log, dt_bias, norm, kh, vh, dim, 1e-6, state=s1, tail=t1)
+    assert np.allclose(np.concatenate([o1, o2]), out) and np.allclose(s2, state) and np.allclose(t2, tail)
+    # the decay is in (0, 1]
+    d = np.exp(-np.exp(a_log)[None, :] * do.softplus(a + dt_bias[None, :]))
+    assert (d > 0).all() and (d <= 1).all()

@@ -192,7 +192,10 @@ typedef struct sepal_b200_trunk_config {
      * the in-projection's bands, key/value caches per layer) instead of the fixed wiring. Then attn_q = 2 * heads * head_dim,
      * attn_kv = kv_heads * head_dim, attn_o = heads * head_dim, head_dim 128 or 256. */
     uint32_t attn_heads, attn_kv_heads, attn_head_dim, attn_rotary_dims;
-    uint32_t reserved;
+    /* dn_value_heads > 0: the DeltaNet layers run the real core (sepal_b200_deltanet on the in-projection's [qkv; z; b; a] bands, a
+     * recurrent state and a convolution tail per request and layer). Then dn_v = 128 * dn_value_heads and dn_in = 256 * dn_key_heads +
+     * 256 * dn_value_heads + 2 * dn_value_heads. dn_conv_kernel: 0 = 4 taps. */
+    uint32_t dn_key_heads, dn_value_heads, dn_conv_kernel;
     double rope_theta;                    /* 0: 1e7 */
 } sepal_b200_trunk_config;
 SEPAL_B200_API int32_t sepal_b200_trunk_open(int32_t device, const sepal_b200_trunk_config* config, sepal_b200_trunk** out);
@@ -321,7 +324,8 @@ SEPAL_B200_API int32_t sepal_b200_trunk_run(sepal_b200_trunk* trunk, const uint3
 SEPAL_B200_API int32_t sepal_b200_trunk_score(sepal_b200_trunk* trunk, uint64_t n_requests, const uint32_t* tokens, const uint64_t* offsets,
                                               float* last_hidden, double* times_s);
 /* Copies a stored weight to the host (size-query protocol: host_out NULL only reports *needed). which: 0 embedding, 1 input norm,
- * 2 mixer in-projection, 3 mixer out-projection, 4 post norm, 5 packed [gate; up], 6 down, 7 / 8 the attention core's q / k head norms. */
+ * 2 mixer in-projection, 3 mixer out-projection, 4 post norm, 5 packed [gate; up], 6 down, 7 / 8 the attention core's q / k head norms,
+ * 9 .. 12 the DeltaNet core's convolution, A_log, dt_bias and norm weight. */
 SEPAL_B200_API int32_t sepal_b200_trunk_weight(sepal_b200_trunk* trunk, uint32_t layer, int32_t which, void* host_out, uint64_t capacity,
                                                uint64_t* needed);
 SEPAL_B200_API int32_t sepal_b200_trunk_info(sepal_b200_trunk* trunk, uint64_t* gemm_flops_per_token, uint64_t* weight_bytes);

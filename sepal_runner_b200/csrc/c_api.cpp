@@ -249,6 +249,9 @@ TrunkConfig trunk_config_of(const sepal_b200_trunk_config& config) {
     c.attn_head_dim = config.attn_head_dim;
     c.attn_rotary_dims = config.attn_rotary_dims;
     if (config.rope_theta > 0.0) c.rope_theta = config.rope_theta;
+    c.dn_key_heads = config.dn_key_heads;
+    c.dn_value_heads = config.dn_value_heads;
+    if (config.dn_conv_kernel != 0) c.dn_conv_kernel = config.dn_conv_kernel;
     return c;
 }
 }  // namespace
@@ -489,7 +492,7 @@ int32_t sepal_b200_trunk_score(sepal_b200_trunk* trunk, uint64_t n_requests, con
 int32_t sepal_b200_trunk_weight(sepal_b200_trunk* trunk, uint32_t layer, int32_t which, void* host_out, uint64_t capacity, uint64_t* needed) {
     return guarded([&] {
         require(trunk, "trunk");
-        if (which < 0 || which > 8) throw std::invalid_argument("which must be 0 .. 8");
+        if (which < 0 || which > 12) throw std::invalid_argument("which must be 0 .. 12");
         const std::size_t bytes = trunk->trunk.weight(layer, static_cast<TrunkWeight>(which), host_out, capacity);
         if (needed != nullptr) *needed = bytes;
     });

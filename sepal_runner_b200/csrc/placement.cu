@@ -199,6 +199,26 @@ void Trunk::place_random() {
             launch_fill_normal_float(L.k_norm, c.attn_head_dim, ++stream_seed, 0.02f, stream_);
             weight_bytes_ += 2 * c.attn_head_dim * 4;
         }
+        if (!L.attention && real_deltanet()) {
+            // small weights of the core: a convolution that passes signal (std 0.5), A_log and dt_bias around zero, a norm weight around one
+            const DeltaNetShape d = deltanet_shape();
+            L.dn_conv = static_cast<float*>(alloc(static_cast<std::size_t>(d.conv_dim()) * d.conv_kernel * 4));
+            L.dn_a_log = static_cast<float*>(alloc(d.value_heads * 4));
+            L.dn_dt_bias = static_cast<float*>(alloc(d.value_heads * 4));
+            L.dn_norm = static_cast<float*>(alloc(128 * 4));
+            launch_fill_normal_float(L.dn_conv, static_cast<std::size_t>(d.conv_dim()) * d.conv_kernel, ++stream_seed, 0.5f, stream_);
+            launch_fill_normal_float(L.dn_a_log, d.value_heads, ++stream_seed, 0.5f, stream_);
+            launch_fill_normal_float(L.dn_dt_bias, d.value_heads, ++stream_seed, 0.5f, stream_);
+            std::vector<float> ones(128);
+            std::uint64_t x = (c.seed + l) * 0x9E3779B97F4A7C15ull;
+            for (float& w : ones) {
+                x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull; x ^= x >> 27; x *= 0x94D049BB133111EBull; x ^= x >> 31;
+                w = 1.0f + 0.1f * (static_cast<float>(x >> 40) / 16777216.0f - 0.5f);
+            }
+            check(cudaMemcpyAsync(L.dn_norm, ones.data(), 128 * 4, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(norm)");
+            check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");  // the host vector goes away
+            weight_bytes_ += (static_cast<std::size_t>(d.conv_dim()) * d.conv_kernel + 2 * d.value_heads + 128) * 4;
+        }
         L.mix_in = alloc(static_cast<std::size_t>(L.mix_in_n) * H * 2);
         fill_half(L.mix_in, static_cast<std::size_t>(L.mix_in_n) * H);
         L.mix_out = alloc(H * static_cast<std::size_t>(L.mix_out_k) * 2);
@@ -290,6 +310,22 @@ void Trunk::place_checkpoint(const Checkpoint& ck) {
             const std::string d = pre + "linear_attn.";
             stack({d + "in_proj_qkv.weight", d + "in_proj_z.weight", d + "in_proj_b.weight", d + "in_proj_a.weight"}, L.mix_in_n, H, ElementType::F16, L.mix_in);
             up.put(need(ck, d + "out_proj.weight", H, L.mix_out_k), ElementType::F16, L.mix_out);
+            if (real_deltanet()) {
+                const DeltaNetShape ds = deltanet_shape();
+                const TensorView& conv = ck.at(d + "conv1d.weight");  // [channels, 1, taps] in the checkpoint: the same values as [channels, taps]
+                if (conv.elements() != static_cast<std::uint64_t>(ds.conv_dim()) * ds.conv_kernel || conv.shape.empty() || conv.shape.front() != ds.conv_dim() ||
+                    conv.shape.back() != ds.conv_kernel)
+                    throw std::invalid_argument("tensor '" + d + "conv1d.weight' must be [" + std::to_string(ds.conv_dim()) + ", 1, " + std::to_string(ds.conv_kernel) + "]");
+                L.dn_conv = static_cast<float*>(alloc(static_cast<std::size_t>(ds.conv_dim()) * ds.conv_kernel * 4));
+                L.dn_a_log = static_cast<float*>(alloc(ds.value_heads * 4));
+                L.dn_dt_bias = static_cast<float*>(alloc(ds.value_heads * 4));
+                L.dn_norm = static_cast<float*>(alloc(128 * 4));
+                up.put(conv, ElementType::F32, L.dn_conv);
+                up.put(need(ck, d + "A_log", ds.value_heads, 0), ElementType::F32, L.dn_a_log);
+                up.put(need(ck, d + "dt_bias", ds.value_heads, 0), ElementType::F32, L.dn_dt_bias);
+                up.put(need(ck, d + "norm.weight", 128, 0), ElementType::F32, L.dn_norm);
+                weight_bytes_ += (static_cast<std::size_t>(ds.conv_dim()) * ds.conv_kernel + 2 * ds.value_heads + 128) * 4;
+            }
         }
         weight_bytes_ += (static_cast<std::size_t>(L.mix_in_n) * H + H * static_cast<std::size_t>(L.mix_out_k)) * 2 + 2 * H * 4;
         const std::string mlp = pre + "mlp.";
@@ -352,6 +388,18 @@ void Trunk::place_saved(const Checkpoint& ck) {
             up.put(same_type(need(ck, pre + "k_norm", c.attn_head_dim, 0), ElementType::F32), ElementType::F32, L.k_norm);
             weight_bytes_ += 2 * c.attn_head_dim * 4;
         }
+        if (!L.attention && real_deltanet()) {
+            const DeltaNetShape ds = deltanet_shape();
+            L.dn_conv = static_cast<float*>(alloc(static_cast<std::size_t>(ds.conv_dim()) * ds.conv_kernel * 4));
+            L.dn_a_log = static_cast<float*>(alloc(ds.value_heads * 4));
+            L.dn_dt_bias = static_cast<float*>(alloc(ds.value_heads * 4));
+            L.dn_norm = static_cast<float*>(alloc(128 * 4));
+            up.put(same_type(need(ck, pre + "dn_conv", ds.conv_dim(), ds.conv_kernel), ElementType::F32), ElementType::F32, L.dn_conv);
+            up.put(same_type(need(ck, pre + "dn_a_log", ds.value_heads, 0), ElementType::F32), ElementType::F32, L.dn_a_log);
+            up.put(same_type(need(ck, pre + "dn_dt_bias", ds.value_heads, 0), ElementType::F32), ElementType::F32, L.dn_dt_bias);
+            up.put(same_type(need(ck, pre + "dn_norm", 128, 0), ElementType::F32), ElementType::F32, L.dn_norm);
+            weight_bytes_ += (static_cast<std::size_t>(ds.conv_dim()) * ds.conv_kernel + 2 * ds.value_heads + 128) * 4;
+        }
         up.put(same_type(need(ck, pre + "mix_in", L.mix_in_n, H), ElementType::F16), ElementType::F16, L.mix_in);
         up.put(same_type(need(ck, pre + "mix_out", H, L.mix_out_k), ElementType::F16), ElementType::F16, L.mix_out);
         weight_bytes_ += (static_cast<std::size_t>(L.mix_in_n) * H + H * static_cast<std::size_t>(L.mix_out_k)) * 2 + 2 * H * 4;
@@ -401,6 +449,13 @@ void Trunk::save(const std::string& path) {
         if (L.q_norm != nullptr) {
             add(pre + "q_norm", ElementType::F32, {c.attn_head_dim}, L.q_norm);
             add(pre + "k_norm", ElementType::F32, {c.attn_head_dim}, L.k_norm);
+        }
+        if (L.dn_conv != nullptr) {
+            const DeltaNetShape ds = deltanet_shape();
+            add(pre + "dn_conv", ElementType::F32, {ds.conv_dim(), ds.conv_kernel}, L.dn_conv);
+            add(pre + "dn_a_log", ElementType::F32, {ds.value_heads}, L.dn_a_log);
+            add(pre + "dn_dt_bias", ElementType::F32, {ds.value_heads}, L.dn_dt_bias);
+            add(pre + "dn_norm", ElementType::F32, {128}, L.dn_norm);
         }
         if (!c.mlp_int8) {
             add(pre + "gate_up", ElementType::F16, {2 * I, H}, L.gate_up);

@@ -2,6 +2,7 @@
 
 #include "ptx.cuh"
 
+#include <algorithm>
 #include <cstring>
 #include <stdexcept>
 #include <string>
@@ -215,10 +216,13 @@ Trunk::Trunk(int device, const TrunkConfig& config, const Checkpoint* checkpoint
         c.max_call_tokens == 0 || c.vocab == 0 ||
         (c.attn_heads != 0 && (c.attn_kv_heads == 0 || c.attn_heads % c.attn_kv_heads != 0 || (c.attn_head_dim != 128 && c.attn_head_dim != 256) ||
                                c.attn_q != 2 * c.attn_heads * c.attn_head_dim || c.attn_kv != c.attn_kv_heads * c.attn_head_dim ||
-                               c.attn_o != c.attn_heads * c.attn_head_dim || c.attn_rotary_dims % 2 != 0 || c.attn_rotary_dims > c.attn_head_dim)))
+                               c.attn_o != c.attn_heads * c.attn_head_dim || c.attn_rotary_dims % 2 != 0 || c.attn_rotary_dims > c.attn_head_dim)) ||
+        (c.dn_value_heads != 0 && (!deltanet_supports(deltanet_shape()) || c.dn_v != c.dn_value_heads * 128 ||
+                                   c.dn_in != 2 * c.dn_key_heads * 128 + 2 * c.dn_value_heads * 128 + 2 * c.dn_value_heads)))
         throw std::invalid_argument("sepal_b200 trunk: widths must be multiples of 128 (k and v, the fused in-projection: of 8), the bands the "
                                     "out-projections read inside the in-projections, and layers, vocabulary and call size non-zero; with attn_heads set, attn_q = 2 heads "
-                                    "head_dim, attn_kv = kv_heads head_dim, attn_o = heads head_dim, head_dim 128 or 256");
+                                    "head_dim, attn_kv = kv_heads head_dim, attn_o = heads head_dim, head_dim 128 or 256; with dn_value_heads set, dn_v = 128 value heads "
+                                    "and dn_in = 256 key heads + 256 value heads + 2 value heads");
     check(cudaSetDevice(device), "cudaSetDevice");
     check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
     for (auto& e : ev_) check(cudaEventCreate(&e), "cudaEventCreate");
@@ -237,9 +241,14 @@ Trunk::Trunk(int device, const TrunkConfig& config, const Checkpoint* checkpoint
     a1_ = alloc(T * H * 2);
     p_ = alloc(T * static_cast<std::size_t>(p_width_) * 2);
     a3_ = alloc(T * I * 2);
-    if (real_attention()) {
-        q_ = alloc(T * static_cast<std::size_t>(c.attn_o) * 2);
-        a2_ = alloc(T * static_cast<std::size_t>(c.attn_o) * 2);
+    if (real_attention()) q_ = alloc(T * static_cast<std::size_t>(c.attn_o) * 2);
+    if (real_attention() || real_deltanet()) {
+        const std::size_t widest = std::max<std::size_t>(real_attention() ? c.attn_o : 0, real_deltanet() ? c.dn_v : 0);
+        a2_ = alloc(T * widest * 2);
+    }
+    if (real_deltanet()) {
+        const DeltaNetShape d = deltanet_shape();
+        dn_scratch_ = static_cast<float*>(alloc(T * (2 * static_cast<std::size_t>(d.key_dim()) + d.value_dim() + 2 * d.value_heads) * 4));
     }
     tokens_dev_ = static_cast<std::uint32_t*>(alloc(2 * T * 4));
     check(cudaMallocHost(reinterpret_cast<void**>(&tokens_pinned_), 2 * T * 4), "cudaMallocHost");
@@ -255,6 +264,8 @@ Trunk::~Trunk() {
     for (Layer& L : layers_) {
         if (L.k_cache != nullptr) (void)cudaFree(L.k_cache);
         if (L.v_cache != nullptr) (void)cudaFree(L.v_cache);
+        if (L.dn_states != nullptr) (void)cudaFree(L.dn_states);
+        if (L.dn_tails != nullptr) (void)cudaFree(L.dn_tails);
     }
     for (cudaEvent_t e : call_done_)
         if (e != nullptr) (void)cudaEventDestroy(e);
@@ -292,7 +303,36 @@ void Trunk::reserve_cache(std::size_t tokens) {
     cache_tokens_ = tokens;
 }
 
-void Trunk::forward_call(const std::uint32_t* tokens_dev, std::size_t rows, const std::vector<AttentionRow>& runs) {
+DeltaNetShape Trunk::deltanet_shape() const {
+    DeltaNetShape d;
+    d.key_heads = cfg_.dn_key_heads;
+    d.value_heads = cfg_.dn_value_heads;
+    d.head_dim = 128;
+    d.conv_kernel = cfg_.dn_conv_kernel;
+    d.eps = cfg_.eps;
+    return d;
+}
+
+// The recurrent states and convolution tails of the DeltaNet layers, one slot for each request of a run or score call. They grow,
+// never shrink; a request's first run starts from zero whatever its slot holds.
+void Trunk::reserve_states(std::size_t slots) {
+    if (!real_deltanet() || slots <= state_slots_) return;
+    check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+    const DeltaNetShape d = deltanet_shape();
+    const std::size_t state_bytes = slots * d.value_heads * 128 * 128 * 4;
+    const std::size_t tail_bytes = slots * std::max<std::size_t>(d.conv_kernel - 1, 1) * d.conv_dim() * 4;
+    for (Layer& L : layers_) {
+        if (L.attention) continue;
+        if (L.dn_states != nullptr) (void)cudaFree(L.dn_states);
+        if (L.dn_tails != nullptr) (void)cudaFree(L.dn_tails);
+        L.dn_states = L.dn_tails = nullptr;
+        check(cudaMalloc(reinterpret_cast<void**>(&L.dn_states), state_bytes), "cudaMalloc(DeltaNet states)");
+        check(cudaMalloc(reinterpret_cast<void**>(&L.dn_tails), tail_bytes), "cudaMalloc(DeltaNet tails)");
+    }
+    state_slots_ = slots;
+}
+
+void Trunk::forward_call(const std::uint32_t* tokens_dev, std::size_t rows, const std::vector<AttentionRow>& runs, const std::vector<DeltaNetRow>& dn_runs) {
     const TrunkConfig& c = cfg_;
     const std::size_t H = c.hidden, I = c.intermediate;
     if (layers_.empty()) {
@@ -317,6 +357,21 @@ void Trunk::forward_call(const std::uint32_t* tokens_dev, std::size_t rows, cons
             launch_attention_prepare(ctx_, shape, runs.data(), runs.size(), q_gate, k, v, L.q_norm, L.k_norm, q_, c.attn_o, L.k_cache, L.v_cache, cache_tokens_, stream_);
             launch_attention(ctx_, shape, runs.data(), runs.size(), rows, q_, c.attn_o, L.k_cache, L.v_cache, cache_tokens_, q_gate, a2_, c.attn_o, stream_);
             launch_gemm_f16(ctx_, a2_, c.attn_o, L.mix_out, L.mix_out_k, x_, H, false, rows, H, L.mix_out_k, Epilogue::Add, -1, stream_);
+        } else if (!L.attention && real_deltanet()) {
+            // [qkv; z; b; a] bands of p -> the DeltaNet core -> a2 -> out_proj
+            const DeltaNetShape d = deltanet_shape();
+            const __half* pm = static_cast<const __half*>(p_);
+            const Band mixed{pm, p_width_, true}, z{pm + d.conv_dim(), p_width_, true}, b{pm + d.conv_dim() + d.value_dim(), p_width_, true},
+                a{pm + d.conv_dim() + d.value_dim() + d.value_heads, p_width_, true};
+            DeltaNetScratch sc;
+            sc.q = dn_scratch_;
+            sc.k = sc.q + rows * d.key_dim();
+            sc.v = sc.k + rows * d.key_dim();
+            sc.decay = sc.v + rows * d.value_dim();
+            sc.beta = sc.decay + rows * d.value_heads;
+            launch_deltanet(ctx_, d, dn_runs.data(), dn_runs.size(), mixed, z, b, a, DeltaNetWeights{L.dn_conv, L.dn_a_log, L.dn_dt_bias, L.dn_norm}, sc, L.dn_states,
+                            L.dn_tails, nullptr, state_slots_, a2_, c.dn_v, stream_);
+            launch_gemm_f16(ctx_, a2_, c.dn_v, L.mix_out, L.mix_out_k, x_, H, false, rows, H, L.mix_out_k, Epilogue::Add, -1, stream_);
         } else {
             const __half* band = static_cast<const __half*>(p_) + L.band;
             launch_gemm_f16(ctx_, band, p_width_, L.mix_out, L.mix_out_k, x_, H, false, rows, H, L.mix_out_k, Epilogue::Add, -1, stream_);
@@ -340,6 +395,7 @@ void Trunk::run(const std::uint32_t* tokens, std::size_t n, float* last_hidden, 
     check(cudaSetDevice(ctx_.device), "cudaSetDevice");
     const std::size_t H = cfg_.hidden, T = cfg_.max_call_tokens;
     reserve_cache(n);
+    reserve_states(1);
     check(cudaEventRecord(ev_[0], stream_), "cudaEventRecord");
     for (std::size_t start = 0; start < n; start += T) {
         const std::size_t rows = n - start < T ? n - start : T;
@@ -347,7 +403,8 @@ void Trunk::run(const std::uint32_t* tokens, std::size_t n, float* last_hidden, 
         std::memcpy(tokens_pinned_, tokens + start, rows * 4);
         check(cudaMemcpyAsync(tokens_dev_, tokens_pinned_, rows * 4, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(tokens)");
         // one run: the request's tokens start .. start + rows, its cache range starting at 0, `start` tokens already in it
-        forward_call(tokens_dev_, rows, {AttentionRow{0u, static_cast<std::uint32_t>(rows), 0u, static_cast<std::uint32_t>(start)}});
+        forward_call(tokens_dev_, rows, {AttentionRow{0u, static_cast<std::uint32_t>(rows), 0u, static_cast<std::uint32_t>(start)}},
+                     {DeltaNetRow{0u, static_cast<std::uint32_t>(rows), 0u, start == 0 ? 1u : 0u}});
         if (all_hidden != nullptr)
             check(cudaMemcpyAsync(all_hidden + start * H, x_, rows * H * 4, cudaMemcpyDeviceToHost, stream_), "cudaMemcpyAsync(hidden)");
         if (start + rows == n)
@@ -392,6 +449,7 @@ void Trunk::score(std::size_t n_requests, const std::uint32_t* tokens, const std
     check(cudaSetDevice(ctx_.device), "cudaSetDevice");
     if (offsets[n_requests] > 0xFFFFFFFFull) throw std::invalid_argument("sepal_b200 trunk: more than 2^32 tokens in one call");
     reserve_cache(offsets[n_requests]);
+    reserve_states(n_requests);
     struct Call {
         std::size_t first, count;  // its segments
     };
@@ -432,14 +490,17 @@ void Trunk::score(std::size_t n_requests, const std::uint32_t* tokens, const std
             check(cudaMemcpyAsync(dev, pinned, rows * 4, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(tokens)");
             // a request's cache range starts where its tokens start in the flat list; a segment continues what the request's earlier ones left
             std::vector<AttentionRow> runs;
+            std::vector<DeltaNetRow> dn_runs;
             std::size_t at = 0;
             for (std::size_t i = calls[c].first; i < calls[c].first + calls[c].count; ++i) {
                 const Segment& sg = segments[i];
                 runs.push_back(AttentionRow{static_cast<std::uint32_t>(at), static_cast<std::uint32_t>(sg.end - sg.begin), static_cast<std::uint32_t>(offsets[sg.request]),
                                             static_cast<std::uint32_t>(sg.begin - offsets[sg.request])});
+                dn_runs.push_back(DeltaNetRow{static_cast<std::uint32_t>(at), static_cast<std::uint32_t>(sg.end - sg.begin), static_cast<std::uint32_t>(sg.request),
+                                              sg.begin == offsets[sg.request] ? 1u : 0u});
                 at += sg.end - sg.begin;
             }
-            forward_call(dev, rows, runs);
+            forward_call(dev, rows, runs, dn_runs);
             std::size_t row = 0, slot = 0;
             for (std::size_t i = calls[c].first; i < calls[c].first + calls[c].count; ++i) {
                 row += segments[i].end - segments[i].begin;
@@ -495,6 +556,10 @@ std::size_t Trunk::weight(std::uint32_t layer, TrunkWeight which, void* host_out
         case TrunkWeight::Down: src = L.down; bytes = H * I * (c.mlp_int8 ? 1 : 2); break;
         case TrunkWeight::QNorm: src = L.q_norm; bytes = L.q_norm != nullptr ? static_cast<std::size_t>(c.attn_head_dim) * 4 : 0; break;
         case TrunkWeight::KNorm: src = L.k_norm; bytes = L.k_norm != nullptr ? static_cast<std::size_t>(c.attn_head_dim) * 4 : 0; break;
+        case TrunkWeight::DnConv: src = L.dn_conv; bytes = L.dn_conv != nullptr ? static_cast<std::size_t>(deltanet_shape().conv_dim()) * c.dn_conv_kernel * 4 : 0; break;
+        case TrunkWeight::DnALog: src = L.dn_a_log; bytes = L.dn_a_log != nullptr ? static_cast<std::size_t>(c.dn_value_heads) * 4 : 0; break;
+        case TrunkWeight::DnDtBias: src = L.dn_dt_bias; bytes = L.dn_dt_bias != nullptr ? static_cast<std::size_t>(c.dn_value_heads) * 4 : 0; break;
+        case TrunkWeight::DnNorm: src = L.dn_norm; bytes = L.dn_norm != nullptr ? 128 * 4 : 0; break;
         default: throw std::invalid_argument("sepal_b200 trunk: no such weight");
         }
     }

@@ -23,6 +23,7 @@
 
 #include "attention.hpp"
 #include "checkpoint.hpp"
+#include "deltanet.hpp"
 
 #include "gemm.hpp"
 
@@ -41,14 +42,16 @@ struct TrunkConfig {
     // attention, output gate) instead of the fixed wiring; then attn_q = 2 * heads * head_dim (query and gate), attn_kv = kv_heads *
     // head_dim, attn_o = heads * head_dim.
     std::uint32_t attn_heads = 0, attn_kv_heads = 0, attn_head_dim = 0, attn_rotary_dims = 0;
-    std::uint32_t reserved = 0;
+    // dn_value_heads > 0: the DeltaNet layers run the real core (convolution, gated delta rule, gated norm) instead of the fixed wiring;
+    // then dn_in = 2 key_dim + 2 value_dim + 2 value_heads ([qkv; z; b; a]) and dn_v = value_dim, with heads of 128.
+    std::uint32_t dn_key_heads = 0, dn_value_heads = 0, dn_conv_kernel = 4;
     double rope_theta = 1.0e7;
 };
 
 /// The value of the "format" metadata key of a file written by Trunk::save.
 extern const char* const kSavedFormat;
 
-enum class TrunkWeight : int { Embedding = 0, NormIn = 1, MixIn = 2, MixOut = 3, NormPost = 4, GateUp = 5, Down = 6, QNorm = 7, KNorm = 8 };
+enum class TrunkWeight : int { Embedding = 0, NormIn = 1, MixIn = 2, MixOut = 3, NormPost = 4, GateUp = 5, Down = 6, QNorm = 7, KNorm = 8, DnConv = 9, DnALog = 10, DnDtBias = 11, DnNorm = 12 };
 
 class Trunk {
 public:
@@ -100,6 +103,12 @@ private:
         W8gMatrix gate_up_q, down_q;
         float* q_norm = nullptr;  // attention layers with the real core: per-head norm weights [head_dim]
         float* k_norm = nullptr;
+        float* dn_conv = nullptr;     // DeltaNet layers with the real core: [conv_dim, taps], [value heads], [value heads], [128]
+        float* dn_a_log = nullptr;
+        float* dn_dt_bias = nullptr;
+        float* dn_norm = nullptr;
+        float* dn_states = nullptr;   // [slots, value heads, 128, 128]: the requests being served
+        float* dn_tails = nullptr;    // [slots, taps - 1, conv_dim]
         void* k_cache = nullptr;  // binary16 [arena tokens, kv width]: the keys (normed, rotated) and values of the requests being served
         void* v_cache = nullptr;
         float* gate_up_scales = nullptr;  // mlp_int8: the quantiser's float32 scales [2 I, hidden / 128] and [hidden, I / 128]
@@ -111,9 +120,12 @@ private:
     void place_saved(const Checkpoint& checkpoint);
     void shape_layer(std::uint32_t l);
     void prepare_mlp_scales(Layer& L);
-    void forward_call(const std::uint32_t* tokens_dev, std::size_t rows, const std::vector<AttentionRow>& runs);
+    void forward_call(const std::uint32_t* tokens_dev, std::size_t rows, const std::vector<AttentionRow>& runs, const std::vector<DeltaNetRow>& dn_runs);
     void reserve_cache(std::size_t tokens);
+    void reserve_states(std::size_t slots);
     bool real_attention() const { return cfg_.attn_heads != 0; }
+    bool real_deltanet() const { return cfg_.dn_value_heads != 0; }
+    DeltaNetShape deltanet_shape() const;
 
     TrunkConfig cfg_;
     Context ctx_;
@@ -129,6 +141,8 @@ private:
     void* q_ = nullptr;          // binary16 [max_call_tokens, attn_o]: normed, rotated queries
     void* a2_ = nullptr;         // binary16 [max_call_tokens, attn_o]: the attention output, o_proj's operand
     std::size_t cache_tokens_ = 0;
+    std::size_t state_slots_ = 0;
+    float* dn_scratch_ = nullptr;  // q, k, v, decay, beta of one call
     std::uint32_t* tokens_dev_ = nullptr;     // two buffers of max_call_tokens: a call's ids are copied while the call before it runs
     std::uint32_t* tokens_pinned_ = nullptr;  // likewise
     float* out_pinned_ = nullptr;             // kMaxCallRows rows of hidden floats, twice

@@ -351,12 +351,12 @@ class TrunkConfig(C.Structure):
     _fields_ = [("layers", _u32), ("hidden", _u32), ("intermediate", _u32), ("vocab", _u32), ("attn_q", _u32), ("attn_kv", _u32),
                 ("dn_in", _u32), ("dn_v_offset", _u32), ("dn_v", _u32), ("max_call_tokens", _u32), ("mlp_int8", _u32), ("eps", C.c_float),
                 ("seed", _u64), ("attn_o", _u32), ("attn_heads", _u32), ("attn_kv_heads", _u32), ("attn_head_dim", _u32), ("attn_rotary_dims", _u32),
-                ("reserved", _u32), ("rope_theta", C.c_double)]
+                ("dn_key_heads", _u32), ("dn_value_heads", _u32), ("dn_conv_kernel", _u32), ("rope_theta", C.c_double)]
 
     def __init__(self, **kw):
         base = dict(layers=36, hidden=2560, intermediate=9728, vocab=151936, attn_q=4096, attn_kv=1024, dn_in=8192, dn_v_offset=4096, dn_v=2048,
                     max_call_tokens=4096, mlp_int8=0, eps=1e-6, seed=1, attn_o=0, attn_heads=0, attn_kv_heads=0, attn_head_dim=0, attn_rotary_dims=0,
-                    reserved=0, rope_theta=1.0e7)
+                    dn_key_heads=0, dn_value_heads=0, dn_conv_kernel=4, rope_theta=1.0e7)
         base.update(kw)
         super().__init__(**base)
 
@@ -364,7 +364,8 @@ class TrunkConfig(C.Structure):
 class Trunk:
     """The synthetic GEMM-chain trunk (sepal_b200_trunk_*): whole requests of host token ids in, final hidden states out."""
 
-    WEIGHTS = {"embedding": 0, "norm_in": 1, "mix_in": 2, "mix_out": 3, "norm_post": 4, "gate_up": 5, "down": 6, "q_norm": 7, "k_norm": 8}
+    WEIGHTS = {"embedding": 0, "norm_in": 1, "mix_in": 2, "mix_out": 3, "norm_post": 4, "gate_up": 5, "down": 6, "q_norm": 7, "k_norm": 8, "dn_conv": 9, "dn_a_log": 10,
+               "dn_dt_bias": 11, "dn_norm": 12}
 
     def __init__(self, device: int = 0, config: Optional[TrunkConfig] = None, checkpoint: "Optional[Checkpoint]" = None) -> None:
         self._lib = library()
@@ -427,7 +428,7 @@ class Trunk:
         code = self.WEIGHTS[which]
         needed = _u64()
         _check(self._lib.sepal_b200_trunk_weight(self._h, layer, code, None, 0, C.byref(needed)))
-        is_norm = code in (1, 4, 7, 8)
+        is_norm = code in (1, 4, 7, 8, 9, 10, 11, 12)
         int8 = self.config.mlp_int8 and code in (5, 6)
         out = np.empty(needed.value // (4 if is_norm else 1 if int8 else 2), np.float32 if is_norm else np.int8 if int8 else np.float16)
         _check(self._lib.sepal_b200_trunk_weight(self._h, layer, code, out.ctypes.data, needed.value, C.byref(needed)))

@@ -48,6 +48,16 @@ def oracle_forward(oracle, trunk, cfg, tokens):
             attended = ao.gated(ao.attend(f16(q.astype(np.float32)).astype(np.float64), f16(kk.astype(np.float32)).astype(np.float64), vv, 0), gate)
             a2 = f16(attended.reshape(len(tokens), heads * hd).astype(np.float32))
             x = oracle.add(x, oracle.gemm(a2, w_out))
+        elif not attention and cfg.dn_value_heads:
+            # the real DeltaNet core on the in-projection's [qkv; z; b; a] bands: one request from a zero state
+            from oracle import deltanet_oracle as do
+
+            kh, vh = cfg.dn_key_heads, cfg.dn_value_heads
+            cd, vd = 256 * kh + 128 * vh, 128 * vh
+            out, _, _ = do.core(p[:, :cd], p[:, cd:cd + vd], p[:, cd + vd:cd + vd + vh], p[:, cd + vd + vh:cd + vd + 2 * vh],
+                                trunk.weight("dn_conv", l).reshape(cd, cfg.dn_conv_kernel), trunk.weight("dn_a_log", l), trunk.weight("dn_dt_bias", l),
+                                trunk.weight("dn_norm", l), kh, vh, 128, cfg.eps)
+            x = oracle.add(x, oracle.gemm(f16(out.astype(np.float32)), w_out))
         else:
             x = oracle.add(x, oracle.gemm(np.ascontiguousarray(p[:, off:off + k_out]), w_out))
         a1 = f16(oracle.rmsnorm(x, trunk.weight("norm_post", l), cfg.eps))
@@ -344,5 +354,40 @@ def test_trunk_with_the_real_attention_core(oracle, tmp_path):
             again.close()
         with pytest.raises(sb.SepalB200Error, match="attn_q = 2 heads"):
             sb.Trunk(0, small_config(sb, attn_q=256, attn_kv=128, attn_o=256, attn_heads=2, attn_kv_heads=1, attn_head_dim=128))
+    finally:
+        trunk.close()
+
+
+def test_trunk_with_the_real_deltanet_core(oracle, tmp_path):
+    """dn_value_heads > 0: the DeltaNet layers run convolution, gated delta rule and gated norm between their projections; with attn_heads
+    as well, no layer is wired. One request in three calls (state and convolution tail carried) against the CPU composition; requests packed
+    into calls give what each gives alone; the core's weights travel through a saved file."""
+    import sepal_runner_b200 as sb
+
+    cfg = small_config(sb, attn_q=512, attn_kv=128, attn_o=256, attn_heads=2, attn_kv_heads=1, attn_head_dim=128, attn_rotary_dims=32, rope_theta=1.0e4,
+                       dn_key_heads=2, dn_value_heads=4, dn_in=1544, dn_v=512, dn_v_offset=0)
+    trunk = sb.Trunk(0, cfg)
+    try:
+        rng = np.random.default_rng(32)
+        tokens = rng.integers(0, cfg.vocab, 650).astype(np.uint32)
+        last, allh, _ = trunk.run(tokens, want_all=True)
+        assert np.isfinite(allh).all()
+        want = oracle_forward(oracle, trunk, cfg, tokens)
+        assert rel_fro(allh, want) < 3e-3
+        requests = [tokens[:40], tokens, tokens[7:8], tokens[:301]]
+        hidden, _ = trunk.score(requests)
+        for i, r in enumerate(requests):
+            assert rel_fro(hidden[i], trunk.run(r)[0]) < 1e-5, i
+        saved = str(tmp_path / "placed.safetensors")
+        trunk.save(saved)
+        again = sb.Trunk(0, cfg, sb.Checkpoint(saved))
+        try:
+            for which in ("dn_conv", "dn_a_log", "dn_dt_bias", "dn_norm"):
+                assert np.array_equal(again.weight(which, 0), trunk.weight(which, 0))
+            assert np.array_equal(again.run(tokens)[0], last)
+        finally:
+            again.close()
+        with pytest.raises(sb.SepalB200Error, match="dn_in = 256 key heads"):
+            sb.Trunk(0, small_config(sb, dn_key_heads=2, dn_value_heads=4, dn_in=1024, dn_v=512, dn_v_offset=0))
     finally:
         trunk.close()

@@ -344,7 +344,10 @@ def trunk_numbers(local, peak_tf):
     # "attention": the nine attention layers run the real core (16 query / 4 key-value heads of 256, q_proj carrying the output gate:
     # 8192 rows instead of 4096) instead of the fixed wiring; the DeltaNet layers stay wired.
     real = dict(attn_q=8192, attn_kv=1024, attn_o=4096, attn_heads=16, attn_kv_heads=4, attn_head_dim=256, attn_rotary_dims=64)
-    for name, int8, extra in (("f16", 0, {}), ("mlp_int8", 1, {}), ("f16_attention", 0, real)):
+    # "cores": as "attention", and the 27 DeltaNet layers run theirs too (16 key / 32 value heads of 128, convolution of 4 taps: an
+    # in-projection of 12,352 rows, an out-projection over 4096), the geometry of the 4b model's mixers.
+    cores = dict(real, dn_key_heads=16, dn_value_heads=32, dn_in=12352, dn_v=4096, dn_v_offset=0)
+    for name, int8, extra in (("f16", 0, {}), ("mlp_int8", 1, {}), ("f16_attention", 0, real), ("f16_cores", 0, cores)):
         trunk = sb.Trunk(local, sb.TrunkConfig(mlp_int8=int8, **extra))
         flops_tok = trunk.gemm_flops_per_token
         row = {"weight_gb": round(trunk.weight_bytes / 1e9, 2), "gemm_gflop_per_token": round(flops_tok / 1e9, 3)}

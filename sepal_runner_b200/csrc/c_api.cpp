@@ -325,9 +325,10 @@ int32_t sepal_b200_deltanet(sepal_b200_ctx* ctx, const sepal_b200_deltanet_shape
         sc.v = sc.k + tokens * s.key_dim();
         sc.decay = sc.v + tokens * s.value_dim();
         sc.beta = sc.decay + tokens * s.value_heads;
+        sc.reads = sc.beta + tokens * s.value_heads;
         const bool half = bands_half != 0;
         launch_deltanet(ctx->ctx, s, reinterpret_cast<const DeltaNetRow*>(rows), n_rows, Band{mixed, mixed_stride, half}, Band{z, z_stride, half},
-                        Band{b, b_stride, half}, Band{a, a_stride, half}, DeltaNetWeights{conv, a_log, dt_bias, norm}, sc, states, tails, nullptr, slots, out,
+                        Band{b, b_stride, half}, Band{a, a_stride, half}, DeltaNetWeights{conv, a_log, dt_bias, norm}, sc, states, tails, slots, out,
                         out_stride, static_cast<cudaStream_t>(stream));
     });
 }

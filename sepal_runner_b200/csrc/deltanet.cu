@@ -37,6 +37,7 @@ struct DeltaParams {
     float* v;
     float* decay;
     float* beta;
+    float* reads;  // [N, value_dim]: the scan's output before the gated norm
     float* states;
     float* tails;  // [slots, taps - 1, conv_dim]
     __half* out;
@@ -46,9 +47,11 @@ struct DeltaParams {
 __device__ __forceinline__ float value_of(const void* base, unsigned long long index, unsigned half) {
     return half != 0 ? __half2float(static_cast<const __half*>(base)[index]) : static_cast<const float*>(base)[index];
 }
-// softplus, sigmoid and silu in the reference's forms (runner/include/sepal/ref/primitives.hpp:25-40).
+// softplus in the reference's form (runner/include/sepal/ref/primitives.hpp:25-40); sigmoid as 1 / (1 + e^-x), which the reference
+// writes as exp(-softplus(-x)): the same function, an ulp or two apart in float32, and a third of the instructions (it runs once per
+// element of the convolution's output).
 __device__ __forceinline__ float softplus(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); }
-__device__ __forceinline__ float sigmoid(float x) { return expf(-softplus(-x)); }
+__device__ __forceinline__ float sigmoid(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
 __device__ __forceinline__ float silu(float x) { return __fmul_rn(x, sigmoid(x)); }
 
 __device__ __forceinline__ unsigned row_of(const DeltaNetRow* rows, unsigned n_rows, unsigned token) {
@@ -73,16 +76,35 @@ __global__ void __launch_bounds__(256) deltanet_prepare_kernel(const DeltaParams
     const unsigned t = token - row.q_begin;
     const unsigned history = p.taps - 1;
     const float* tail = p.tails + static_cast<size_t>(row.slot) * history * p.conv_dim;
-    for (unsigned c = threadIdx.x; c < p.conv_dim; c += blockDim.x) {
-        float acc = 0.0f;
-        for (unsigned j = 0; j < p.taps; ++j) {
-            // window index t + j over (tail, then the run's inputs): the input of token t + j - history, or tail row t + j
-            float x;
-            if (t + j >= history) x = value_of(p.mixed, (static_cast<size_t>(token) + j - history) * p.mixed_stride + c, p.mixed_half);
-            else x = row.fresh != 0 ? 0.0f : tail[static_cast<size_t>(t + j) * p.conv_dim + c];
-            acc = __fadd_rn(acc, __fmul_rn(p.conv[static_cast<size_t>(c) * p.taps + j], x));
+    if (p.mixed_half != 0 && p.taps == 4 && t >= history && p.mixed_stride % 2 == 0 && p.conv_dim % 2 == 0 &&
+        reinterpret_cast<unsigned long long>(p.mixed) % 4 == 0 && reinterpret_cast<unsigned long long>(p.conv) % 16 == 0) {
+        // the common case: every tap reads the call's own rows; two channels a thread (one 4-byte load a tap, the taps of a channel as
+        // one 16-byte load), the same sums in the same order as the general loop below
+        const __half2* in = reinterpret_cast<const __half2*>(static_cast<const __half*>(p.mixed) + (static_cast<size_t>(token) - history) * p.mixed_stride);
+        const unsigned pitch = static_cast<unsigned>(p.mixed_stride / 2);
+        const float4* taps = reinterpret_cast<const float4*>(p.conv);
+        for (unsigned c2 = threadIdx.x; c2 < p.conv_dim / 2; c2 += blockDim.x) {
+            const float2 x0 = __half22float2(in[c2]), x1 = __half22float2(in[c2 + pitch]), x2 = __half22float2(in[c2 + 2 * pitch]),
+                         x3 = __half22float2(in[c2 + 3 * pitch]);
+            const float4 w0 = taps[2 * c2], w1 = taps[2 * c2 + 1];
+            float lo = __fadd_rn(0.0f, __fmul_rn(w0.x, x0.x)), hi = __fadd_rn(0.0f, __fmul_rn(w1.x, x0.y));
+            lo = __fadd_rn(lo, __fmul_rn(w0.y, x1.x)), hi = __fadd_rn(hi, __fmul_rn(w1.y, x1.y));
+            lo = __fadd_rn(lo, __fmul_rn(w0.z, x2.x)), hi = __fadd_rn(hi, __fmul_rn(w1.z, x2.y));
+            lo = __fadd_rn(lo, __fmul_rn(w0.w, x3.x)), hi = __fadd_rn(hi, __fmul_rn(w1.w, x3.y));
+            *reinterpret_cast<float2*>(&activated[2 * c2]) = make_float2(silu(lo), silu(hi));
         }
-        activated[c] = silu(acc);
+    } else {
+        for (unsigned c = threadIdx.x; c < p.conv_dim; c += blockDim.x) {
+            float acc = 0.0f;
+            for (unsigned j = 0; j < p.taps; ++j) {
+                // window index t + j over (tail, then the run's inputs): the input of token t + j - history, or tail row t + j
+                float x;
+                if (t + j >= history) x = value_of(p.mixed, (static_cast<size_t>(token) + j - history) * p.mixed_stride + c, p.mixed_half);
+                else x = row.fresh != 0 ? 0.0f : tail[static_cast<size_t>(t + j) * p.conv_dim + c];
+                acc = __fadd_rn(acc, __fmul_rn(p.conv[static_cast<size_t>(c) * p.taps + j], x));
+            }
+            activated[c] = silu(acc);
+        }
     }
     __syncthreads();
     // q and k heads: 2 * key_heads vectors of 128; one warp per head in turn
@@ -112,12 +134,14 @@ __global__ void __launch_bounds__(256) deltanet_prepare_kernel(const DeltaParams
     }
 }
 
-// After the prepare launch: the slot's tail becomes the last K - 1 rows of (old tail, then the run's inputs). One block per run.
+// After the prepare launch: the slot's tail becomes the last K - 1 rows of (old tail, then the run's inputs). One thread per run and
+// channel.
 __global__ void deltanet_tail_kernel(const DeltaParams p) {
     const DeltaNetRow row = p.rows[blockIdx.x];
     const unsigned history = p.taps - 1;
     float* tail = p.tails + static_cast<size_t>(row.slot) * history * p.conv_dim;
-    for (unsigned c = threadIdx.x; c < p.conv_dim; c += blockDim.x) {
+    const unsigned c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c < p.conv_dim) {
         for (unsigned i = 0; i < history; ++i) {  // ascending: row length + i of the window is read before row i is written (length >= 1)
             const unsigned w = row.length + i;
             float x;
@@ -128,121 +152,152 @@ __global__ void deltanet_tail_kernel(const DeltaParams p) {
     }
 }
 
-// One CTA per run and value head, 256 threads: thread (half, j) holds rows 64 half .. 64 half + 63 of column j of the state S [dk, dv].
-// Tokens are taken sixteen at a time: their k and q (and the products q . k) go to shared memory, their v, z, decay and beta to
-// registers / shared memory, with one barrier for the sixteen. Per token, ONE pass over the column decays it and forms both k . S'[:, j]
-// and q . S'[:, j] (two halves, summed first half then second through shared memory: one barrier); the correction beta (v - k . S') then
-// updates the column in a second pass, and the read of the updated state is q . S'[:, j] + (q . k) correction, which needs no third
-// pass. The sixteen tokens' reads wait in shared memory; after the sixteenth, each warp norms two tokens (RMS over the 128 reads, a
-// butterfly), applies the norm weight and the silu(z) gate and stores binary16.
+// The columns of a head's state S [dk, dv] evolve independently of one another (recall, correction and read of column j involve
+// column j alone), so a head is spread over eight CTAs of 16 columns: 128 threads, each holding 16 rows (one of eight row groups) of
+// one column in registers. Tokens are taken sixteen at a time: their k, q, v, decay and beta arrive in shared memory by asynchronous
+// copies issued while the sixteen before them are worked on (two buffers), and the products q . k are formed once they are in. Per token, ONE pass over the rows decays them and forms both k . S'[:, j] and
+// q . S'[:, j] (eight partial sums each, held by lanes of one warp and added by shuffles: no barrier); the correction beta (v - k . S') then
+// updates the rows in a second pass, and the read of the updated state is q . S'[:, j] + (q . k) correction, which needs no third
+// pass. The reads go to global memory in float32; the gated norm over a head's 128 reads is the next launch.
 constexpr int kChunk = 16;
+constexpr int kCols = 16;    // columns of the state per CTA: four warps of four columns
+constexpr int kScanThreads = 8 * kCols;  // eight row groups of 16 rows a column
 
-__global__ void __launch_bounds__(256) deltanet_scan_kernel(const DeltaParams p) {
-    __shared__ __align__(16) float k_sh[kChunk][kDim], q_sh[kChunk][kDim];
-    __shared__ float reads[kChunk][kDim], gates[kChunk][kDim];
-    __shared__ float part[2][2][2][kDim];  // [token parity][recall, read][half][column]
-    __shared__ float qk_sh[kChunk], decay_sh[kChunk], beta_sh[kChunk];
+// What the tokens t0 .. t0 + kChunk - 1 of a run need from global memory, fetched by asynchronous copies into one of two buffers while
+// the chunk before it is being worked on.
+struct ScanStage {
+    float k[kChunk][kDim], q[kChunk][kDim];
+    float v[kChunk][kCols];
+    float decay[kChunk], beta[kChunk];
+};
+
+__device__ __forceinline__ void scan_prefetch(const DeltaParams& p, ScanStage& st, const DeltaNetRow& row, unsigned t0, unsigned head,
+                                              unsigned key_head, unsigned first_col) {
+    if (t0 >= row.length) return;
+    const unsigned count = min(static_cast<unsigned>(kChunk), row.length - t0);
+    const size_t token0 = static_cast<size_t>(row.q_begin) + t0;
+    for (unsigned e = threadIdx.x; e < 2 * kChunk * kDim / 4; e += kScanThreads) {  // 16 bytes a copy
+        const unsigned which = e / (kChunk * kDim / 4), tt = (e / (kDim / 4)) % kChunk, d = 4 * (e % (kDim / 4));
+        if (tt < count)
+            ptx::cp_async_16(which == 0 ? &st.k[tt][d] : &st.q[tt][d],
+                             (which == 0 ? p.k : p.q) + (token0 + tt) * p.key_dim + key_head * kDim + d);
+    }
+    for (unsigned e = threadIdx.x; e < kChunk * kCols; e += kScanThreads) {
+        const unsigned tt = e / kCols, c = e % kCols;
+        if (tt < count) ptx::cp_async_4(&st.v[tt][c], p.v + (token0 + tt) * p.value_dim + head * kDim + first_col + c);
+    }
+    if (threadIdx.x < 2 * kChunk) {
+        const unsigned tt = threadIdx.x % kChunk;
+        if (tt < count)
+            ptx::cp_async_4(threadIdx.x < kChunk ? &st.decay[tt] : &st.beta[tt],
+                            (threadIdx.x < kChunk ? p.decay : p.beta) + (token0 + tt) * p.value_heads + head);
+    }
+}
+
+__global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const DeltaParams p) {
+    extern __shared__ __align__(16) unsigned char scan_smem[];
+    ScanStage* stages = reinterpret_cast<ScanStage*>(scan_smem);
+    __shared__ float qk_sh[kChunk];
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
     const DeltaNetRow row = p.rows[blockIdx.x];
     const unsigned head = blockIdx.y, key_head = head / (p.value_heads / p.key_heads);
-    const unsigned j = threadIdx.x % kDim, half = threadIdx.x / kDim;
     const unsigned warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    float s[64];
+    // A warp owns four columns; lane = 4 g + c holds rows 16 g .. 16 g + 15 of column c of them, so the eight row groups of a column
+    // sit in one warp (their partial sums meet by three shuffles, no barrier between tokens), and the eight lanes of a quarter warp
+    // read two 16-byte pieces of k or q (no bank conflict).
+    const unsigned g = lane / 4, jl = 4 * warp + lane % 4;
+    const unsigned j = blockIdx.z * kCols + jl;  // this thread's column of the head
+    scan_prefetch(p, stages[0], row, 0, head, key_head, blockIdx.z * kCols);
+    float s[16];
     float* state = p.states + (static_cast<size_t>(row.slot) * p.value_heads + head) * kDim * kDim;
 #pragma unroll
-    for (int i = 0; i < 64; ++i) s[i] = row.fresh != 0 ? 0.0f : state[static_cast<size_t>(64 * half + i) * kDim + j];
+    for (int i = 0; i < 16; ++i) s[i] = row.fresh != 0 ? 0.0f : state[static_cast<size_t>(16 * g + i) * kDim + j];
     const float scale = rsqrtf(static_cast<float>(kDim));
-    const float w_norm = p.norm[j];
-    for (unsigned t0 = 0; t0 < row.length; t0 += kChunk) {
+    for (unsigned t0 = 0, turn = 0; t0 < row.length; t0 += kChunk, turn ^= 1u) {
         const unsigned count = min(static_cast<unsigned>(kChunk), row.length - t0);
         const size_t token0 = static_cast<size_t>(row.q_begin) + t0;
-        __syncthreads();  // the chunk before this one has been normed and stored: its buffers may be overwritten
-        // k, q of the chunk: 2 x 16 x 128 values over 256 threads; v of this thread's column (needed by both halves) into registers
-        for (unsigned e = threadIdx.x; e < 2 * kChunk * kDim; e += 256) {
-            const unsigned which = e / (kChunk * kDim), tt = (e / kDim) % kChunk, d = e % kDim;
-            if (tt < count) {
-                const float value = (which == 0 ? p.k : p.q)[(token0 + tt) * p.key_dim + key_head * kDim + d];
-                (which == 0 ? k_sh : q_sh)[tt][d] = value;
-            }
-        }
-        float v[kChunk];
-#pragma unroll
-        for (int tt = 0; tt < kChunk; ++tt) v[tt] = tt < static_cast<int>(count) ? p.v[(token0 + tt) * p.value_dim + head * kDim + j] : 0.0f;
-        if (half == 1) {
-#pragma unroll
-            for (int tt = 0; tt < kChunk; ++tt)
-                if (tt < static_cast<int>(count)) gates[tt][j] = silu(value_of(p.z, (token0 + tt) * p.z_stride + head * kDim + j, p.z_half));
-        }
-        if (threadIdx.x < kChunk && threadIdx.x < count) {
-            decay_sh[threadIdx.x] = p.decay[(token0 + threadIdx.x) * p.value_heads + head];
-            beta_sh[threadIdx.x] = p.beta[(token0 + threadIdx.x) * p.value_heads + head];
-        }
-        __syncthreads();
-        for (unsigned tt = warp; tt < count; tt += 8) {  // q . k of each token: four values a lane, a butterfly
+        const ScanStage& st = stages[turn];
+        ptx::cp_async_wait_all();
+        __syncthreads();  // this chunk's values are in place; the chunk before it is done with the other buffer
+        scan_prefetch(p, stages[turn ^ 1u], row, t0 + kChunk, head, key_head, blockIdx.z * kCols);
+        for (unsigned tt = warp; tt < count; tt += kScanThreads / 32) {  // q . k of each token: four values a lane, a butterfly
             float dot = 0.0f;
-            for (int e = 0; e < 4; ++e) dot = __fmaf_rn(q_sh[tt][lane + 32 * e], k_sh[tt][lane + 32 * e], dot);
+            for (int e = 0; e < 4; ++e) dot = __fmaf_rn(st.q[tt][lane + 32 * e], st.k[tt][lane + 32 * e], dot);
             for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, o);
             if (lane == 0) qk_sh[tt] = dot;
         }
         __syncthreads();
+#pragma unroll 4
         for (unsigned tt = 0; tt < count; ++tt) {
-            const unsigned parity = tt & 1u;
-            const float decay = decay_sh[tt];
-            // k and q come from shared memory four at a time (every lane reads the same 16 bytes: one broadcast): a scalar load for each
-            // of the 3 x 64 products would make the load unit, not the arithmetic, the limit
-            const float4* k4 = reinterpret_cast<const float4*>(&k_sh[tt][64 * half]);
-            const float4* q4 = reinterpret_cast<const float4*>(&q_sh[tt][64 * half]);
-            float rec[2] = {0.0f, 0.0f}, rd[2] = {0.0f, 0.0f};
+            const float decay = st.decay[tt];
+            const float4* k4 = reinterpret_cast<const float4*>(&st.k[tt][16 * g]);
+            const float4* q4 = reinterpret_cast<const float4*>(&st.q[tt][16 * g]);
+            float4 kk[4];
+            float rec[4] = {0.0f, 0.0f, 0.0f, 0.0f}, rd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int g = 0; g < 16; ++g) {
-                const float4 kk = k4[g], qq = q4[g];
-                s[4 * g] = __fmul_rn(s[4 * g], decay);
-                s[4 * g + 1] = __fmul_rn(s[4 * g + 1], decay);
-                s[4 * g + 2] = __fmul_rn(s[4 * g + 2], decay);
-                s[4 * g + 3] = __fmul_rn(s[4 * g + 3], decay);
-                rec[0] = __fmaf_rn(kk.x, s[4 * g], rec[0]);
-                rec[1] = __fmaf_rn(kk.y, s[4 * g + 1], rec[1]);
-                rec[0] = __fmaf_rn(kk.z, s[4 * g + 2], rec[0]);
-                rec[1] = __fmaf_rn(kk.w, s[4 * g + 3], rec[1]);
-                rd[0] = __fmaf_rn(qq.x, s[4 * g], rd[0]);
-                rd[1] = __fmaf_rn(qq.y, s[4 * g + 1], rd[1]);
-                rd[0] = __fmaf_rn(qq.z, s[4 * g + 2], rd[0]);
-                rd[1] = __fmaf_rn(qq.w, s[4 * g + 3], rd[1]);
+            for (int c = 0; c < 4; ++c) {
+                kk[c] = k4[c];
+                const float4 qq = q4[c];
+                s[4 * c] = __fmul_rn(s[4 * c], decay);
+                s[4 * c + 1] = __fmul_rn(s[4 * c + 1], decay);
+                s[4 * c + 2] = __fmul_rn(s[4 * c + 2], decay);
+                s[4 * c + 3] = __fmul_rn(s[4 * c + 3], decay);
+                rec[0] = __fmaf_rn(kk[c].x, s[4 * c], rec[0]);
+                rec[1] = __fmaf_rn(kk[c].y, s[4 * c + 1], rec[1]);
+                rec[2] = __fmaf_rn(kk[c].z, s[4 * c + 2], rec[2]);
+                rec[3] = __fmaf_rn(kk[c].w, s[4 * c + 3], rec[3]);
+                rd[0] = __fmaf_rn(qq.x, s[4 * c], rd[0]);
+                rd[1] = __fmaf_rn(qq.y, s[4 * c + 1], rd[1]);
+                rd[2] = __fmaf_rn(qq.z, s[4 * c + 2], rd[2]);
+                rd[3] = __fmaf_rn(qq.w, s[4 * c + 3], rd[3]);
             }
-            part[parity][0][half][j] = rec[0] + rec[1];
-            part[parity][1][half][j] = rd[0] + rd[1];
-            __syncthreads();  // the slots of this parity are next written two tokens on, after the barrier of the token in between
-            const float correction = __fmul_rn(beta_sh[tt], __fsub_rn(v[tt], part[parity][0][0][j] + part[parity][0][1][j]));
+            float recall = (rec[0] + rec[1]) + (rec[2] + rec[3]), read = (rd[0] + rd[1]) + (rd[2] + rd[3]);
 #pragma unroll
-            for (int g = 0; g < 16; ++g) {
-                const float4 kk = k4[g];
-                s[4 * g] = __fmaf_rn(kk.x, correction, s[4 * g]);
-                s[4 * g + 1] = __fmaf_rn(kk.y, correction, s[4 * g + 1]);
-                s[4 * g + 2] = __fmaf_rn(kk.z, correction, s[4 * g + 2]);
-                s[4 * g + 3] = __fmaf_rn(kk.w, correction, s[4 * g + 3]);
+            for (int o = 4; o < 32; o <<= 1) {  // over the eight row groups of the column: every lane ends with the same sums
+                recall += __shfl_xor_sync(0xFFFFFFFFu, recall, o);
+                read += __shfl_xor_sync(0xFFFFFFFFu, read, o);
             }
-            if (half == 0) reads[tt][j] = __fmul_rn(__fmaf_rn(qk_sh[tt], correction, part[parity][1][0][j] + part[parity][1][1][j]), scale);
-        }
-        __syncthreads();
-        for (unsigned tt = warp; tt < count; tt += 8) {  // the gated norm of a token's 128 reads: lane l holds reads l, l + 32, ...
-            float x[4], ss = 0.0f;
-            for (int e = 0; e < 4; ++e) {
-                x[e] = reads[tt][lane + 32 * e];
-                ss = __fmaf_rn(x[e], x[e], ss);
+            const float correction = __fmul_rn(st.beta[tt], __fsub_rn(st.v[tt][jl], recall));
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                s[4 * c] = __fmaf_rn(kk[c].x, correction, s[4 * c]);
+                s[4 * c + 1] = __fmaf_rn(kk[c].y, correction, s[4 * c + 1]);
+                s[4 * c + 2] = __fmaf_rn(kk[c].z, correction, s[4 * c + 2]);
+                s[4 * c + 3] = __fmaf_rn(kk[c].w, correction, s[4 * c + 3]);
             }
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-            const float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(kDim)), p.eps));
-            __half* dst = p.out + (token0 + tt) * p.out_stride + head * kDim;
-            for (int e = 0; e < 4; ++e) {
-                const unsigned d = lane + 32 * e;
-                dst[d] = __float2half_rn(__fmul_rn(__fmul_rn(__fdiv_rn(x[e], rms), p.norm[d]), gates[tt][d]));
-            }
+            if (g == 0) p.reads[(token0 + tt) * p.value_dim + head * kDim + j] = __fmul_rn(__fmaf_rn(qk_sh[tt], correction, read), scale);
         }
     }
-    (void)w_norm;
 #pragma unroll
-    for (int i = 0; i < 64; ++i) state[static_cast<size_t>(64 * half + i) * kDim + j] = s[i];
+    for (int i = 0; i < 16; ++i) state[static_cast<size_t>(16 * g + i) * kDim + j] = s[i];
+}
+
+// The gated norm of every token's and value head's 128 reads: x / sqrt(mean(x^2) + eps) * weight * silu(z) (the weight itself, not
+// 1 + weight). One warp per (token, head): lane l holds reads l, l + 32, ...; squares by fused multiply-add in that order, a butterfly.
+__global__ void __launch_bounds__(256) deltanet_norm_kernel(const DeltaParams p, unsigned tokens) {
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+    const size_t unit = static_cast<size_t>(blockIdx.x) * 8 + threadIdx.x / 32;  // (token, head)
+    if (unit >= static_cast<size_t>(tokens) * p.value_heads) return;
+    const size_t token = unit / p.value_heads;
+    const unsigned head = static_cast<unsigned>(unit % p.value_heads), lane = threadIdx.x % 32;
+    const DeltaNetRow row = p.rows[row_of(p.rows, p.n_rows, static_cast<unsigned>(token))];
+    if (token < row.q_begin || token >= static_cast<size_t>(row.q_begin) + row.length) return;
+    const float* x = p.reads + token * p.value_dim + head * kDim;
+    float v[4], ss = 0.0f;
+    for (int e = 0; e < 4; ++e) {
+        v[e] = x[lane + 32 * e];
+        ss = __fmaf_rn(v[e], v[e], ss);
+    }
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+    const float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(kDim)), p.eps));
+    __half* dst = p.out + token * p.out_stride + head * kDim;
+    for (int e = 0; e < 4; ++e) {
+        const unsigned d = lane + 32 * e;
+        const float z = value_of(p.z, token * p.z_stride + head * kDim + d, p.z_half);
+        dst[d] = __float2half_rn(__fmul_rn(__fmul_rn(__fdiv_rn(v[e], rms), p.norm[d]), silu(z)));
+    }
 }
 
 }  // namespace
@@ -253,14 +308,14 @@ bool deltanet_supports(const DeltaNetShape& s) {
 }
 
 void launch_deltanet(Context& ctx, const DeltaNetShape& shape, const DeltaNetRow* rows, std::size_t n_rows, Band mixed, Band z, Band b, Band a,
-                     const DeltaNetWeights& weights, const DeltaNetScratch& scratch, float* states, float* tails, float* /*unused*/, std::size_t slots,
+                     const DeltaNetWeights& weights, const DeltaNetScratch& scratch, float* states, float* tails, std::size_t slots,
                      void* out, std::size_t out_stride, cudaStream_t stream) {
     if (!deltanet_supports(shape))
         throw std::invalid_argument("sepal_b200 deltanet: head_dim must be 128, value_heads a multiple of key_heads (at most 32 key heads), 1 to 8 conv taps");
     if (n_rows == 0) return;
     if (rows == nullptr || mixed.data == nullptr || z.data == nullptr || b.data == nullptr || a.data == nullptr || weights.conv == nullptr ||
         weights.a_log == nullptr || weights.dt_bias == nullptr || weights.norm == nullptr || scratch.q == nullptr || scratch.k == nullptr ||
-        scratch.v == nullptr || scratch.decay == nullptr || scratch.beta == nullptr || states == nullptr || tails == nullptr || out == nullptr)
+        scratch.v == nullptr || scratch.decay == nullptr || scratch.beta == nullptr || scratch.reads == nullptr || states == nullptr || tails == nullptr || out == nullptr)
         throw std::invalid_argument("sepal_b200 deltanet: null pointer");
     for (std::size_t i = 0; i < n_rows; ++i) {
         if (rows[i].length == 0) throw std::invalid_argument("sepal_b200 deltanet: row " + std::to_string(i) + " is empty");
@@ -304,6 +359,7 @@ void launch_deltanet(Context& ctx, const DeltaNetShape& shape, const DeltaNetRow
     p.v = scratch.v;
     p.decay = scratch.decay;
     p.beta = scratch.beta;
+    p.reads = scratch.reads;
     p.states = states;
     p.tails = tails;
     p.out = static_cast<__half*>(out);
@@ -319,11 +375,14 @@ void launch_deltanet(Context& ctx, const DeltaNetShape& shape, const DeltaNetRow
     launch_kernel(deltanet_prepare_kernel, dim3(last), dim3(256), prepare_smem, stream, "deltanet_prepare_kernel launch", p);
     count_launch();
     if (shape.conv_kernel > 1) {
-        deltanet_tail_kernel<<<static_cast<unsigned>(n_rows), 256, 0, stream>>>(p);
+        deltanet_tail_kernel<<<dim3(static_cast<unsigned>(n_rows), (p.conv_dim + 255) / 256), 256, 0, stream>>>(p);
         check(cudaGetLastError(), "deltanet_tail_kernel launch");
         count_launch();
     }
-    launch_kernel(deltanet_scan_kernel, dim3(static_cast<unsigned>(n_rows), shape.value_heads), dim3(256), 0, stream, "deltanet_scan_kernel launch", p);
+    launch_kernel(deltanet_scan_kernel, dim3(static_cast<unsigned>(n_rows), shape.value_heads, kDim / kCols), dim3(kScanThreads), 2 * sizeof(ScanStage), stream, "deltanet_scan_kernel launch", p);
+    count_launch();
+    const std::size_t units = static_cast<std::size_t>(last) * shape.value_heads;
+    launch_kernel(deltanet_norm_kernel, dim3(static_cast<unsigned>((units + 7) / 8)), dim3(256), 0, stream, "deltanet_norm_kernel launch", p, last);
     count_launch();
 }
 

@@ -52,6 +52,18 @@ __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddep
 // Orders this thread's ordinary accesses (any state space) with accesses made through the async proxy (bulk copies).
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
+// Per-thread asynchronous copies global -> shared (16 or 4 bytes, both addresses aligned to the size); a thread's copies complete, for
+// that thread, at cp_async_wait_all (other threads see them after a barrier that follows it).
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_addr(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
 // ---- TMA ---------------------------------------------------------------------------------------------------------------
 
 // One tile of a 2-D tensor into shared memory; completion is counted in bytes on `bar`. c0 is the innermost (contiguous)

@@ -319,13 +319,7 @@ int32_t sepal_b200_deltanet(sepal_b200_ctx* ctx, const sepal_b200_deltanet_shape
         }
         std::size_t tokens = 0;
         if (n_rows != 0) tokens = static_cast<std::size_t>(rows[n_rows - 1].q_begin) + rows[n_rows - 1].length;
-        DeltaNetScratch sc;  // q, k, v, decay, beta one after the other
-        sc.q = scratch;
-        sc.k = sc.q + tokens * s.key_dim();
-        sc.v = sc.k + tokens * s.key_dim();
-        sc.decay = sc.v + tokens * s.value_dim();
-        sc.beta = sc.decay + tokens * s.value_heads;
-        sc.reads = sc.beta + tokens * s.value_heads;
+        const DeltaNetScratch sc = deltanet_scratch(scratch, s, tokens);
         const bool half = bands_half != 0;
         launch_deltanet(ctx->ctx, s, reinterpret_cast<const DeltaNetRow*>(rows), n_rows, Band{mixed, mixed_stride, half}, Band{z, z_stride, half},
                         Band{b, b_stride, half}, Band{a, a_stride, half}, DeltaNetWeights{conv, a_log, dt_bias, norm}, sc, states, tails, slots, out,

@@ -9,8 +9,9 @@
 //
 // State. A request owns a slot: its recurrent state [value heads, dk, dv] float32 and the last K - 1 rows of `mixed`. A call holds runs
 // of consecutive tokens of different requests; a run continues its slot's state and leaves it updated, so a request cut into several
-// calls gives what it gives in one. The scan walks a run token by token (eight CTAs per run and value head, each with 16 columns of the
-// state in registers): the chunked form on the tensor cores is the next step for this row of the scope table.
+// calls gives what it gives in one. The scan takes a run in chunks of sixteen tokens (eight CTAs per run and value head, each with 16
+// columns of the state in registers, on the ordinary cores): larger chunks on the tensor cores are the next step for this row of the
+// scope table.
 #pragma once
 
 #include <cstddef>
@@ -48,17 +49,35 @@ struct DeltaNetWeights {
     const float* norm = nullptr;
 };
 
-/// Scratch of one call (device, float32), sized for the call's tokens N: q, k [N, key_dim]; v, reads [N, value_dim]; decay, beta [N, value_heads].
+/// Scratch of one call (device, float32, 16-byte aligned), sized for the call's tokens N: q, k [N, key_dim]; v, reads [N, value_dim];
+/// coef [N, value_heads, 36] (the chunk coefficients); decay, beta [N, value_heads].
 struct DeltaNetScratch {
     float* q = nullptr;
     float* k = nullptr;
     float* v = nullptr;
+    float* reads = nullptr;
+    float* coef = nullptr;
     float* decay = nullptr;
     float* beta = nullptr;
-    float* reads = nullptr;
 };
 
-/// The launches of a layer (prepare, tail, scan, gated norm). mixed [N, conv_dim], z [N, value_dim], b and a [N, value_heads] are bands of the in-projection's output;
+/// Floats of scratch a call of `tokens` tokens needs, and the scratch carved out of one such allocation.
+inline std::size_t deltanet_scratch_floats(const DeltaNetShape& s, std::size_t tokens) {
+    return tokens * (2 * static_cast<std::size_t>(s.key_dim()) + 2 * s.value_dim() + 38 * static_cast<std::size_t>(s.value_heads));
+}
+inline DeltaNetScratch deltanet_scratch(float* base, const DeltaNetShape& s, std::size_t tokens) {
+    DeltaNetScratch sc;
+    sc.q = base;
+    sc.k = sc.q + tokens * s.key_dim();
+    sc.v = sc.k + tokens * s.key_dim();
+    sc.reads = sc.v + tokens * s.value_dim();
+    sc.coef = sc.reads + tokens * s.value_dim();
+    sc.decay = sc.coef + tokens * s.value_heads * 36;
+    sc.beta = sc.decay + tokens * s.value_heads;
+    return sc;
+}
+
+/// The launches of a layer (prepare, tail, chunk coefficients, scan, gated norm). mixed [N, conv_dim], z [N, value_dim], b and a [N, value_heads] are bands of the in-projection's output;
 /// states float32 [slots, value_heads, head_dim, head_dim] and tails float32 [slots, K - 1, conv_dim], both updated in place; out
 /// binary16 [N, value_dim] with row stride out_stride.
 /// `rows` is a HOST array sorted by q_begin.

@@ -248,7 +248,7 @@ Trunk::Trunk(int device, const TrunkConfig& config, const Checkpoint* checkpoint
     }
     if (real_deltanet()) {
         const DeltaNetShape d = deltanet_shape();
-        dn_scratch_ = static_cast<float*>(alloc(T * (2 * static_cast<std::size_t>(d.key_dim()) + 2 * d.value_dim() + 2 * d.value_heads) * 4));
+        dn_scratch_ = static_cast<float*>(alloc(deltanet_scratch_floats(d, T) * 4));
     }
     tokens_dev_ = static_cast<std::uint32_t*>(alloc(2 * T * 4));
     check(cudaMallocHost(reinterpret_cast<void**>(&tokens_pinned_), 2 * T * 4), "cudaMallocHost");
@@ -363,13 +363,7 @@ void Trunk::forward_call(const std::uint32_t* tokens_dev, std::size_t rows, cons
             const __half* pm = static_cast<const __half*>(p_);
             const Band mixed{pm, p_width_, true}, z{pm + d.conv_dim(), p_width_, true}, b{pm + d.conv_dim() + d.value_dim(), p_width_, true},
                 a{pm + d.conv_dim() + d.value_dim() + d.value_heads, p_width_, true};
-            DeltaNetScratch sc;
-            sc.q = dn_scratch_;
-            sc.k = sc.q + rows * d.key_dim();
-            sc.v = sc.k + rows * d.key_dim();
-            sc.decay = sc.v + rows * d.value_dim();
-            sc.beta = sc.decay + rows * d.value_heads;
-            sc.reads = sc.beta + rows * d.value_heads;
+            const DeltaNetScratch sc = deltanet_scratch(dn_scratch_, d, rows);
             launch_deltanet(ctx_, d, dn_runs.data(), dn_runs.size(), mixed, z, b, a, DeltaNetWeights{L.dn_conv, L.dn_a_log, L.dn_dt_bias, L.dn_norm}, sc, L.dn_states,
                             L.dn_tails, state_slots_, a2_, c.dn_v, stream_);
             launch_gemm_f16(ctx_, a2_, c.dn_v, L.mix_out, L.mix_out_k, x_, H, false, rows, H, L.mix_out_k, Epilogue::Add, -1, stream_);

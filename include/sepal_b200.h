@@ -244,10 +244,11 @@ SEPAL_B200_API int32_t sepal_b200_attention(sepal_b200_ctx* ctx, const sepal_b20
  * (S <- decay S; S <- S + k (x) beta (v - k . S); read = S^T q / sqrt(dk); decay = exp(-exp(A_log) softplus(a + dt_bias)), beta =
  * sigmoid(b)), the head-wise RMSNorm of the read with the norm weight itself and the silu(z) gate, binary16 out for out_proj.
  * mixed [N, 2 key_dim + value_dim], z [N, value_dim], b and a [N, value_heads] are bands of the in-projection (all binary16 or all
- * float32); conv float32 [conv_dim, K], a_log and dt_bias [value_heads], norm [head_dim]; scratch: N * (2 key_dim + 2 value_dim + 38
+ * float32); conv float32 [conv_dim, K], a_log and dt_bias [value_heads], norm [head_dim]; scratch: N * (264 key_heads + 2 value_dim + 58
  * value_heads) floats, 16-byte aligned; states float32 [slots, value_heads, 128, 128] and tails float32 [slots, K - 1, conv_dim] persist between calls
  * (a row with fresh = 1 starts from zero whatever its slot holds); a row is {first token, length, slot, fresh}; rows: host array sorted
- * by first token, one row per slot in a call. head_dim 128. The scan takes a row in chunks of sixteen tokens (eight CTAs per row and value head). */
+ * by first token, one row per slot in a call. head_dim 128. The scan takes a row in chunks of sixteen tokens (eight warps per row and value head; float32 state, TF32 operands in the
+ * chunk's matrix products). */
 typedef struct sepal_b200_deltanet_shape {
     uint32_t key_heads, value_heads, head_dim, conv_kernel;
     float eps;

@@ -17,6 +17,7 @@ void count_launch();
 namespace {
 
 constexpr int kDim = 128;  // dk = dv
+constexpr int kPair = 2 * kDim + 8;  // floats of a token's (k, q) row: the pitch that keeps the scan's fragment loads free of bank conflicts
 
 // Sixteen (at the end of a run: fewer) consecutive tokens of a run, counted from the run's first token.
 struct DeltaChunk {
@@ -39,13 +40,14 @@ struct DeltaParams {
     const float* a_log;
     const float* dt_bias;
     const float* norm;
-    float* q;
-    float* k;
+    float* kq;  // [key_heads, N, 264]: per token the head's k (128), q (128) and 8 floats of padding
     float* v;
     float* decay;
     float* beta;
     float* reads;  // [N, value_dim]: the scan's output before the gated norm
-    float* coef;   // [N, value_heads, 36]: the chunk coefficients of every token
+    float* coef;   // [value_heads, N, 56]: the chunk coefficients of every token
+    unsigned n_tokens;
+    int* status;
     const DeltaChunk* chunks;
     float* states;
     float* tails;  // [slots, taps - 1, conv_dim]
@@ -62,6 +64,13 @@ __device__ __forceinline__ float value_of(const void* base, unsigned long long i
 __device__ __forceinline__ float softplus(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); }
 __device__ __forceinline__ float sigmoid(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
 __device__ __forceinline__ float silu(float x) { return __fmul_rn(x, sigmoid(x)); }
+
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float round_tf32(float x) { return __uint_as_float(to_tf32(x)); }
 
 __device__ __forceinline__ unsigned row_of(const DeltaNetRow* rows, unsigned n_rows, unsigned token) {
     unsigned lo = 0, hi = n_rows;
@@ -129,8 +138,8 @@ __global__ void __launch_bounds__(256) deltanet_prepare_kernel(const DeltaParams
     for (unsigned c = threadIdx.x; c < p.conv_dim; c += blockDim.x) {
         if (c < 2 * p.key_dim) {
             const float value = __fdiv_rn(activated[c], __fsqrt_rn(__fadd_rn(head_sums[c / kDim], 1.0e-6f)));
-            if (c < p.key_dim) p.q[static_cast<size_t>(token) * p.key_dim + c] = value;
-            else p.k[static_cast<size_t>(token) * p.key_dim + (c - p.key_dim)] = value;
+            const unsigned which = c < p.key_dim ? 1u : 0u, inner = c < p.key_dim ? c : c - p.key_dim;  // q comes first in the convolution's channels
+            p.kq[(static_cast<size_t>(inner / kDim) * p.n_tokens + token) * kPair + which * kDim + inner % kDim] = value;
         } else {
             p.v[static_cast<size_t>(token) * p.value_dim + (c - 2 * p.key_dim)] = activated[c];
         }
@@ -163,24 +172,39 @@ __global__ void deltanet_tail_kernel(const DeltaParams p) {
 
 // The delta rule in chunks of sixteen tokens. With d_t the decay of token t, c_t its correction beta_t (v_t - k_t . d_t S_{t-1}) and
 // S_t = d_t S_{t-1} + k_t (x) c_t, unrolling from the state S_0 before the chunk gives, with P(s, t) = d_{s+1} ... d_t and
-// gamma_t = d_0 ... d_t (tokens numbered from 0 inside the chunk):
-//     c_t    = beta_t (v_t - gamma_t k_t . S_0 - sum_{s<t} P(s, t) (k_t . k_s) c_s)
-//     read_t = (gamma_t q_t . S_0 + sum_{s<=t} P(s, t) (q_t . k_s) c_s) / sqrt(dk)
-//     S_end  = gamma_last S_0 + sum_s P(s, last) k_s (x) c_s
-// so the products with S_0 of all sixteen tokens are independent (their cross-lane sums go out together: one shuffle latency a chunk
-// instead of one a token), and what is left of the chain is a few multiply-adds per token on coefficients that do not involve the
-// state. Those coefficients, per token s and value head, are formed by deltanet_gram_kernel: col_a[t] = P(s, t) (k_t . k_s) for t > s,
-// col_b[t] = P(s, t) (q_t . k_s) for t >= s, gamma_s and the carry P(s, last). The same sums as the token-by-token rule in another
-// order: float32 results agree to rounding.
+// gamma_t = d_0 ... d_t (tokens numbered from 0 inside the chunk), y_t = v_t - gamma_t k_t . S_0 and the strictly lower triangular
+// L[t][s] = beta_t P(s, t) (k_t . k_s):
+//     c      = (I + L)^-1 diag(beta) y                                  =: T1 y
+//     read_t = (gamma_t q_t . S_0 + sum_{s<=t} P(s, t) (q_t . k_s) c_s) / sqrt(dk)   = (gamma_t q_t . S_0 + (W y)_t) / sqrt(dk)
+//     S_end  = gamma_last S_0 + sum_s P(s, last) k_s (x) c_s            = gamma_last S_0 + K^T (T2 y)
+// so a chunk is four small matrix products per block of columns of the state: K S_0 and Q S_0 (16 x 128 by 128 x columns), T2 y and W y
+// (16 x 16 by 16 x columns), K^T (T2 y) (128 x 16 by 16 x columns). The matrices T2 = diag(P(s, last)) T1 and W (both 16 x 16, lower
+// triangular) and gamma do not involve the state: deltanet_gram_kernel forms them per chunk and value head. The products run on the
+// tensor cores as mma.sync m16n8k8 with TF32 operands (k, q, the state, y and the coefficients rounded to 10 bits of mantissa, as the
+// reference's chunked kernels round theirs to binary16, runner/cuda/src/kernels_deltanet_chunked.cu:262-344) and float32 sums; the
+// state itself stays in float32 registers, as the accumulators of the last product, which are at the same time the A operand of the
+// first two (the rows of an 8-row block are paired with the k slots t and t + 4 as rows 2 t and 2 t + 1, and B is read accordingly).
 constexpr int kChunk = 16;
-constexpr int kCoef = 36;  // floats per (token, value head): col_a[16], col_b[16], gamma, carry, two of padding (rows of 144 bytes)
-constexpr int kCols = 16;  // columns of the state per CTA: four warps of four columns
-constexpr int kScanThreads = 8 * kCols;  // eight row groups of 16 rows a column
+constexpr int kCols = 16;                  // columns of the state per warp (the M of the products)
+constexpr int kRowPitch = kDim + 8;        // floats between the tokens of k and q in shared memory: conflict-free fragment loads
+constexpr int kCoef = 56;                  // floats per (token, value head): T2 row at 0, W row at 24, gamma at 48 (224 bytes)
+constexpr int kStatusDeltaNet = 24;        // status code: a wait of the scan kernel ran out
+constexpr long long kWaitLimit = 1ll << 30;
+constexpr int kStages = 4;                 // chunks in flight: a chunk's copies take longer to land than a chunk takes to work through
 
-// One block per chunk and key head, 256 threads: thread (s, t) forms k_t . k_s and q_t . k_s once and, for every value head of the
-// key head, scales them by that head's P(s, t).
+// d (16 x 8, float32) += a (16 x 8, TF32, row-major fragments) * b (8 x 8, TF32, column-major fragments).
+__device__ __forceinline__ void mma_tf32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One block per chunk and key head, 256 threads: thread (s, t) forms k_t . k_s and q_t . k_s once; then, for every value head of the
+// key head, L and the q-k matrix scaled by that head's decays, (I + L)^-1 by forward substitution (one thread a column), and T2 and W.
 __global__ void __launch_bounds__(256) deltanet_gram_kernel(const DeltaParams p) {
     __shared__ float k_sh[kChunk][kDim + 1], q_sh[kChunk][kDim + 1];
+    __shared__ float low[kChunk][kChunk + 1], qk_sh[kChunk][kChunk + 1], inv[kChunk][kChunk + 1];
+    __shared__ float decay_sh[kChunk], beta_sh[kChunk], carry_sh[kChunk], gamma_sh[kChunk];
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
     const DeltaChunk chunk = p.chunks[blockIdx.x];
@@ -188,12 +212,22 @@ __global__ void __launch_bounds__(256) deltanet_gram_kernel(const DeltaParams p)
     for (unsigned e = threadIdx.x; e < kChunk * kDim; e += 256) {
         const unsigned t = e / kDim, d = e % kDim;
         const bool live = t < chunk.count;
-        k_sh[t][d] = live ? p.k[(static_cast<size_t>(chunk.token0) + t) * p.key_dim + key_head * kDim + d] : 0.0f;
-        q_sh[t][d] = live ? p.q[(static_cast<size_t>(chunk.token0) + t) * p.key_dim + key_head * kDim + d] : 0.0f;
+        const float* pair = p.kq + (static_cast<size_t>(key_head) * p.n_tokens + chunk.token0 + t) * kPair;
+        k_sh[t][d] = live ? pair[d] : 0.0f;
+        q_sh[t][d] = live ? pair[kDim + d] : 0.0f;
     }
     __syncthreads();
-    const unsigned s = threadIdx.x / kChunk, t = threadIdx.x % kChunk;
-    if (s >= chunk.count) return;
+    // The dot products below take k and q as they are (the first token's read is (q . k) beta v, one dot product with heavy
+    // cancellation); what the scan's tensor-core products read is rounded to TF32 here, once, in place: this block alone owns the rows.
+    for (unsigned e = threadIdx.x; e < kChunk * kDim; e += 256) {
+        const unsigned t = e / kDim, d = e % kDim;
+        if (t < chunk.count) {
+            float* pair = p.kq + (static_cast<size_t>(key_head) * p.n_tokens + chunk.token0 + t) * kPair;
+            pair[d] = round_tf32(k_sh[t][d]);
+            pair[kDim + d] = round_tf32(q_sh[t][d]);
+        }
+    }
+    const unsigned s = threadIdx.x / kChunk, t = threadIdx.x % kChunk;  // as (s, t) for the dot products, as (row, column) = (s, t) later
     float kk = 0.0f, qk = 0.0f;
     for (int d = 0; d < kDim; ++d) {
         kk = __fmaf_rn(k_sh[t][d], k_sh[s][d], kk);
@@ -201,161 +235,265 @@ __global__ void __launch_bounds__(256) deltanet_gram_kernel(const DeltaParams p)
     }
     const unsigned group = p.value_heads / p.key_heads;
     for (unsigned h = key_head * group; h < (key_head + 1) * group; ++h) {
-        const float* decay = p.decay + static_cast<size_t>(chunk.token0) * p.value_heads + h;  // token r of the chunk at decay[r * value_heads]
-        float product = 1.0f;  // P(s, t), 0 where t < s or the token does not exist
-        for (unsigned r = s + 1; r <= t && r < chunk.count; ++r) product = __fmul_rn(product, decay[static_cast<size_t>(r) * p.value_heads]);
-        float* row = p.coef + ((static_cast<size_t>(chunk.token0) + s) * p.value_heads + h) * kCoef;
-        const bool live = t < chunk.count;
-        row[t] = live && t > s ? __fmul_rn(product, kk) : 0.0f;
-        row[kChunk + t] = live && t >= s ? __fmul_rn(product, qk) : 0.0f;
-        if (t == 0) {
+        __syncthreads();  // the head before this one is done with the shared arrays
+        if (threadIdx.x < kChunk) {
+            const bool live = threadIdx.x < chunk.count;
+            const size_t at = (static_cast<size_t>(chunk.token0) + threadIdx.x) * p.value_heads + h;
+            decay_sh[threadIdx.x] = live ? p.decay[at] : 1.0f;
+            beta_sh[threadIdx.x] = live ? p.beta[at] : 0.0f;
+        }
+        __syncthreads();
+        {
+            float product = 1.0f;  // P(s, t)
+            for (unsigned r = s + 1; r <= t; ++r) product = __fmul_rn(product, decay_sh[r]);
+            const bool live = s < chunk.count && t < chunk.count;
+            low[t][s] = live && t > s ? __fmul_rn(beta_sh[t], __fmul_rn(product, kk)) : 0.0f;
+            qk_sh[t][s] = live && t >= s ? __fmul_rn(product, qk) : 0.0f;
+        }
+        if (threadIdx.x < kChunk) {
             float gamma = 1.0f, carry = 1.0f;
-            for (unsigned r = 0; r <= s; ++r) gamma = __fmul_rn(gamma, decay[static_cast<size_t>(r) * p.value_heads]);
-            for (unsigned r = s + 1; r < chunk.count; ++r) carry = __fmul_rn(carry, decay[static_cast<size_t>(r) * p.value_heads]);
-            row[2 * kChunk] = gamma;
-            row[2 * kChunk + 1] = carry;
-            row[2 * kChunk + 2] = 0.0f;
-            row[2 * kChunk + 3] = 0.0f;
+            for (unsigned r = 0; r <= threadIdx.x; ++r) gamma = __fmul_rn(gamma, decay_sh[r]);
+            for (unsigned r = threadIdx.x + 1; r < chunk.count; ++r) carry = __fmul_rn(carry, decay_sh[r]);
+            gamma_sh[threadIdx.x] = gamma;
+            carry_sh[threadIdx.x] = carry;
+        }
+        __syncthreads();
+        if (threadIdx.x < kChunk) {  // column c of T1 = (I + L)^-1 diag(beta)
+            const unsigned c = threadIdx.x;
+            for (unsigned r = 0; r < kChunk; ++r) {
+                float value = r == c ? 1.0f : 0.0f;
+                for (unsigned m = c; m < r; ++m) value = __fmaf_rn(-low[r][m], inv[m][c], value);
+                inv[r][c] = r < c ? 0.0f : value;
+            }
+            for (unsigned r = 0; r < kChunk; ++r) inv[r][c] = __fmul_rn(inv[r][c], beta_sh[c]);
+        }
+        __syncthreads();
+        if (s < chunk.count) {  // row s, column t of T2 and W
+            float w = 0.0f;
+            for (unsigned m = t; m <= s; ++m) w = __fmaf_rn(qk_sh[s][m], inv[m][t], w);
+            float* row = p.coef + (static_cast<size_t>(h) * p.n_tokens + chunk.token0 + s) * kCoef;
+            row[t] = t <= s ? round_tf32(__fmul_rn(carry_sh[s], inv[s][t])) : 0.0f;
+            row[24 + t] = t <= s ? round_tf32(w) : 0.0f;
+            if (t == 0) row[48] = gamma_sh[s];
         }
     }
 }
 
-// What the sixteen tokens of a chunk need from global memory, fetched by asynchronous copies into one of two buffers while the chunk
-// before it is being worked on.
+// What the sixteen tokens of a chunk need from global memory, brought by bulk copies into one of two buffers while the chunk before it
+// is being worked on.
 struct ScanStage {
-    float k[kChunk][kDim], q[kChunk][kDim];
+    float kq[kChunk][kPair];
     float coef[kChunk][kCoef];
-    float v[kChunk][kCols];
-    float beta[kChunk];
 };
 
-__device__ __forceinline__ void scan_prefetch(const DeltaParams& p, ScanStage& st, const DeltaNetRow& row, unsigned t0, unsigned head,
-                                              unsigned key_head, unsigned first_col) {
-    if (t0 >= row.length) return;
+// Two bulk copies a chunk (a token's k and q, and its coefficients, lie one after the other in global memory as they do here); many
+// small copies were measured to take longer to issue than the chunk's arithmetic. Called by one thread of the loading warp.
+__device__ __forceinline__ void scan_fetch(const DeltaParams& p, ScanStage& st, uint32_t bar, const DeltaNetRow& row, unsigned t0, unsigned head,
+                                           unsigned key_head) {
     const unsigned count = min(static_cast<unsigned>(kChunk), row.length - t0);
     const size_t token0 = static_cast<size_t>(row.q_begin) + t0;
-    for (unsigned e = threadIdx.x; e < 2 * kChunk * kDim / 4; e += kScanThreads) {  // 16 bytes a copy
-        const unsigned which = e / (kChunk * kDim / 4), tt = (e / (kDim / 4)) % kChunk, d = 4 * (e % (kDim / 4));
-        if (tt < count)
-            ptx::cp_async_16(which == 0 ? &st.k[tt][d] : &st.q[tt][d],
-                             (which == 0 ? p.k : p.q) + (token0 + tt) * p.key_dim + key_head * kDim + d);
-    }
-    for (unsigned e = threadIdx.x; e < kChunk * kCoef / 4; e += kScanThreads) {
-        const unsigned tt = e / (kCoef / 4), d = 4 * (e % (kCoef / 4));
-        if (tt < count) ptx::cp_async_16(&st.coef[tt][d], p.coef + ((token0 + tt) * p.value_heads + head) * kCoef + d);
-    }
-    for (unsigned e = threadIdx.x; e < kChunk * kCols / 4; e += kScanThreads) {
-        const unsigned tt = e / (kCols / 4), d = 4 * (e % (kCols / 4));
-        if (tt < count) ptx::cp_async_16(&st.v[tt][d], p.v + (token0 + tt) * p.value_dim + head * kDim + first_col + d);
-    }
-    if (threadIdx.x < kChunk && threadIdx.x < count) ptx::cp_async_4(&st.beta[threadIdx.x], p.beta + (token0 + threadIdx.x) * p.value_heads + head);
+    ptx::mbar_arrive_expect_tx(bar, count * ((kPair + kCoef) * 4));
+    ptx::bulk_load(ptx::smem_addr(&st.kq[0][0]), p.kq + (static_cast<size_t>(key_head) * p.n_tokens + token0) * kPair, count * kPair * 4, bar);
+    ptx::bulk_load(ptx::smem_addr(&st.coef[0][0]), p.coef + (static_cast<size_t>(head) * p.n_tokens + token0) * kCoef, count * kCoef * 4, bar);
 }
 
-// The columns of a head's state S [dk, dv] evolve independently of one another, so a head is spread over eight CTAs of 16 columns:
-// 128 threads, each holding 16 rows (one of eight row groups) of one column in registers; a warp owns four columns, lane = 4 g + c
-// holding row group g of column c of them, so the eight partial sums of a column meet by three shuffles inside the warp, and the
-// eight lanes of a quarter warp read two 16-byte pieces of k or q (no bank conflict). The reads go to global memory in float32; the
-// gated norm over a head's 128 reads is the next launch.
-__global__ void __launch_bounds__(kScanThreads) deltanet_scan_kernel(const DeltaParams p) {
+// One arithmetic warp (and one loading warp) per run, value head and block of 16 columns of the state (columns evolve independently of
+// one another): the block, 128 rows by 16 columns, is the warp's 64 accumulator registers a thread. The reads go to global memory in float32; the gated norm over a
+// head's 128 reads is the next launch.
+__global__ void __launch_bounds__(64) deltanet_scan_kernel(const DeltaParams p) {
     extern __shared__ __align__(16) unsigned char scan_smem[];
     ScanStage* stages = reinterpret_cast<ScanStage*>(scan_smem);
+    __shared__ __align__(8) unsigned long long full[kStages], empty[kStages];
+    __shared__ unsigned abort_flag;
+    const unsigned lane = threadIdx.x % 32, g = lane / 4, t = lane % 4;
+    for (unsigned e = threadIdx.x; e < kStages * sizeof(ScanStage) / 4; e += 64) reinterpret_cast<float*>(scan_smem)[e] = 0.0f;  // what a short chunk leaves unwritten must be finite
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStages; ++i) {
+            ptx::mbar_init(ptx::smem_addr(&full[i]), 1);
+            ptx::mbar_init(ptx::smem_addr(&empty[i]), 1);
+        }
+        abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    ptx::fence_proxy_async_smem();
+    __syncthreads();
     ptx::grid_dependency_wait();
     const DeltaNetRow row = p.rows[blockIdx.x];
     const unsigned head = blockIdx.y, key_head = head / (p.value_heads / p.key_heads);
-    const unsigned warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const unsigned g = lane / 4, jl = 4 * warp + lane % 4;
-    const unsigned j = blockIdx.z * kCols + jl;  // this thread's column of the head
-    scan_prefetch(p, stages[0], row, 0, head, key_head, blockIdx.z * kCols);
-    float s[16];
-    float* state = p.states + (static_cast<size_t>(row.slot) * p.value_heads + head) * kDim * kDim;
+    const unsigned first_col = blockIdx.z * kCols;
+    if (threadIdx.x >= 32) {
+        // the loading warp: a bulk copy holds the issuing thread for hundreds of cycles, which the arithmetic warp cannot spare
+        if (lane == 0) {
+            for (unsigned t0 = 0, round = 0; t0 < row.length; t0 += kChunk, ++round) {
+                const unsigned turn = round % kStages;
+                if (round >= kStages) {  // the buffer's last chunk has been worked through: a bounded wait
+                    const uint32_t bar = ptx::smem_addr(&empty[turn]), parity = (round / kStages - 1) & 1u;
+                    const long long began = clock64();
+                    bool given_up = false;
+                    while (!ptx::mbar_try_wait(bar, parity)) {
+                        if (*static_cast<volatile unsigned*>(&abort_flag) != 0 || clock64() - began > kWaitLimit) {
+                            given_up = true;
+                            break;
+                        }
+                    }
+                    if (given_up) {
+                        abort_flag = 1;
+                        atomicCAS(p.status, 0, kStatusDeltaNet | (static_cast<int>(blockIdx.x) << 8));
+                        break;
+                    }
+                }
+                scan_fetch(p, stages[turn], ptx::smem_addr(&full[turn]), row, t0, head, key_head);
+            }
+        }
+        return;
+    }
+    // block b of the state: rows 8 b + 2 t and 8 b + 2 t + 1 of columns g ([0], [1]) and g + 8 ([2], [3])
+    float st[kDim / 8][4];
+    float* state = p.states + (static_cast<size_t>(row.slot) * p.value_heads + head) * kDim * kDim + first_col;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) s[i] = row.fresh != 0 ? 0.0f : state[static_cast<size_t>(16 * g + i) * kDim + j];
+    for (int b = 0; b < kDim / 8; ++b) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            st[b][e] = row.fresh != 0 ? 0.0f : state[static_cast<size_t>(8 * b + 2 * t + (e & 1)) * kDim + g + 8 * (e >> 1)];
+    }
     const float scale = rsqrtf(static_cast<float>(kDim));
-    for (unsigned t0 = 0, turn = 0; t0 < row.length; t0 += kChunk, turn ^= 1u) {
-        const int count = static_cast<int>(min(static_cast<unsigned>(kChunk), row.length - t0));
-        const size_t token0 = static_cast<size_t>(row.q_begin) + t0;
-        const ScanStage& st = stages[turn];
-        ptx::cp_async_wait_all();
-        __syncthreads();  // this chunk's values are in place; the chunk before it is done with the other buffer
-        scan_prefetch(p, stages[turn ^ 1u], row, t0 + kChunk, head, key_head, blockIdx.z * kCols);
-        // x[t] = k_t . S_0[:, j] and o[t] = q_t . S_0[:, j] over this thread's rows, then over the eight row groups
-        float x[kChunk], o[kChunk];
+    const float* v_base = p.v + static_cast<size_t>(row.q_begin) * p.value_dim + head * kDim + first_col + g;
+    float v_next[2][4];
 #pragma unroll
-        for (int t = 0; t < kChunk; ++t) {
-            x[t] = 0.0f;
-            o[t] = 0.0f;
-            if (t < count) {
-                const float4* k4 = reinterpret_cast<const float4*>(&st.k[t][16 * g]);
-                const float4* q4 = reinterpret_cast<const float4*>(&st.q[t][16 * g]);
-                float rec[4] = {0.0f, 0.0f, 0.0f, 0.0f}, rd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int i = 0; i < 2; ++i) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const float4 kk = k4[c], qq = q4[c];
-                    rec[0] = __fmaf_rn(kk.x, s[4 * c], rec[0]);
-                    rec[1] = __fmaf_rn(kk.y, s[4 * c + 1], rec[1]);
-                    rec[2] = __fmaf_rn(kk.z, s[4 * c + 2], rec[2]);
-                    rec[3] = __fmaf_rn(kk.w, s[4 * c + 3], rec[3]);
-                    rd[0] = __fmaf_rn(qq.x, s[4 * c], rd[0]);
-                    rd[1] = __fmaf_rn(qq.y, s[4 * c + 1], rd[1]);
-                    rd[2] = __fmaf_rn(qq.z, s[4 * c + 2], rd[2]);
-                    rd[3] = __fmaf_rn(qq.w, s[4 * c + 3], rd[3]);
-                }
-                x[t] = (rec[0] + rec[1]) + (rec[2] + rec[3]);
-                o[t] = (rd[0] + rd[1]) + (rd[2] + rd[3]);
-            }
-        }
-#pragma unroll
-        for (int t = 0; t < kChunk; ++t) {
-            if (t < count) {
-#pragma unroll
-                for (int w = 4; w < 32; w <<= 1) {  // every lane ends with the same sums
-                    x[t] += __shfl_xor_sync(0xFFFFFFFFu, x[t], w);
-                    o[t] += __shfl_xor_sync(0xFFFFFFFFu, o[t], w);
-                }
-                const float gamma = st.coef[t][2 * kChunk];
-                x[t] = __fsub_rn(st.v[t][jl], __fmul_rn(gamma, x[t]));
-                o[t] = __fmul_rn(gamma, o[t]);
-            }
-        }
-        const float gamma_last = st.coef[count - 1][2 * kChunk];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) s[i] = __fmul_rn(s[i], gamma_last);
-        // the corrections in turn: each enters the later tokens' x and o through its coefficients, and the state through its carry
-#pragma unroll
-        for (int u = 0; u < kChunk; ++u) {
-            if (u >= count) break;
-            const float correction = __fmul_rn(st.beta[u], x[u]);
-            float col[2 * kChunk];
-#pragma unroll
-            for (int c = u / 4; c < 4; ++c) {
-                const float4 a4 = reinterpret_cast<const float4*>(&st.coef[u][0])[c], b4 = reinterpret_cast<const float4*>(&st.coef[u][kChunk])[c];
-                col[4 * c] = a4.x, col[4 * c + 1] = a4.y, col[4 * c + 2] = a4.z, col[4 * c + 3] = a4.w;
-                col[kChunk + 4 * c] = b4.x, col[kChunk + 4 * c + 1] = b4.y, col[kChunk + 4 * c + 2] = b4.z, col[kChunk + 4 * c + 3] = b4.w;
-            }
-#pragma unroll
-            for (int t = u + 1; t < kChunk; ++t) x[t] = __fmaf_rn(-col[t], correction, x[t]);
-#pragma unroll
-            for (int t = u; t < kChunk; ++t) o[t] = __fmaf_rn(col[kChunk + t], correction, o[t]);
-            const float carried = __fmul_rn(correction, st.coef[u][2 * kChunk + 1]);
-            const float4* k4 = reinterpret_cast<const float4*>(&st.k[u][16 * g]);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float4 kk = k4[c];
-                s[4 * c] = __fmaf_rn(kk.x, carried, s[4 * c]);
-                s[4 * c + 1] = __fmaf_rn(kk.y, carried, s[4 * c + 1]);
-                s[4 * c + 2] = __fmaf_rn(kk.z, carried, s[4 * c + 2]);
-                s[4 * c + 3] = __fmaf_rn(kk.w, carried, s[4 * c + 3]);
-            }
-        }
-        if (g == 0) {
-#pragma unroll
-            for (int t = 0; t < kChunk; ++t)
-                if (t < count) p.reads[(token0 + t) * p.value_dim + head * kDim + j] = __fmul_rn(o[t], scale);
+        for (int e = 0; e < 4; ++e) {
+            const unsigned token = 8 * i + 2 * t + (e & 1);
+            v_next[i][e] = token < row.length ? v_base[static_cast<size_t>(token) * p.value_dim + 8 * (e >> 1)] : 0.0f;
         }
     }
-    ptx::grid_launch_dependents();
+    bool ok = true;
+    for (unsigned t0 = 0, round = 0; t0 < row.length; t0 += kChunk, ++round) {
+        const unsigned turn = round % kStages;
+        const unsigned count = min(static_cast<unsigned>(kChunk), row.length - t0);
+        const size_t token0 = static_cast<size_t>(row.q_begin) + t0;
+        const ScanStage& sg = stages[turn];
+        float v[2][4];  // this chunk's v in accumulator layout; the next chunk's is fetched now
 #pragma unroll
-    for (int i = 0; i < 16; ++i) state[static_cast<size_t>(16 * g + i) * kDim + j] = s[i];
+        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                v[i][e] = v_next[i][e];
+                const unsigned token = t0 + kChunk + 8 * i + 2 * t + (e & 1);
+                v_next[i][e] = token < row.length ? v_base[static_cast<size_t>(token) * p.value_dim + 8 * (e >> 1)] : 0.0f;
+            }
+        }
+        {  // this chunk's values: a bounded wait
+            const uint32_t bar = ptx::smem_addr(&full[turn]), parity = (round / kStages) & 1u;
+            const long long began = clock64();
+            while (!ptx::mbar_try_wait(bar, parity)) {
+                if (*static_cast<volatile unsigned*>(&abort_flag) != 0 || clock64() - began > kWaitLimit) {
+                    ok = false;
+                    break;
+                }
+            }
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) {
+                if (lane == 0) {
+                    abort_flag = 1;
+                    atomicCAS(p.status, 0, kStatusDeltaNet | (static_cast<int>(blockIdx.x) << 8));
+                }
+                break;
+            }
+        }
+        // X^T = S_0^T K^T and O^T = S_0^T Q^T: [columns, tokens], tokens 0-7 in [0], 8-15 in [1]; two partial sums each for the chain
+        float x[2][2][4] = {}, o[2][2][4] = {};
+        // Each product phase sits behind a branch that is always taken (the call has rows) but that the compiler cannot see through:
+        // scheduled as one straight line with its neighbours, the chunk was measured a fifth slower.
+        if (p.n_rows != 0) {
+            float2 kf[2][2], qf[2][2];  // the B fragments of block b in [b & 1], fetched one block ahead
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                kf[0][i] = *reinterpret_cast<const float2*>(&sg.kq[8 * i + g][2 * t]);
+                qf[0][i] = *reinterpret_cast<const float2*>(&sg.kq[8 * i + g][kDim + 2 * t]);
+            }
+#pragma unroll
+            for (int b = 0; b < kDim / 8; ++b) {
+                if (b + 1 < kDim / 8) {
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        kf[(b + 1) & 1][i] = *reinterpret_cast<const float2*>(&sg.kq[8 * i + g][8 * (b + 1) + 2 * t]);
+                        qf[(b + 1) & 1][i] = *reinterpret_cast<const float2*>(&sg.kq[8 * i + g][kDim + 8 * (b + 1) + 2 * t]);
+                    }
+                }
+                const uint32_t a0 = to_tf32(st[b][0]), a1 = to_tf32(st[b][2]), a2 = to_tf32(st[b][1]), a3 = to_tf32(st[b][3]);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    mma_tf32(x[b & 1][i], a0, a1, a2, a3, __float_as_uint(kf[b & 1][i].x), __float_as_uint(kf[b & 1][i].y));
+                    mma_tf32(o[b & 1][i], a0, a1, a2, a3, __float_as_uint(qf[b & 1][i].x), __float_as_uint(qf[b & 1][i].y));
+                }
+            }
+        }
+        // y = v - gamma x (zero beyond the chunk's tokens) and the reads' first term gamma o, in accumulator layout: element e of
+        // tile i is token 8 i + 2 t + (e & 1), column g + 8 (e >> 1)
+        float y[2][4], rd[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const unsigned token = 8 * i + 2 * t + (e & 1);
+                const float gamma = sg.coef[token][48];
+                const bool live = token < count;
+                y[i][e] = live ? __fsub_rn(v[i][e], __fmul_rn(gamma, x[0][i][e] + x[1][i][e])) : 0.0f;
+                rd[i][e] = live ? __fmul_rn(gamma, o[0][i][e] + o[1][i][e]) : 0.0f;
+            }
+        }
+        // C^T = y T2^T and the reads' second term y W^T: [columns, tokens] again; the coefficient matrices are lower triangular
+        float c[2][4] = {};
+        if (p.n_rows != 0)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t a0 = to_tf32(y[j][0]), a1 = to_tf32(y[j][2]), a2 = to_tf32(y[j][1]), a3 = to_tf32(y[j][3]);
+#pragma unroll
+            for (int i = j; i < 2; ++i) {
+                const float2 tf = *reinterpret_cast<const float2*>(&sg.coef[8 * i + g][8 * j + 2 * t]);
+                const float2 wf = *reinterpret_cast<const float2*>(&sg.coef[8 * i + g][24 + 8 * j + 2 * t]);
+                mma_tf32(c[i], a0, a1, a2, a3, __float_as_uint(tf.x), __float_as_uint(tf.y));
+                mma_tf32(rd[i], a0, a1, a2, a3, __float_as_uint(wf.x), __float_as_uint(wf.y));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const unsigned token = 8 * i + 2 * t + (e & 1), col = g + 8 * (e >> 1);
+                if (token < count) p.reads[(token0 + token) * p.value_dim + head * kDim + first_col + col] = __fmul_rn(rd[i][e], scale);
+                else c[i][e] = 0.0f;  // a row of T2 beyond the chunk is whatever an earlier chunk left there
+            }
+        }
+        // S^T = gamma_last S_0^T + C^T K
+        const float gamma_last = sg.coef[count - 1][48];
+        uint32_t ca[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) ca[j][0] = to_tf32(c[j][0]), ca[j][1] = to_tf32(c[j][2]), ca[j][2] = to_tf32(c[j][1]), ca[j][3] = to_tf32(c[j][3]);
+#pragma unroll
+        for (int b = 0; b < kDim / 8; ++b) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) st[b][e] = __fmul_rn(st[b][e], gamma_last);
+        }
+        if (p.n_rows != 0)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {  // the two products into one block of the state depend on each other: sixteen others between them
+#pragma unroll
+            for (int b = 0; b < kDim / 8; ++b)
+                mma_tf32(st[b], ca[j][0], ca[j][1], ca[j][2], ca[j][3], __float_as_uint(sg.kq[8 * j + 2 * t][8 * b + g]),
+                         __float_as_uint(sg.kq[8 * j + 2 * t + 1][8 * b + g]));
+        }
+        __syncwarp();  // every lane has read what it needs of the buffer
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&empty[turn]));
+    }
+    ptx::grid_launch_dependents();
+    if (!ok) return;
+#pragma unroll
+    for (int b = 0; b < kDim / 8; ++b) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) state[static_cast<size_t>(8 * b + 2 * t + (e & 1)) * kDim + g + 8 * (e >> 1)] = st[b][e];
+    }
 }
 
 // The gated norm of every token's and value head's 128 reads: x / sqrt(mean(x^2) + eps) * weight * silu(z) (the weight itself, not
@@ -399,7 +537,7 @@ void launch_deltanet(Context& ctx, const DeltaNetShape& shape, const DeltaNetRow
         throw std::invalid_argument("sepal_b200 deltanet: head_dim must be 128, value_heads a multiple of key_heads (at most 32 key heads), 1 to 8 conv taps");
     if (n_rows == 0) return;
     if (rows == nullptr || mixed.data == nullptr || z.data == nullptr || b.data == nullptr || a.data == nullptr || weights.conv == nullptr ||
-        weights.a_log == nullptr || weights.dt_bias == nullptr || weights.norm == nullptr || scratch.q == nullptr || scratch.k == nullptr ||
+        weights.a_log == nullptr || weights.dt_bias == nullptr || weights.norm == nullptr || scratch.kq == nullptr ||
         scratch.v == nullptr || scratch.decay == nullptr || scratch.beta == nullptr || scratch.reads == nullptr || scratch.coef == nullptr || states == nullptr || tails == nullptr || out == nullptr)
         throw std::invalid_argument("sepal_b200 deltanet: null pointer");
     for (std::size_t i = 0; i < n_rows; ++i) {
@@ -449,23 +587,25 @@ void launch_deltanet(Context& ctx, const DeltaNetShape& shape, const DeltaNetRow
     p.a_log = weights.a_log;
     p.dt_bias = weights.dt_bias;
     p.norm = weights.norm;
-    p.q = scratch.q;
-    p.k = scratch.k;
+    p.kq = scratch.kq;
     p.v = scratch.v;
     p.decay = scratch.decay;
     p.beta = scratch.beta;
     p.reads = scratch.reads;
     p.coef = scratch.coef;
+    p.status = ctx.status;
     p.states = states;
     p.tails = tails;
     p.out = static_cast<__half*>(out);
     p.out_stride = out_stride;
     const unsigned last = rows[n_rows - 1].q_begin + rows[n_rows - 1].length;
+    p.n_tokens = last;
     const std::size_t prepare_smem = static_cast<std::size_t>(p.conv_dim) * sizeof(float);
     if (prepare_smem > 160 * 1024) throw std::invalid_argument("sepal_b200 deltanet: the convolution is wider than the prepare kernel's shared memory");
     static bool configured[64] = {};
     if (ctx.device >= 64 || !configured[ctx.device]) {
         check(cudaFuncSetAttribute(deltanet_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024), "cudaFuncSetAttribute");
+        check(cudaFuncSetAttribute(deltanet_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kStages * sizeof(ScanStage))), "cudaFuncSetAttribute");
         if (ctx.device < 64) configured[ctx.device] = true;
     }
     launch_kernel(deltanet_prepare_kernel, dim3(last), dim3(256), prepare_smem, stream, "deltanet_prepare_kernel launch", p);
@@ -478,8 +618,8 @@ void launch_deltanet(Context& ctx, const DeltaNetShape& shape, const DeltaNetRow
     launch_kernel(deltanet_gram_kernel, dim3(static_cast<unsigned>(chunks.size()), shape.key_heads), dim3(256), 0, stream, "deltanet_gram_kernel launch", p);
     count_launch();
     // An ordinary launch, not an overlapped one: blocks of the scan that arrive while the launch before it still fills the SMs settle
-    // wherever room appears first, several to an SM with other SMs left empty, and a run's eight blocks per head then take twice as long.
-    deltanet_scan_kernel<<<dim3(static_cast<unsigned>(n_rows), shape.value_heads, kDim / kCols), dim3(kScanThreads), 2 * sizeof(ScanStage), stream>>>(p);
+    // wherever room appears first, several to an SM with other SMs left empty, and a run's eight warps per head then take twice as long.
+    deltanet_scan_kernel<<<dim3(static_cast<unsigned>(n_rows), shape.value_heads, kDim / kCols), dim3(64), kStages * sizeof(ScanStage), stream>>>(p);
     check(cudaGetLastError(), "deltanet_scan_kernel launch");
     count_launch();
     const std::size_t units = static_cast<std::size_t>(last) * shape.value_heads;

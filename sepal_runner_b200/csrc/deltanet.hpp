@@ -9,9 +9,8 @@
 //
 // State. A request owns a slot: its recurrent state [value heads, dk, dv] float32 and the last K - 1 rows of `mixed`. A call holds runs
 // of consecutive tokens of different requests; a run continues its slot's state and leaves it updated, so a request cut into several
-// calls gives what it gives in one. The scan takes a run in chunks of sixteen tokens (eight CTAs per run and value head, each with 16
-// columns of the state in registers, on the ordinary cores): larger chunks on the tensor cores are the next step for this row of the
-// scope table.
+// calls gives what it gives in one. The scan takes a run in chunks of sixteen tokens (eight warps per run and value head, each with 16
+// columns of the float32 state in registers; the chunk's matrix products on the tensor cores with TF32 operands).
 #pragma once
 
 #include <cstddef>
@@ -49,11 +48,11 @@ struct DeltaNetWeights {
     const float* norm = nullptr;
 };
 
-/// Scratch of one call (device, float32, 16-byte aligned), sized for the call's tokens N: q, k [N, key_dim]; v, reads [N, value_dim];
-/// coef [N, value_heads, 36] (the chunk coefficients); decay, beta [N, value_heads].
+/// Scratch of one call (device, float32, 16-byte aligned), sized for the call's tokens N: kq [key_heads, N, 264] (a token's k, q and 8
+/// floats of padding per key head); v, reads [N, value_dim]; coef [value_heads, N, 56] (the chunk coefficients); decay, beta
+/// [N, value_heads].
 struct DeltaNetScratch {
-    float* q = nullptr;
-    float* k = nullptr;
+    float* kq = nullptr;
     float* v = nullptr;
     float* reads = nullptr;
     float* coef = nullptr;
@@ -63,16 +62,15 @@ struct DeltaNetScratch {
 
 /// Floats of scratch a call of `tokens` tokens needs, and the scratch carved out of one such allocation.
 inline std::size_t deltanet_scratch_floats(const DeltaNetShape& s, std::size_t tokens) {
-    return tokens * (2 * static_cast<std::size_t>(s.key_dim()) + 2 * s.value_dim() + 38 * static_cast<std::size_t>(s.value_heads));
+    return tokens * (264 * static_cast<std::size_t>(s.key_heads) + 2 * s.value_dim() + 58 * static_cast<std::size_t>(s.value_heads));
 }
 inline DeltaNetScratch deltanet_scratch(float* base, const DeltaNetShape& s, std::size_t tokens) {
     DeltaNetScratch sc;
-    sc.q = base;
-    sc.k = sc.q + tokens * s.key_dim();
-    sc.v = sc.k + tokens * s.key_dim();
+    sc.kq = base;
+    sc.v = sc.kq + tokens * s.key_heads * 264;
     sc.reads = sc.v + tokens * s.value_dim();
     sc.coef = sc.reads + tokens * s.value_dim();
-    sc.decay = sc.coef + tokens * s.value_heads * 36;
+    sc.decay = sc.coef + tokens * s.value_heads * 56;
     sc.beta = sc.decay + tokens * s.value_heads;
     return sc;
 }

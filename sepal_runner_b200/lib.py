@@ -336,7 +336,7 @@ def deltanet(ctx, shape, rows, mixed, z, b, a, conv, a_log, dt_bias, norm, state
     table = (DeltaNetRow * len(rows))(*[DeltaNetRow(*r) for r in rows])
     n = max((r[0] + r[1] for r in rows), default=0)
     kd, vd = shape.key_heads * shape.head_dim, shape.value_heads * shape.head_dim
-    scratch = torch.empty(max(1, n * (2 * kd + 2 * vd + 38 * shape.value_heads)), dtype=torch.float32, device=out.device)
+    scratch = torch.empty(max(1, n * (264 * shape.key_heads + 2 * vd + 58 * shape.value_heads)), dtype=torch.float32, device=out.device)
     assert mixed.dtype == z.dtype == b.dtype == a.dtype
     _check(ctx._lib.sepal_b200_deltanet(ctx._h, C.byref(shape), table, len(rows), mixed.data_ptr(), mixed.stride(0), z.data_ptr(), z.stride(0), b.data_ptr(),
                                         b.stride(0), a.data_ptr(), a.stride(0), 1 if mixed.dtype == torch.float16 else 0, conv.data_ptr(), a_log.data_ptr(),

@@ -1,6 +1,7 @@
 """The Gated DeltaNet core on the device against the float64 restatement of the reference's mixer (oracle/deltanet_oracle.py). The
-device works in float32 on a recurrent state, so the bound is a float32 one: relative Frobenius error 1e-4 on the binary16 output's
-float64 counterpart after rounding (2^-11 per element dominates: 1e-3), 1e-4 on the states."""
+device keeps the recurrent state in float32 and forms a chunk's matrix products on the tensor cores with TF32 operands (10 bits of
+mantissa, the precision the reference's chunked kernels give theirs by rounding to binary16), so the bounds are those of a 2^-11
+rounding per operand: relative Frobenius error 2e-3 on the binary16 output and 1e-3 on the float32 states (measured: 4e-4)."""
 import numpy as np
 import pytest
 
@@ -22,7 +23,7 @@ def ctx():
     c.close()
 
 
-def run_case(ctx, key_heads, value_heads, taps, requests, seed, half):
+def run_case(ctx, key_heads, value_heads, taps, requests, seed, half, a_log=None):
     """requests: list of (first call's tokens, second call's tokens): every request runs as two calls; the second continues the first."""
     import torch
 
@@ -35,7 +36,7 @@ def run_case(ctx, key_heads, value_heads, taps, requests, seed, half):
     kd, vd = key_heads * dim, value_heads * dim
     conv_dim = 2 * kd + vd
     conv = (rng.standard_normal((conv_dim, taps)) * 0.5).astype(np.float32)
-    a_log = (rng.standard_normal(value_heads) * 0.5).astype(np.float32)
+    a_log = (rng.standard_normal(value_heads) * 0.5).astype(np.float32) if a_log is None else np.asarray(a_log, np.float32)
     dt_bias = (rng.standard_normal(value_heads) * 0.5).astype(np.float32)
     norm = (1.0 + rng.standard_normal(dim) * 0.1).astype(np.float32)
     slots = len(requests) + 1
@@ -75,8 +76,8 @@ def run_case(ctx, key_heads, value_heads, taps, requests, seed, half):
         want, state, tail = do.core(mixed, z, b, a, conv, a_log, dt_bias, norm, key_heads, value_heads, dim, 1e-6)
         got = np.concatenate(outs[i])
         assert np.isfinite(got).all()
-        assert rel_fro(got, want) < 1e-3, (i, rel_fro(got, want))
-        assert rel_fro(states[i + 1].cpu().numpy(), state) < 1e-4
+        assert rel_fro(got, want) < 2e-3, (i, rel_fro(got, want))
+        assert rel_fro(states[i + 1].cpu().numpy(), state) < 1e-3, (i, rel_fro(states[i + 1].cpu().numpy(), state))
         if taps > 1:
             assert np.array_equal(tails[i + 1, :taps - 1].cpu().numpy(), tail.astype(np.float32))
 
@@ -91,6 +92,21 @@ def test_several_requests_and_other_tap_counts(ctx):
     run_case(ctx, key_heads=2, value_heads=2, taps=4, requests=[(5, 70), (1, 1), (64, 0), (33, 200)], seed=4, half=True)
     run_case(ctx, key_heads=1, value_heads=2, taps=1, requests=[(20, 20)], seed=5, half=False)
     run_case(ctx, key_heads=1, value_heads=1, taps=3, requests=[(20, 20), (7, 3)], seed=6, half=False)
+
+
+def test_chunk_boundaries(ctx):
+    """Run lengths around the scan's chunk of sixteen tokens, as one call and cut at every kind of place
+    (runner/cuda/tests/test_kernels_deltanet.cpp:1061 walks the same lengths)."""
+    run_case(ctx, key_heads=1, value_heads=2, taps=4, requests=[(1, 0), (5, 0), (16, 0), (17, 0), (33, 0), (70, 0)], seed=7, half=True)
+    run_case(ctx, key_heads=1, value_heads=1, taps=4, requests=[(16, 16), (15, 1), (1, 15), (17, 47), (31, 33)], seed=8, half=True)
+
+
+def test_strong_decay(ctx):
+    """Decays from 0.97 a token down to exactly zero in float32 (runner/cuda/tests/test_kernels_deltanet.cpp:1015-1030): the products
+    of decays inside a chunk underflow to zero, which must stay zero and not turn into a NaN."""
+    heads = 4
+    a_log = [np.log(0.03 + h / (heads - 1) * 200.0) for h in range(heads)]
+    run_case(ctx, key_heads=2, value_heads=heads, taps=4, requests=[(1, 0), (5, 12), (16, 1), (33, 37)], seed=9, half=True, a_log=a_log)
 
 
 def test_arguments_are_checked(ctx):

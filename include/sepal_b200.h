@@ -67,7 +67,8 @@ SEPAL_B200_API void sepal_b200_close(sepal_b200_ctx* ctx);
 SEPAL_B200_API int32_t sepal_b200_info(sepal_b200_ctx* ctx, char* buffer, uint64_t capacity, uint64_t* needed);
 
 /* Waits for `stream`, then reads and clears the device status word: *status_out = 0 when no kernel reported a problem, otherwise
- * the code of the first bounded wait that ran out (low byte: which wait; higher bits: the CTA). A non-zero status means the
+ * the code of the first bounded wait that ran out (low byte: which wait, 1 .. 8 in the GEMM kernels, 16 .. 23 in the attention
+ * kernels, 24 in the DeltaNet scan; higher bits: the CTA). A non-zero status means the
  * outputs of the launches since the last call are not to be trusted. The reference reports device faults through
  * cudaStreamSynchronize in CudaEngine::run (runner/cuda/src/cuda_engine.cpp:1969); this is the same place in the flow. */
 SEPAL_B200_API int32_t sepal_b200_status(sepal_b200_ctx* ctx, void* stream, int32_t* status_out);

@@ -46,7 +46,7 @@ TRUNK_SHAPES = [("gate_up+swiglu", 19456, 2560, "swiglu"), ("up (config 0)", 972
                 ("dn_in", 8192, 2560, "store"), ("dn_out+residual", 2560, 2048, "add")]
 # DRAM bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the workload's kernel; the summaries under
 # profiles/ give the command). None: not captured.
-NCU_TRAFFIC = {"w8g_down_m900": 52.0e6, "f16_up_m4096": None}
+NCU_TRAFFIC = {"w8g_down_m900": 47.6e6, "f16_up_m4096": None}
 L2_BYTES = 126 * 1024 * 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 

@@ -1489,14 +1489,19 @@ unsigned size_pair_grid(const Context& ctx, GemmParams& p, unsigned max_pairs, u
 // the whole launch waiting. (M 900, N 2560, K 9728: 50 us against 56 us for whole tiles in fp16, 59 against 69 in int8; with K 4096,
 // 34 us against 30.) With more than 1024 rows splitting every tile does not pay: the pairs no longer walk k in step, the operands lose
 // their reuse in the L2 and the main loop slows down by as much as the idle pairs cost. There the split is kept to the last waves
-// (2: whole tiles first), which needs at least two full waves before the partial one. `config` can force either.
-unsigned pick_pair_stream_k(unsigned pairs, unsigned pair_tiles, unsigned m, unsigned k) {
+// (2: whole tiles first) when there are at least two full waves before the partial one; with fewer, every tile is split as for few
+// rows. `config` can force either.
+unsigned pick_pair_stream_k(unsigned pairs, unsigned pair_tiles, unsigned m, unsigned k, bool w8) {
     if (pairs == 0) return 0;
     const unsigned waves = (pair_tiles + pairs - 1) / pairs;
     const double idle = waves - static_cast<double>(pair_tiles) / pairs;
     if (idle * k < 2400.0) return 0;
     if (m <= 1024) return 1;
-    return pair_tiles / pairs >= 2 ? 2u : 0u;
+    if (pair_tiles / pairs >= 2) return 2;
+    // Fewer than two full waves: there is no whole-tile part to keep, every tile is split as for few rows (M 2048, down projection:
+    // 117 -> 89 us in fp16, 152 -> 102 us in int8). The fp16 main loop, the faster one, feels the lost reuse in the L2 from about 2500
+    // rows up and then needs half a wave of idle pairs to win (M 3000: 127 us whole, 140 us split; int8: 183 against 164).
+    return w8 || idle >= 0.45 ? 1u : 0u;
 }
 
 // The order of the tiles of a pair launch. The pairs of a wave work on consecutive tiles at about the same k, so what consecutive
@@ -1539,7 +1544,7 @@ void launch_w8_pair(const Context& ctx, const CUtensorMap& map_x, const CUtensor
     const unsigned smem = total();
     static int cache[64] = {};
     const unsigned max_pairs = static_cast<unsigned>(max_pairs_of(ctx, reinterpret_cast<const void*>(gemm_w8_pair_kernel), kW8Threads, cache));
-    p.stream_k = stream_k < 0 ? pick_pair_stream_k(max_pairs, pair_tiles, p.m, p.k) : static_cast<unsigned>(stream_k);
+    p.stream_k = stream_k < 0 ? pick_pair_stream_k(max_pairs, pair_tiles, p.m, p.k, true) : static_cast<unsigned>(stream_k);
     const unsigned pairs = size_pair_grid(ctx, p, max_pairs, pair_tiles);
     launch_kernel(gemm_w8_pair_kernel, dim3(2 * pairs), dim3(kW8Threads), smem, stream, "gemm_w8_pair_kernel launch", map_x, map_w, map_y, p);
     ++g_launches;
@@ -1589,7 +1594,7 @@ void launch_pair(const Context& ctx, const CUtensorMap& map_x, const CUtensorMap
         }
         max_pairs[slot] = clusters < ctx.sm_count / 2 ? clusters : ctx.sm_count / 2;
     }
-    p.stream_k = stream_k < 0 ? pick_pair_stream_k(static_cast<unsigned>(max_pairs[slot]), pair_tiles, p.m, p.k) : static_cast<unsigned>(stream_k);
+    p.stream_k = stream_k < 0 ? pick_pair_stream_k(static_cast<unsigned>(max_pairs[slot]), pair_tiles, p.m, p.k, false) : static_cast<unsigned>(stream_k);
     const unsigned pairs = size_pair_grid(ctx, p, static_cast<unsigned>(max_pairs[slot]), pair_tiles);
     launch_kernel(gemm_pair_kernel, dim3(2 * pairs), dim3(kPairThreads), smem, stream, "gemm_pair_kernel launch", map_x, map_w, map_y, p);
     ++g_launches;

@@ -21,6 +21,7 @@
 // sepal_b200_status.
 #include "gemm.hpp"
 
+#include <cmath>
 #include <cstdint>
 #include <cstring>
 #include <mutex>
@@ -1495,7 +1496,9 @@ unsigned pick_pair_stream_k(unsigned pairs, unsigned pair_tiles, unsigned m, uns
     if (pairs == 0) return 0;
     const unsigned waves = (pair_tiles + pairs - 1) / pairs;
     const double idle = waves - static_cast<double>(pair_tiles) / pairs;
-    if (idle * k < 2400.0) return 0;
+    // With more than two pairs to a tile most tiles have three or more pieces that end together and the fix-up takes the long way
+    // (o projection at M 300, 20 tiles on 74 pairs, int8: 35 us whole, 61 us split): the gain must be twice as large to pay for it.
+    if (idle * k < (pairs <= 2 * pair_tiles ? 2600.0 : 4800.0)) return 0;
     if (m <= 1024) return 1;
     if (pair_tiles / pairs >= 2) return 2;
     // Fewer than two full waves: there is no whole-tile part to keep, every tile is split as for few rows (M 2048, down projection:
@@ -1657,8 +1660,11 @@ unsigned pick_bn(std::size_t n, bool coarse) {
 }
 
 // CTA pairs pay a cluster launch and two cluster barriers; measured, they win from about 24 GFLOP per product up (fp16 weights).
+// A pair's tile has 256 rows: when that pads the rows by over a tenth more than tiles of 128 rows do (300 rows: 512 against 384), the
+// lone CTAs win (gate_up at M 300: 48 us against 56).
 bool pick_pair(std::size_t t, std::size_t n, std::size_t k) {
-    return t > kBM && static_cast<double>(t) * static_cast<double>(n) * static_cast<double>(k) >= 1.2e10;
+    const std::size_t rows_pair = (t + 2 * kBM - 1) / (2 * kBM) * (2 * kBM), rows_lone = (t + kBM - 1) / kBM * kBM;
+    return t > kBM && 10 * rows_pair <= 11 * rows_lone && static_cast<double>(t) * static_cast<double>(n) * static_cast<double>(k) >= 1.2e10;
 }
 
 // config: -1 picks; 0..3 are the four fixed schedules of gemm.hpp; otherwise the tile width (a multiple of 16 in [16, 256]) plus 1
@@ -1747,6 +1753,15 @@ void launch_gemm_f16(Context& ctx, const void* x, std::size_t ld_x, const void* 
     unsigned bn = 256;
     bool stream_k = false, pair = false, late = false;
     decode_config(config, n, epilogue == Epilogue::SwiGLU, pick_pair(t, n, k), "launch_gemm_f16", bn, stream_k, pair, &late);
+    if (config == -1 && !pair) {
+        // Lone CTAs: the even split of k when whole tiles leave many SMs idle over a long k and no tile gets more than three pieces
+        // (down projection at M 600: 50 tiles on 148 SMs, 58 us whole, 45 us split; its fix-up costs more than on pairs, so the bar
+        // is higher: the o projection at the same M, 27 us whole, takes 31 us split).
+        const std::size_t tiles = ((t + kBM - 1) / kBM) * ((n + bn - 1) / bn), ctas = static_cast<std::size_t>(ctx.sm_count);
+        const double waves = static_cast<double>(tiles) / static_cast<double>(ctas);
+        const double idle = std::ceil(waves) - waves;
+        stream_k = (bn == 128 || bn == 256) && idle * static_cast<double>(k) >= 4800.0 && ctas <= 3 * tiles;
+    }
     GemmParams p = common_params(ctx, y, ld_y, y_half, t, n, k, epilogue);
     const CUtensorMap map_x = make_tensor_map_2d(ctx, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, t, k, ld_x, kBM, kBK, true);
     const CUtensorMap map_w = make_tensor_map_2d(ctx, w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n, k, ld_w, pair ? bn / 2 : bn, kBK, true);
@@ -1778,6 +1793,15 @@ void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMat
     // The pair kernel takes any tile width; the lone-CTA kernel (few rows, or the even split of k) takes 128 or 256.
     const bool wants_pair = config == -1 ? t > kBM : (config >= kConfigs && (config & 2) != 0);
     decode_config(config, n, epilogue == Epilogue::SwiGLU || !wants_pair, wants_pair, "launch_gemm_w8g", bn, stream_k, pair, &late);
+    // Few tiles of 256 columns (less than half of the pairs busy): tiles of 128 columns put twice as many pairs to work and each is
+    // somewhat shorter (o projection at M 300: 35 -> 31 us; k or v at M 900: 25 -> 23 us), unless the even split of k already fills
+    // the pairs with at most two and a half of them to a tile (down projection at M 600: 55 us split at 256 columns, 61 at 128).
+    if (config == -1 && pair && bn == 256 && n > 128) {
+        const unsigned pairs = static_cast<unsigned>(ctx.sm_count / 2);
+        const unsigned tiles = static_cast<unsigned>(((t + 2 * kBM - 1) / (2 * kBM)) * ((n + 255) / 256));
+        const bool split_fills = pick_pair_stream_k(pairs, tiles, static_cast<unsigned>(t), static_cast<unsigned>(k), true) != 0 && 2 * pairs <= 5 * tiles;
+        if (2 * tiles <= pairs && !split_fills) bn = 128;
+    }
     GemmParams p = common_params(ctx, y, ld_y, y_half, t, n, k, epilogue);
     p.scales_t = static_cast<const __half*>(scales_t);
     p.ld_st = ld_st;

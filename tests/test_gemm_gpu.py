@@ -528,3 +528,26 @@ def test_late_split_with_swiglu(ctx, oracle):
     y = ctx.gemm_f16(dev(x).half(), packed, epilogue=sb.SWIGLU, y_half=False, config=128 + 6)
     ctx.check_status()
     assert rel_fro(y.cpu().numpy(), want) < 1e-5
+
+
+# ---- the automatic choice (config -1) on shapes that reach each of its branches ----------------------------------------------------------
+
+
+@pytest.mark.parametrize("t,n,k", [(600, 2560, 9728),    # lone CTAs, even split of k (50 tiles on 148 SMs, long k)
+                                   (2048, 2560, 3072),   # pairs, many rows, fewer than two full waves: every tile split
+                                   (4096, 2560, 4096),   # pairs, whole tiles first, the split kept to the last waves
+                                   (300, 2560, 512)])    # int8: tiles of 128 columns because tiles of 256 would be few
+def test_automatic_choice_branches(ctx, oracle, t, n, k):
+    x, w = make(oracle, 8000 + t + k, t, n, k)
+    want = oracle.gemm(x, w)
+    y = ctx.gemm_f16(dev(x).half(), dev(w).half(), y_half=False)
+    ctx.check_status()
+    assert rel_fro(y.cpu().numpy(), want) < 1e-5
+    if k % 128 == 0:
+        wf = (np.random.default_rng(8100 + t).standard_normal((n, k)) / np.sqrt(k)).astype(np.float32)
+        q, s = ctx.quantize_group_s8(dev(wf))
+        wq = ctx.prepare_w8g(q, s)
+        y8 = ctx.gemm_w8g(dev(x).half(), wq, y_half=False)
+        ctx.check_status()
+        qo, so = oracle.quantize_group_s8(wf)
+        assert rel_fro(y8.cpu().numpy(), oracle.gemm(x, oracle.dequant_group_s8(qo, so))) < 1e-3

@@ -551,3 +551,21 @@ def test_automatic_choice_branches(ctx, oracle, t, n, k):
         ctx.check_status()
         qo, so = oracle.quantize_group_s8(wf)
         assert rel_fro(y8.cpu().numpy(), oracle.gemm(x, oracle.dequant_group_s8(qo, so))) < 1e-3
+
+
+def test_split_schedules_are_deterministic_over_many_launches(ctx, oracle):
+    """The even split's fix-up depends on which CTA arrives last at a tile; the sums do not. Fifty back-to-back launches of the
+    headline shape (two late pieces per tile) and of a late-split shape give the same bits every time and leave the status word clear."""
+    import torch
+
+    for t, n, k in ((900, 2560, 9728), (4096, 2560, 4096)):
+        x, w = make(oracle, 9000 + t, t, n, k)
+        xd, wd = dev(x).half(), dev(w).half()
+        wf = (np.random.default_rng(9100 + t).standard_normal((n, k)) / np.sqrt(k)).astype(np.float32)
+        q, s = ctx.quantize_group_s8(dev(wf))
+        wq = ctx.prepare_w8g(q, s)
+        for call in (lambda: ctx.gemm_f16(xd, wd, y_half=False), lambda: ctx.gemm_w8g(xd, wq, y_half=False)):
+            first = call().clone()
+            for _ in range(50):
+                assert torch.equal(call(), first)
+            ctx.check_status()

@@ -1,9 +1,11 @@
-"""ctypes loaders for the two checkers. TEST INFRASTRUCTURE, not product code.
+"""ctypes loaders for the checkers. TEST INFRASTRUCTURE, not product code.
 
 `Oracle`  -> oracle/libsepal_oracle.so, the C restatement (sepal_oracle.c).
 `Ref`     -> oracle/_ref/libsepal_ref.so, the reference's own CPU GEMM compiled from its sources (ref_shim.cpp, Makefile).
+`RefGpu`  -> oracle/_ref/libsepal_ref_gpu.so, the reference's own GPU multiplies compiled from its sources for sm_100, and
+             the cuBLAS call its engine makes (ref_gpu_shim.cu, Makefile).
 
-Only tests/, the smoke check and the benchmark's CPU-baseline leg import this module.
+Only tests/, the smoke check and the benchmark's baseline legs import this module.
 """
 from __future__ import annotations
 
@@ -16,7 +18,12 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "libsepal_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libsepal_ref.so")
-REFERENCE_ROOT = "/root/reference"
+REF_GPU_SO = os.path.join(HERE, "_ref", "libsepal_ref_gpu.so")
+
+
+def reference_root() -> str:
+    """Where the reference tree is: the environment variable SEPAL_REFERENCE, else a directory `reference` beside this repository."""
+    return os.environ.get("SEPAL_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 _f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
 _f64p = np.ctypeslib.ndpointer(dtype=np.float64, flags="C_CONTIGUOUS")
@@ -28,9 +35,10 @@ _sz = C.c_size_t
 def build(want_ref: bool = True) -> None:
     """Compile the checkers (make in oracle/). The reference library is built only where the reference tree exists."""
     targets = ["oracle"]
-    if want_ref and os.path.exists(os.path.join(REFERENCE_ROOT, "runner", "src", "cpu", "gemm.cpp")):
-        targets.append("ref")
-    subprocess.run(["make", "-s", "-C", HERE, f"REF={REFERENCE_ROOT}", *targets], check=True)
+    root = reference_root()
+    if want_ref and os.path.exists(os.path.join(root, "runner", "src", "cpu", "gemm.cpp")):
+        targets += ["ref", "ref_gpu"]
+    subprocess.run(["make", "-s", "-C", HERE, f"REF={root}", *targets], check=True)
 
 
 def f32(a) -> np.ndarray:
@@ -275,3 +283,103 @@ class Ref:
         finally:
             self.lib.ref_packed_free(handle)
         return out, y
+
+
+class RefGpu:
+    """The reference's own GPU multiplies and its cuBLAS call, on torch CUDA tensors. `available()` is False where it was never built."""
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(REF_GPU_SO)
+
+    def __init__(self) -> None:
+        if not self.available():
+            raise RuntimeError("oracle/_ref/libsepal_ref_gpu.so is not built (needs the reference tree: make -C oracle ref_gpu)")
+        L = self.lib = C.CDLL(REF_GPU_SO)
+        p, z, i, u = C.c_void_p, C.c_size_t, C.c_int, C.c_uint
+        L.ref_gpu_last_error.restype = C.c_char_p
+        L.ref_gpu_gemm_nt.argtypes = [p, z, p, z, p, z, i, z, z, z, i, u, i, p]
+        L.ref_gpu_quantize_weights_s8.argtypes = [p, z, p, p, z, z, i, p]
+        L.ref_gpu_gemm_w8a16.argtypes = [p, z, p, z, p, p, z, i, z, z, z, i, p]
+        L.ref_gpu_gemm_simt.argtypes = [p, z, p, z, p, z, i, p, z, z, z, z, i, i, p]
+        L.ref_gpu_quantize_group_s8.argtypes = [p, z, p, z, p, z, z, z, p]
+        L.ref_gpu_cublas_gemm.argtypes = [p, z, p, p, z, i, z, z, z, i, p]
+
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise RuntimeError(self.lib.ref_gpu_last_error().decode())
+
+    @staticmethod
+    def _stream() -> int:
+        import torch
+
+        return int(torch.cuda.current_stream().cuda_stream)
+
+    def gemm_nt(self, x, w, y_half: bool = False, accumulate: int = 0, flush_k: int = 0, config: int = -1, y=None):
+        """launch_gemm_nt: x [T, K], w [N, K] float16 CUDA tensors -> y [T, N] float32 (or float16)."""
+        import torch
+
+        t, k = x.shape
+        n = w.shape[0]
+        if y is None:
+            y = torch.empty((t, n), dtype=torch.float16 if y_half else torch.float32, device=x.device)
+        self._check(self.lib.ref_gpu_gemm_nt(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), y.data_ptr(), y.stride(0), int(y_half), t, n, k,
+                                             accumulate, flush_k, config, self._stream()))
+        return y
+
+    def cublas(self, x, w, y_half: bool = False, compute16: bool = False, y=None):
+        """cublasGemmEx as the reference's engine calls it (COMPUTE_32F, or COMPUTE_16F with a float16 result)."""
+        import torch
+
+        t, k = x.shape
+        n = w.shape[0]
+        assert w.is_contiguous()
+        if y is None:
+            y = torch.empty((t, n), dtype=torch.float16 if (y_half or compute16) else torch.float32, device=x.device)
+        self._check(self.lib.ref_gpu_cublas_gemm(x.data_ptr(), x.stride(0), w.data_ptr(), y.data_ptr(), y.stride(0), int(y.dtype == torch.float16), t, n, k,
+                                                 int(compute16), self._stream()))
+        return y
+
+    def quantize_group_s8(self, w32):
+        """launch_quantize_group_s8: float32 [N, K] -> (int8 [N, K], float32 [N, K / 128])."""
+        import torch
+
+        n, k = w32.shape
+        q = torch.empty((n, k), dtype=torch.int8, device=w32.device)
+        s = torch.empty((n, k // 128), dtype=torch.float32, device=w32.device)
+        self._check(self.lib.ref_gpu_quantize_group_s8(w32.data_ptr(), w32.stride(0), q.data_ptr(), k, s.data_ptr(), k // 128, n, k, self._stream()))
+        return q, s
+
+    def gemm_simt(self, x32, w, scales=None, kind: int = 2, epilogue: int = 0, config: int = -1, y=None):
+        """launch_gemm_simt: x float32 [T, K]; w int8 [N, K] with scales [N, K / 128] (kind 2), or float32 (kind 0). y float32, in place for Add."""
+        import torch
+
+        t, k = x32.shape
+        n = w.shape[0]
+        if y is None:
+            y = torch.zeros((t, n // 2 if epilogue == 2 else n), dtype=torch.float32, device=x32.device)
+        self._check(self.lib.ref_gpu_gemm_simt(x32.data_ptr(), x32.stride(0), w.data_ptr(), w.stride(0), scales.data_ptr() if scales is not None else None,
+                                               scales.stride(0) if scales is not None else 0, kind, y.data_ptr(), y.stride(0), t, n, k, epilogue, config,
+                                               self._stream()))
+        return y
+
+    def quantize_weights_s8(self, w16, pairs: bool):
+        """launch_quantize_weights_s8: float16 [N, K] -> (int8 [N, K] in the Plain or Fp16Pairs layout, float32 [N])."""
+        import torch
+
+        n, k = w16.shape
+        q = torch.empty((n, k), dtype=torch.int8, device=w16.device)
+        s = torch.empty((n,), dtype=torch.float32, device=w16.device)
+        self._check(self.lib.ref_gpu_quantize_weights_s8(w16.data_ptr(), w16.stride(0), q.data_ptr(), s.data_ptr(), n, k, 1 if pairs else 0, self._stream()))
+        return q, s
+
+    def gemm_w8a16(self, x, wq_pairs, sw, y_half: bool = False, config: int = -1):
+        """launch_gemm_w8a16: x float16 [T, K], wq int8 [N, K] in the Fp16Pairs layout, sw float32 [N]."""
+        import torch
+
+        t, k = x.shape
+        n = wq_pairs.shape[0]
+        y = torch.empty((t, n), dtype=torch.float16 if y_half else torch.float32, device=x.device)
+        self._check(self.lib.ref_gpu_gemm_w8a16(x.data_ptr(), x.stride(0), wq_pairs.data_ptr(), wq_pairs.stride(0), sw.data_ptr(), y.data_ptr(), y.stride(0),
+                                                int(y_half), t, n, k, config, self._stream()))
+        return y

@@ -14,7 +14,13 @@ A step is one batch of `calls_per_step` independent products of that shape (as m
 ring of operand sets whose total size exceeds the 126 MB L2, so no timed launch finds its operands in cache. `value` is the
 whole-job TFLOP/s with operands resident in HBM; `e2e` is the same metric through the host-pointer provider (pinned host X in,
 float32 Y out, copies inside the timed region). With N > 1 (torchrun, one rank per GPU) every GPU holds its own replica and runs the
-same steps (requests shard whole, no collective on the data path); time is the max over ranks.
+same steps (requests shard whole, no collective on the data path); time is the max over ranks. The default 512 calls a step make
+the timed region of the driver's 20 steps longer than half a second: the GPU then runs under its power cap, so `roofline.frac` is
+taken against the SUSTAINED measured peak (`roofline.peak_source` says which; `frac_of_burst` is the same time against the burst
+peak). Further keys of the default line: `gpu_baseline` (the reference's own GPU kernels and its cuBLAS call, compiled for sm_100
+into oracle/_ref, timed on the same box by the reference probe's method; outside the timed region), `shapes` (every named trunk GEMM
+with operands from HBM and hot in the L2), `trunk` (whole passes) and `serve` (the request-sharded sweep of configs[4] on the N GPUs
+of this run, with each rank's clock so that runs at different N can be compared at equal clock).
 
 `--impl reference` times the reference's own CPU implementation of the same product (its cpu-bf16 packed GEMM compiled from its
 sources into oracle/_ref, on all host cores it takes) on the same metric.
@@ -222,7 +228,10 @@ def run_ours(args):
     elapsed_ms, e2e_ms = float(times[0]), float(times[1])
 
     peaks, peak_kind = measured_peaks()
-    peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    burst_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    sustained_tf = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    long_region = elapsed_ms >= 250.0  # a quarter of a second of back-to-back GEMMs runs under the power cap, like the sustained peak's loop
+    peak_tf = sustained_tf if long_region else burst_tf
     total_calls = args.steps * calls
     per_call_ms = elapsed_ms / total_calls
     tflops_gpu = flops_call / (per_call_ms * 1e-3) / 1e12
@@ -246,7 +255,8 @@ def run_ours(args):
             "workload": f"{args.workload} (BASELINE configs[{cfg_index}]): M={m} K={k} N={n}",
             "calls_per_step": calls,
             "l2": f"ring of {len(sets)} operand sets, {ring_bytes >> 20} MiB > 126 MiB L2: every launch reads its operands from HBM",
-            "prefill_tokens_per_s": round(m * total_calls / (elapsed_ms * 1e-3) * world, 1),
+            "gemm_rows_per_s": round(m * total_calls / (elapsed_ms * 1e-3) * world, 1),
+            "timed_region_ms": round(elapsed_ms, 1),
             "parallelism": f"request-sharded x{world}, full replica per GPU, no collective",
         },
         "roofline": {
@@ -255,7 +265,9 @@ def run_ours(args):
             "peak": peak_tf,
             "unit": "TFLOP/s",
             "frac": round(tflops_gpu / peak_tf, 4),
-            "peak_source": f"bf16_tflops of MEASURED_PEAKS.json ({peak_kind}; burst: the kernel is timed alone)",
+            "frac_of_burst": round(tflops_gpu / burst_tf, 4),
+            "peak_source": (f"bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_kind}; the timed region is {elapsed_ms:.0f} ms of back-to-back launches: under the power cap)"
+                            if long_region else f"bf16_tflops of MEASURED_PEAKS.json ({peak_kind}; burst: a timed region of {elapsed_ms:.0f} ms)"),
             "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC.get(args.workload),
             "traffic_source": "--traffic" if args.traffic is not None else ("profiles/gemm_w8_pair_kernel_w8g_down_m900.md" if NCU_TRAFFIC.get(args.workload) else None),
             "algorithmic_bytes": algorithmic_bytes(kind, m, n, k),
@@ -265,34 +277,65 @@ def run_ours(args):
         "e2e": {
             "value": round(e2e_value, 3),
             "unit": "TFLOP/s",
-            "h2d_bytes_per_step": m * k * 2 * calls,
-            "d2h_bytes_per_step": m * n * 4 * calls,
-            "note": f"sepal_b200_provider_gemm_f, pinned host buffers, {e2e_steps * e2e_calls} calls timed by wall clock around a device sync",
+            "h2d_bytes_per_step": m * k * 2 * e2e_calls,
+            "d2h_bytes_per_step": m * n * 4 * e2e_calls,
+            "calls_per_step": e2e_calls,
+            "steps": e2e_steps,
+            "note": f"sepal_b200_provider_gemm_f, pinned host buffers, {e2e_steps} steps of {e2e_calls} calls timed by wall clock around a device sync; "
+                    "a call's rows go in four pieces whose upload, multiply and download overlap",
         },
         "gpu_launches": int(launches),
         "clocks": sampler.summary(),
     }
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(kind, m, n, k)
+    if rank == 0 and world == 1 and args.gpu_baseline:
+        line["gpu_baseline"] = gpu_baseline(ctx, device)
     if rank == 0 and world == 1 and args.shapes:
-        line["shapes"] = shape_table(ctx, device, peak_tf)
-    if rank == 0 and world == 1 and args.trunk:
-        prov.close()
-        ctx.close()
-        torch.cuda.empty_cache()
-        line["trunk"] = trunk_numbers(local, float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])))
-    if rank == 0:
-        print(json.dumps(line), flush=True)
+        line["shapes"] = shape_table(ctx, device, burst_tf)
     prov.close()
     ctx.close()
+    del sets
+    torch.cuda.empty_cache()
+    if rank == 0 and world == 1 and args.trunk:
+        line["trunk"] = trunk_numbers(local, sustained_tf)
+        line["config"]["prefill_tokens_per_s_per_gpu"] = line["trunk"]["f16"]["log_15900"]["tokens_per_s"]
+    if args.serve:
+        serve = serve_sweep(local, rank, world, int8=False, passes=3)  # every rank takes part; rank 0 gets the summary
+        if rank == 0:
+            line["serve"] = serve
+    if rank == 0:
+        print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
 
         dist.destroy_process_group()
 
 
+def probe_time_ms(fn, reps: int = 10, batches: int = 3) -> float:
+    """Minimum over `batches` of the mean time of `reps` back-to-back calls (the reference probe's method, gemm_probe.cpp:69-89)."""
+    import torch
+
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    best = None
+    for _ in range(batches):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        best = ms if best is None else min(best, ms)
+    return best
+
+
 def shape_table(ctx, device, peak_tf):
-    """TFLOP/s of every named trunk GEMM at M = 900 and M = 4096, fp16 and int8-group weights, with the fused epilogues."""
+    """TFLOP/s of every named trunk GEMM at M = 900 and M = 4096, fp16 and int8-group weights, with the fused epilogues. `us` /
+    `tflops` / `frac_of_peak`: consecutive launches rotate over copies of the operands that together exceed the L2 (every launch reads
+    from HBM, as in the trunk, where 7 GB of weights pass between two uses of a matrix); `us_hot_l2`: one operand set, relaunched."""
     import torch
 
     import sepal_runner_b200 as sb
@@ -302,34 +345,84 @@ def shape_table(ctx, device, peak_tf):
     for m in (900, 4096):
         for name, n, k, ep in TRUNK_SHAPES:
             epi = {"store": sb.STORE, "add": sb.ADD, "swiglu": sb.SWIGLU}[ep]
-            x = torch.randn((m, k), generator=gen, device=device).half()
-            w = (torch.randn((n, k), generator=gen, device=device) * 0.02).half()
             n_out = n // 2 if ep == "swiglu" else n
-            y = torch.zeros((m, n_out), dtype=torch.float32 if ep == "add" else torch.float16, device=device)
-            variants = [("f16", lambda: ctx.gemm_f16(x, w, y, epilogue=epi))]
+            per_set = m * k * 2 + n * k * 2 + m * n_out * (4 if ep == "add" else 2)
+            copies = max(2, -(-int(1.25 * L2_BYTES) // per_set))
+            xs = [torch.randn((m, k), generator=gen, device=device).half() for _ in range(copies)]
+            ws = [(torch.randn((n, k), generator=gen, device=device) * 0.02).half() for _ in range(copies)]
+            ys = [torch.zeros((m, n_out), dtype=torch.float32 if ep == "add" else torch.float16, device=device) for _ in range(copies)]
+            variants = [("f16", lambda i: ctx.gemm_f16(xs[i], ws[i], ys[i], epilogue=epi))]
             if k % 128 == 0:
-                q, s = ctx.quantize_group_s8(w.float())
-                wq = ctx.prepare_w8g(q, s)
-                variants.append(("w8g", lambda: ctx.gemm_w8g(x, wq, y, epilogue=epi)))
+                wqs = []
+                for w in ws:
+                    q, s = ctx.quantize_group_s8(w.float())
+                    wqs.append(ctx.prepare_w8g(q, s))
+                variants.append(("w8g", lambda i: ctx.gemm_w8g(xs[i], wqs[i], ys[i], epilogue=epi)))
             for vname, fn in variants:
-                for _ in range(3):
-                    fn()
-                torch.cuda.synchronize()
-                best = None
-                for _ in range(3):  # min over 3 batches of back-to-back launches (the reference's probe method, gemm_probe.cpp:69-89)
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    e0.record()
-                    for _ in range(10):
-                        fn()
-                    e1.record()
-                    torch.cuda.synchronize()
-                    ms = e0.elapsed_time(e1) / 10
-                    best = ms if best is None else min(best, ms)
-                tf = 2.0 * m * n * k / (best * 1e-3) / 1e12
-                rows.append({"gemm": name, "weights": vname, "m": m, "n": n, "k": k, "us": round(best * 1e3, 1), "tflops": round(tf, 1),
-                             "frac_of_peak": round(tf / peak_tf, 3)})
+                turn = [0]
+
+                def rotating():
+                    fn(turn[0] % copies)
+                    turn[0] += 1
+
+                cold = probe_time_ms(rotating)
+                hot = probe_time_ms(lambda: fn(0))
+                tf = 2.0 * m * n * k / (cold * 1e-3) / 1e12
+                rows.append({"gemm": name, "weights": vname, "m": m, "n": n, "k": k, "us": round(cold * 1e3, 1), "tflops": round(tf, 1),
+                             "frac_of_peak": round(tf / peak_tf, 3), "us_hot_l2": round(hot * 1e3, 1), "operand_copies": copies})
+            del xs, ws, ys
+    # the entry point that allocates nothing, on one shape (the o projection at M = 900: 80 tiles of 128 x 256 ... split evenly over the SMs)
+    m, n, k = 900, 2560, 4096
+    x = torch.randn((m, k), generator=gen, device=device).half()
+    w = (torch.randn((n, k), generator=gen, device=device) * 0.02).half()
+    y = torch.zeros((m, n), dtype=torch.float16, device=device)
+    ms = probe_time_ms(lambda: sb.gemm_f16_noalloc(x, w, y, wait=False))
+    tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    rows.append({"gemm": "o (sepal_b200_gemm_f16_noalloc)", "weights": "f16", "m": m, "n": n, "k": k, "us_hot_l2": round(ms * 1e3, 1),
+                 "tflops": round(tf, 1), "frac_of_peak": round(tf / peak_tf, 3)})
     ctx.check_status()
     return rows
+
+
+def gpu_baseline(ctx, device):
+    """The reference's own GPU code on this box, on identical buffers: its kernels launch_gemm_nt (float32 accumulation),
+    launch_gemm_w8a16 and launch_gemm_simt (Int8Group), compiled unmodified for sm_100, and cublasGemmEx as its engine calls it
+    (COMPUTE_32F and COMPUTE_16F), next to this repository's kernels. Timed by the reference probe's method (minimum over three
+    batches of back-to-back launches, runner/cuda/tools/gemm_probe.cpp:69-89), operands hot in the L2 for every row alike."""
+    import torch
+
+    from oracle.oracle import RefGpu
+
+    if not RefGpu.available():
+        return {"unavailable": "oracle/_ref/libsepal_ref_gpu.so was not built (the reference tree was absent at build time)"}
+    r = RefGpu()
+    out = []
+    gen = torch.Generator(device=device).manual_seed(1001)
+    for label, m, n, k in (("w8g_down_m900", 900, 2560, 9728), ("f16_up_m900", 900, 9728, 2560), ("f16_up_m4096", 4096, 9728, 2560)):
+        flops = 2.0 * m * n * k
+        reps = 8 if flops > 2e10 else 20  # the probe's reps_for
+        x = torch.randn((m, k), generator=gen, device=device).bfloat16().half()
+        w = (torch.randn((n, k), generator=gen, device=device) * 0.02).bfloat16().half()
+        y32 = torch.empty((m, n), dtype=torch.float32, device=device)
+        y16 = torch.empty((m, n), dtype=torch.float16, device=device)
+        q, s = ctx.quantize_group_s8(w.float())
+        wq = ctx.prepare_w8g(q, s)
+        q_pairs, sw = r.quantize_weights_s8(w, pairs=True)
+        x32 = x.float()
+        row = {"shape": label, "m": m, "n": n, "k": k, "tflops": {}}
+
+        def tf(fn, reps=reps):
+            return round(flops / (probe_time_ms(fn, reps=reps) * 1e-3) / 1e12, 1)
+
+        row["tflops"]["sepal_b200_gemm_f16"] = tf(lambda: ctx.gemm_f16(x, w, y16))
+        row["tflops"]["sepal_b200_gemm_w8g"] = tf(lambda: ctx.gemm_w8g(x, wq, y16))
+        row["tflops"]["reference cublasGemmEx COMPUTE_32F"] = tf(lambda: r.cublas(x, w, y=y16))
+        row["tflops"]["reference cublasGemmEx COMPUTE_16F"] = tf(lambda: r.cublas(x, w, compute16=True, y=y16))
+        row["tflops"]["reference launch_gemm_nt Float32"] = tf(lambda: r.gemm_nt(x, w, y=y16, y_half=True))
+        row["tflops"]["reference launch_gemm_w8a16"] = tf(lambda: r.gemm_w8a16(x, q_pairs, sw, y_half=True))
+        row["tflops"]["reference launch_gemm_simt Int8Group"] = tf(lambda: r.gemm_simt(x32, q, s, y=y32), reps=3)
+        out.append(row)
+    return {"method": "min over 3 batches of back-to-back launches (CUDA events), operands hot in the L2", "rows": out}
 
 
 def trunk_numbers(local, peak_tf):
@@ -368,34 +461,25 @@ def trunk_numbers(local, peak_tf):
     return out
 
 
-def run_serve(args):
-    """BASELINE configs[4]: request-sharded serving sweep. Every rank holds a full replica; requests are dealt whole, longest first,
-    each to the GPU with the least work so far; all requests arrive at time zero, so a request's latency is its completion time."""
+def serve_sweep(local, rank, world, int8: bool, passes: int):
+    """BASELINE configs[4] on the GPUs of this run: 64 requests of 600-1200 tokens and 4 of 15,900 through the 36-layer trunk, every rank
+    holding a full replica, requests dealt whole, longest first, each to the GPU with the least work so far; all requests arrive at
+    time zero, so a request's latency is its completion time (queue + compute, as runner/cuda/tools/gpu_bench.cpp:54-58 defines it).
+    Every rank calls this; rank 0 gets the summary, the others None. Needs the process group when world > 1."""
     import numpy as np
     import torch
 
     import sepal_runner_b200 as sb
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    torch.cuda.set_device(local)
-    rng = np.random.default_rng(5005)
-    lengths = [int(v) for v in rng.integers(600, 1201, 64)] + [15900] * 4
     from sepal_runner_b200.sharding import deal_requests, ideal_speedup
 
+    rng = np.random.default_rng(5005)
+    lengths = [int(v) for v in rng.integers(600, 1201, 64)] + [15900] * 4
     mine = deal_requests(lengths, world)[rank]
-    trunk = sb.Trunk(local, sb.TrunkConfig(mlp_int8=1 if args.int8 else 0))
+    trunk = sb.Trunk(local, sb.TrunkConfig(mlp_int8=1 if int8 else 0))
     tok_rng = np.random.default_rng(4004 + rank)
     requests = {i: tok_rng.integers(0, 151936, lengths[i]).astype(np.uint32) for i in mine}
     for i in mine[:1]:
         trunk.run(requests[i][:900])  # warm up: first launches, kernel attributes
-    sampler = ClockSampler(local)
-    sampler.start()
 
     def barrier():
         if world > 1:
@@ -407,39 +491,89 @@ def run_serve(args):
     # Short requests first: they share calls of up to 4096 rows (sepal_b200_trunk_score packs them as the reference's engine does), and
     # the long logs, four calls each, follow. A request's latency is the time until its call has finished on the device.
     mine = sorted(mine, key=lambda i: lengths[i])
-    passes = []
-    for _ in range(max(1, args.steps if args.steps <= 5 else 3)):
+    sb.Context.take_launch_count()
+    results = []
+    for _ in range(max(1, passes)):
+        sampler = ClockSampler(local)
+        sampler.start()
         barrier()
         t0 = time.perf_counter()
         _, done = trunk.score([requests[i] for i in mine])
         span = time.perf_counter() - t0
+        sampler.stop_flag.set()
+        sampler.join(timeout=2)
         lat = {i: float(done[j]) for j, i in enumerate(mine)}
         dev_ms = float(done.max()) * 1e3 if len(mine) else 0.0
         barrier()
-        passes.append((span, lat, dev_ms))
-    sampler.stop_flag.set()
-    sampler.join(timeout=2)
-    span, lat, dev_ms = min(passes, key=lambda p: p[0])
+        results.append((span, lat, dev_ms, sampler.summary()))
+    launches = int(sb.Context.take_launch_count())
+    flops_tok = trunk.gemm_flops_per_token
+    trunk.close()
+    span, lat, dev_ms, clocks = min(results, key=lambda p: p[0])
+    mine_summary = (span, lat, dev_ms, len(mine), sum(lengths[i] for i in mine), clocks)
     if world > 1:
         import torch.distributed as dist
 
         gathered = [None] * world
-        dist.all_gather_object(gathered, (span, lat, dev_ms, len(mine), sum(lengths[i] for i in mine)))
+        dist.all_gather_object(gathered, mine_summary)
     else:
-        gathered = [(span, lat, dev_ms, len(mine), sum(lengths[i] for i in mine))]
+        gathered = [mine_summary]
+    if rank != 0:
+        return None
+    makespan = max(g[0] for g in gathered)
+    all_lat = sorted(v for g in gathered for v in g[1].values())
+    total = sum(lengths)
+    # The same work at every rank's maximum clock: a rank that sat at a lower clock under the power cap would have finished sooner.
+    at_max = [g[0] * (g[5]["sm_mhz"] / g[5]["sm_max_mhz"]) if g[5].get("sm_mhz") and g[5].get("sm_max_mhz") else g[0] for g in gathered]
+    return {
+        "workload": "serve (BASELINE configs[4]): 64 requests of 600-1200 tokens + 4 of 15900, whole requests per GPU (dealt longest first), packed into calls of up to 4096 rows",
+        "weights": "int8-group MLP" if int8 else "fp16",
+        "n_gpus": world,
+        "tokens_per_s": round(total / makespan, 1),
+        "tokens_per_s_at_max_clock": round(total / max(at_max), 1),
+        "makespan_s": round(makespan, 4),
+        "total_tokens": total,
+        "ideal_speedup_over_1_gpu": round(ideal_speedup(lengths, world), 3),
+        "p50_latency_s": round(all_lat[len(all_lat) // 2], 4),
+        "p95_latency_s": round(all_lat[min(len(all_lat) - 1, int(0.95 * len(all_lat)))], 4),
+        "per_gpu": [{"requests": g[3], "tokens": g[4], "span_s": round(g[0], 4), "device_s": round(g[2] / 1e3, 4), "sm_mhz": g[5].get("sm_mhz"),
+                     "sm_max_mhz": g[5].get("sm_max_mhz"), "reasons": g[5].get("reasons")} for g in gathered],
+        "passes": len(results),
+        "gemm_flops_per_token": flops_tok,
+        "gpu_launches": launches,
+        "note": "speed-up between runs at different N: divide their tokens_per_s_at_max_clock (span x median SM clock / maximum clock per rank, "
+                "slowest rank), so that a run that sat lower under the power cap is not flattered or punished",
+    }
+
+
+def run_serve(args):
+    """`--workload serve`: the request-sharded sweep of BASELINE configs[4] as the line's own metric."""
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    sampler = ClockSampler(local)
+    sampler.start()
+    serve = serve_sweep(local, rank, world, args.int8, max(1, args.steps if args.steps <= 5 else 3))
+    sampler.stop_flag.set()
+    sampler.join(timeout=2)
     if rank == 0:
-        makespan = max(g[0] for g in gathered)
-        all_lat = sorted(v for g in gathered for v in g[1].values())
-        total = sum(lengths)
+        total, makespan = serve["total_tokens"], serve["makespan_s"]
         peaks, peak_kind = measured_peaks()
         peak_tf = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
-        flops = trunk.gemm_flops_per_token * total
+        flops = serve["gemm_flops_per_token"] * total
         line = {
             "metric": "prefill tokens/s (request-sharded, 36-layer GEMM-chain trunk)",
-            "value": round(total / makespan, 1),
+            "value": serve["tokens_per_s"],
             "unit": "tokens/s",
             "n_gpus": world,
-            "steps": len(passes),
+            "steps": serve["passes"],
             "warmup": 1,
             "ms_per_step": round(makespan * 1e3, 3),
             "higher_is_better": True,
@@ -447,21 +581,19 @@ def run_serve(args):
             "vs_baseline": None,
             "dtype": "f16 x int8-group MLP" if args.int8 else "f16 x f16 -> f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": "serve (BASELINE configs[4]): 64 requests of 600-1200 tokens + 4 of 15900, whole requests per GPU (dealt longest first), packed into calls of up to 4096 rows",
-                       "total_tokens": total, "ideal_speedup_over_1_gpu": round(ideal_speedup(lengths, world), 3), "p50_latency_s": round(all_lat[len(all_lat) // 2], 4),
-                       "p95_latency_s": round(all_lat[min(len(all_lat) - 1, int(0.95 * len(all_lat)))], 4),
-                       "per_gpu": [{"requests": g[3], "tokens": g[4], "span_s": round(g[0], 4), "device_s": round(g[2] / 1e3, 4)} for g in gathered],
+            "config": {"workload": serve["workload"], "total_tokens": total, "ideal_speedup_over_1_gpu": serve["ideal_speedup_over_1_gpu"],
+                       "p50_latency_s": serve["p50_latency_s"], "p95_latency_s": serve["p95_latency_s"], "per_gpu": serve["per_gpu"],
+                       "tokens_per_s_at_max_clock": serve["tokens_per_s_at_max_clock"],
                        "l2": "weights 7.3 GB per replica: far larger than the L2", "parallelism": f"request-sharded x{world}, full replica per GPU, no collective"},
             "roofline": {"bound": "tensor", "achieved": round(flops / makespan / 1e12 / world, 1), "peak": peak_tf, "unit": "TFLOP/s",
                          "frac": round(flops / makespan / 1e12 / world / peak_tf, 4),
                          "peak_source": f"bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_kind}; the GEMMs run inside a long step)", "traffic": None},
-            "e2e": {"value": round(total / makespan, 1), "unit": "tokens/s", "h2d_bytes_per_step": total * 4, "d2h_bytes_per_step": len(lengths) * 2560 * 4,
+            "e2e": {"value": serve["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": total * 4, "d2h_bytes_per_step": 68 * 2560 * 4,
                     "note": "the same number: sepal_b200_trunk_score takes host token ids and returns the last hidden states to the host"},
-            "gpu_launches": int(sb.Context.take_launch_count()),
+            "gpu_launches": serve["gpu_launches"],
             "clocks": sampler.summary(),
         }
         print(json.dumps(line), flush=True)
-    trunk.close()
     if world > 1:
         import torch.distributed as dist
 
@@ -698,9 +830,11 @@ def main():
     ap.add_argument("--heads128", action="store_true", help="attention: 32 / 8 heads of 128 instead of 16 / 4 heads of 256")
     ap.add_argument("--int8", action="store_true", help="serve: store the MLP weights as int8 groups")
     ap.add_argument("--no-trunk", dest="trunk", action="store_false", help="skip the whole-trunk passes")
-    ap.add_argument("--calls-per-step", type=int, default=32)
+    ap.add_argument("--calls-per-step", type=int, default=512)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-shapes", dest="shapes", action="store_false", help="skip the per-shape table")
+    ap.add_argument("--no-serve", dest="serve", action="store_false", help="skip the request-sharded sweep appended to the default line")
+    ap.add_argument("--no-gpu-baseline", dest="gpu_baseline", action="store_false", help="skip the reference's GPU kernels / cuBLAS leg")
     ap.add_argument("--traffic", type=float, default=None, help="DRAM bytes per launch from an ncu capture (reported as roofline.traffic)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -328,7 +328,8 @@ SEPAL_B200_API int32_t sepal_b200_trunk_score(sepal_b200_trunk* trunk, uint64_t 
                                               float* last_hidden, double* times_s);
 /* Copies a stored weight to the host (size-query protocol: host_out NULL only reports *needed). which: 0 embedding, 1 input norm,
  * 2 mixer in-projection, 3 mixer out-projection, 4 post norm, 5 packed [gate; up], 6 down, 7 / 8 the attention core's q / k head norms,
- * 9 .. 12 the DeltaNet core's convolution, A_log, dt_bias and norm weight. */
+ * 9 .. 12 the DeltaNet core's convolution, A_log, dt_bias and norm weight, 13 / 14 (int8 MLP only) the group quantiser's float32 scales of
+ * [gate; up] and down, [rows, k / 128]. */
 SEPAL_B200_API int32_t sepal_b200_trunk_weight(sepal_b200_trunk* trunk, uint32_t layer, int32_t which, void* host_out, uint64_t capacity,
                                                uint64_t* needed);
 SEPAL_B200_API int32_t sepal_b200_trunk_info(sepal_b200_trunk* trunk, uint64_t* gemm_flops_per_token, uint64_t* weight_bytes);

@@ -19,6 +19,7 @@ from .lib import (  # noqa: F401
     DeltaNetRow,
     DeltaNetShape,
     deltanet,
+    gemm_f16_noalloc,
     Provider,
     SepalB200Error,
     Trunk,

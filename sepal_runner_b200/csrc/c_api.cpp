@@ -487,7 +487,7 @@ int32_t sepal_b200_trunk_score(sepal_b200_trunk* trunk, uint64_t n_requests, con
 int32_t sepal_b200_trunk_weight(sepal_b200_trunk* trunk, uint32_t layer, int32_t which, void* host_out, uint64_t capacity, uint64_t* needed) {
     return guarded([&] {
         require(trunk, "trunk");
-        if (which < 0 || which > 12) throw std::invalid_argument("which must be 0 .. 12");
+        if (which < 0 || which > 14) throw std::invalid_argument("which must be 0 .. 14");
         const std::size_t bytes = trunk->trunk.weight(layer, static_cast<TrunkWeight>(which), host_out, capacity);
         if (needed != nullptr) *needed = bytes;
     });

@@ -1,5 +1,6 @@
 #include "provider.hpp"
 
+#include <initializer_list>
 #include <stdexcept>
 #include <string>
 
@@ -25,15 +26,25 @@ B200Gemm::B200Gemm(int device, std::size_t arena_bytes) : ctx_(device, 0) {
     arena_bytes_ = arena_bytes != 0 ? arena_bytes : (std::size_t{1} << 30);
     check(cudaSetDevice(device), "cudaSetDevice");
     check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+    check(cudaStreamCreateWithFlags(&stream_in_, cudaStreamNonBlocking), "cudaStreamCreate");
+    check(cudaStreamCreateWithFlags(&stream_out_, cudaStreamNonBlocking), "cudaStreamCreate");
+    for (cudaEvent_t& e : uploaded_) check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+    for (cudaEvent_t& e : multiplied_) check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
     check(cudaMalloc(reinterpret_cast<void**>(&arena_), arena_bytes_), "cudaMalloc(arena)");
 }
 
 B200Gemm::~B200Gemm() {
     (void)cudaSetDevice(ctx_.device);
-    if (stream_ != nullptr) {
-        (void)cudaStreamSynchronize(stream_);
-        (void)cudaStreamDestroy(stream_);
+    for (cudaStream_t s : {stream_in_, stream_, stream_out_}) {
+        if (s != nullptr) {
+            (void)cudaStreamSynchronize(s);
+            (void)cudaStreamDestroy(s);
+        }
     }
+    for (cudaEvent_t e : uploaded_)
+        if (e != nullptr) (void)cudaEventDestroy(e);
+    for (cudaEvent_t e : multiplied_)
+        if (e != nullptr) (void)cudaEventDestroy(e);
     if (arena_ != nullptr) (void)cudaFree(arena_);
 }
 
@@ -115,46 +126,70 @@ WeightId B200Gemm::upload_weights_w8g(const float* w, std::size_t n, std::size_t
 }
 
 void B200Gemm::gemm_f(const void* x, HostType type, std::size_t t, WeightId id, float* y, float beta) {
-    if (!id.valid() || id.index >= weights_.size()) throw std::invalid_argument("gemm_f: unknown weight id");
-    if (t == 0) return;
+    if (t == 0) {
+        std::lock_guard<std::mutex> lock(mutex_);
+        if (!id.valid() || id.index >= weights_.size()) throw std::invalid_argument("gemm_f: unknown weight id");
+        return;
+    }
     if (x == nullptr || y == nullptr) throw std::invalid_argument("gemm_f: null data pointer");
     std::lock_guard<std::mutex> lock(mutex_);
+    if (!id.valid() || id.index >= weights_.size()) throw std::invalid_argument("gemm_f: unknown weight id");
     check(cudaSetDevice(ctx_.device), "cudaSetDevice");
     const Weight& w = weights_[id.index];
     std::size_t top = arena_bytes_;
-    void* dx = scratch(t * w.k * 2, top);
+    char* dx = static_cast<char*>(scratch(t * w.k * 2, top));
     float* dy = static_cast<float*>(scratch(t * w.n * 4, top));
-    if (type == HostType::F16) {
-        check(cudaMemcpyAsync(dx, x, t * w.k * 2, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(X)");
-    } else {
-        float* tmp = static_cast<float*>(scratch(t * w.k * 4, top));
-        check(cudaMemcpyAsync(tmp, x, t * w.k * 4, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(X)");
-        launch_float_to_half(tmp, dx, t * w.k, stream_);
-    }
-    Epilogue ep = Epilogue::Store;
-    if (beta != 0.0f) {
-        check(cudaMemcpyAsync(dy, y, t * w.n * 4, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(Y)");
-        if (beta != 1.0f) {
-            const std::size_t count = t * w.n;
-            scale_rows_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream_>>>(dy, count, beta);
-            check(cudaGetLastError(), "scale_rows_kernel launch");
-            count_launch();
+    float* tmp = type == HostType::F16 ? nullptr : static_cast<float*>(scratch(t * w.k * 4, top));
+    // The rows of a large call go through in up to kChunks pieces on three streams, so that the upload of piece i + 1, the multiply of
+    // piece i and the download of piece i - 1 run at the same time (the bus carries both directions at once). The multiplies of all
+    // pieces run on one stream, one after another: they share the context's split-k scratch.
+    constexpr std::size_t kChunks = 4, kMinChunk = 256;
+    std::size_t pieces = t / kMinChunk;
+    pieces = pieces < 1 ? 1 : (pieces > kChunks ? kChunks : pieces);
+    const std::size_t rows_per = ((t + pieces - 1) / pieces + 127) / 128 * 128;
+    const std::size_t x_elem = type == HostType::F16 ? 2 : 4;
+    std::size_t piece = 0;
+    for (std::size_t r0 = 0; r0 < t; r0 += rows_per, ++piece) {
+        const std::size_t rows = t - r0 < rows_per ? t - r0 : rows_per;
+        const char* hx = static_cast<const char*>(x) + r0 * w.k * x_elem;
+        char* dxp = dx + r0 * w.k * 2;
+        float* dyp = dy + r0 * w.n;
+        float* hy = y + r0 * w.n;
+        if (type == HostType::F16)
+            check(cudaMemcpyAsync(dxp, hx, rows * w.k * 2, cudaMemcpyHostToDevice, stream_in_), "cudaMemcpyAsync(X)");
+        else
+            check(cudaMemcpyAsync(tmp + r0 * w.k, hx, rows * w.k * 4, cudaMemcpyHostToDevice, stream_in_), "cudaMemcpyAsync(X)");
+        if (beta != 0.0f) check(cudaMemcpyAsync(dyp, hy, rows * w.n * 4, cudaMemcpyHostToDevice, stream_in_), "cudaMemcpyAsync(Y)");
+        check(cudaEventRecord(uploaded_[piece], stream_in_), "cudaEventRecord");
+        check(cudaStreamWaitEvent(stream_, uploaded_[piece], 0), "cudaStreamWaitEvent");
+        if (type != HostType::F16) launch_float_to_half(tmp + r0 * w.k, dxp, rows * w.k, stream_);
+        Epilogue ep = Epilogue::Store;
+        if (beta != 0.0f) {
+            if (beta != 1.0f) {
+                const std::size_t count = rows * w.n;
+                scale_rows_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream_>>>(dyp, count, beta);
+                check(cudaGetLastError(), "scale_rows_kernel launch");
+                count_launch();
+            }
+            ep = Epilogue::Add;
         }
-        ep = Epilogue::Add;
+        if (w.w8g) {
+            W8gMatrix m;
+            m.q = static_cast<const std::int8_t*>(w.data);
+            m.ld_q = w.k;
+            m.scales_t = w.scales_t;
+            m.ld_st = (w.n + 255) / 256 * 256;
+            m.descale = w.descale;
+            launch_gemm_w8g(ctx_, dxp, w.k, m, dyp, w.n, false, rows, w.n, w.k, ep, -1, stream_);
+        } else {
+            launch_gemm_f16(ctx_, dxp, w.k, w.data, w.k, dyp, w.n, false, rows, w.n, w.k, ep, -1, stream_);
+        }
+        check(cudaEventRecord(multiplied_[piece], stream_), "cudaEventRecord");
+        check(cudaStreamWaitEvent(stream_out_, multiplied_[piece], 0), "cudaStreamWaitEvent");
+        check(cudaMemcpyAsync(hy, dyp, rows * w.n * 4, cudaMemcpyDeviceToHost, stream_out_), "cudaMemcpyAsync(Y)");
     }
-    if (w.w8g) {
-        W8gMatrix m;
-        m.q = static_cast<const std::int8_t*>(w.data);
-        m.ld_q = w.k;
-        m.scales_t = w.scales_t;
-        m.ld_st = (w.n + 255) / 256 * 256;
-        m.descale = w.descale;
-        launch_gemm_w8g(ctx_, dx, w.k, m, dy, w.n, false, t, w.n, w.k, ep, -1, stream_);
-    } else {
-        launch_gemm_f16(ctx_, dx, w.k, w.data, w.k, dy, w.n, false, t, w.n, w.k, ep, -1, stream_);
-    }
-    check(cudaMemcpyAsync(y, dy, t * w.n * 4, cudaMemcpyDeviceToHost, stream_), "cudaMemcpyAsync(Y)");
-    const int status = ctx_.read_status(stream_);  // waits for the stream
+    const int status = ctx_.read_status(stream_);  // waits for the multiplies
+    check(cudaStreamSynchronize(stream_out_), "cudaStreamSynchronize");
     if (status != 0) throw std::runtime_error("sepal_b200 provider: a kernel gave up waiting (status " + std::to_string(status) + ")");
 }
 

@@ -33,7 +33,8 @@ public:
     /// W float32 [N, K] on the host -> int8 groups + prepared scales on the device (K a multiple of 128).
     WeightId upload_weights_w8g(const float* w, std::size_t n, std::size_t k);
     /// Y [T, N] float32 (host) = beta Y + X [T, K] (host) W^T. Returns when Y is complete. Throws std::runtime_error when a kernel
-    /// reported a wait that ran out.
+    /// reported a wait that ran out. Calls of 512 rows and more are cut into up to four pieces of rows whose upload, multiply and
+    /// download overlap (a piece is a product of its own, so a row's float32 sum may be rounded differently than in the uncut product).
     void gemm_f(const void* x, HostType type, std::size_t t, WeightId w, float* y, float beta);
 
     Context& context() { return ctx_; }
@@ -51,7 +52,9 @@ private:
     void* scratch(std::size_t bytes, std::size_t& top);  // from the top: the caller resets `top` when done
 
     Context ctx_;
-    cudaStream_t stream_ = nullptr;
+    cudaStream_t stream_ = nullptr;                          // the multiplies (and the weight uploads)
+    cudaStream_t stream_in_ = nullptr, stream_out_ = nullptr;  // a call's uploads and downloads, overlapped with its multiplies
+    cudaEvent_t uploaded_[4] = {}, multiplied_[4] = {};        // one pair per piece of a call
     unsigned char* arena_ = nullptr;
     std::size_t arena_bytes_ = 0, resident_ = 0;
     std::vector<Weight> weights_;

@@ -555,6 +555,8 @@ std::size_t Trunk::weight(std::uint32_t layer, TrunkWeight which, void* host_out
         case TrunkWeight::DnALog: src = L.dn_a_log; bytes = L.dn_a_log != nullptr ? static_cast<std::size_t>(c.dn_value_heads) * 4 : 0; break;
         case TrunkWeight::DnDtBias: src = L.dn_dt_bias; bytes = L.dn_dt_bias != nullptr ? static_cast<std::size_t>(c.dn_value_heads) * 4 : 0; break;
         case TrunkWeight::DnNorm: src = L.dn_norm; bytes = L.dn_norm != nullptr ? 128 * 4 : 0; break;
+        case TrunkWeight::GateUpScales: src = L.gate_up_scales; bytes = L.gate_up_scales != nullptr ? 2 * I * (H / kGroup) * 4 : 0; break;
+        case TrunkWeight::DownScales: src = L.down_scales; bytes = L.down_scales != nullptr ? H * (I / kGroup) * 4 : 0; break;
         default: throw std::invalid_argument("sepal_b200 trunk: no such weight");
         }
     }

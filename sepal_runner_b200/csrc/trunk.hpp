@@ -51,7 +51,8 @@ struct TrunkConfig {
 /// The value of the "format" metadata key of a file written by Trunk::save.
 extern const char* const kSavedFormat;
 
-enum class TrunkWeight : int { Embedding = 0, NormIn = 1, MixIn = 2, MixOut = 3, NormPost = 4, GateUp = 5, Down = 6, QNorm = 7, KNorm = 8, DnConv = 9, DnALog = 10, DnDtBias = 11, DnNorm = 12 };
+enum class TrunkWeight : int { Embedding = 0, NormIn = 1, MixIn = 2, MixOut = 3, NormPost = 4, GateUp = 5, Down = 6, QNorm = 7, KNorm = 8, DnConv = 9, DnALog = 10, DnDtBias = 11, DnNorm = 12,
+                               GateUpScales = 13, DownScales = 14 };  // mlp_int8: the quantiser's float32 scales, [rows, k / 128]
 
 class Trunk {
 public:

@@ -365,7 +365,7 @@ class Trunk:
     """The synthetic GEMM-chain trunk (sepal_b200_trunk_*): whole requests of host token ids in, final hidden states out."""
 
     WEIGHTS = {"embedding": 0, "norm_in": 1, "mix_in": 2, "mix_out": 3, "norm_post": 4, "gate_up": 5, "down": 6, "q_norm": 7, "k_norm": 8, "dn_conv": 9, "dn_a_log": 10,
-               "dn_dt_bias": 11, "dn_norm": 12}
+               "dn_dt_bias": 11, "dn_norm": 12, "gate_up_scales": 13, "down_scales": 14}
 
     def __init__(self, device: int = 0, config: Optional[TrunkConfig] = None, checkpoint: "Optional[Checkpoint]" = None) -> None:
         self._lib = library()
@@ -428,7 +428,7 @@ class Trunk:
         code = self.WEIGHTS[which]
         needed = _u64()
         _check(self._lib.sepal_b200_trunk_weight(self._h, layer, code, None, 0, C.byref(needed)))
-        is_norm = code in (1, 4, 7, 8, 9, 10, 11, 12)
+        is_norm = code in (1, 4, 7, 8, 9, 10, 11, 12, 13, 14)  # float32 arrays
         int8 = self.config.mlp_int8 and code in (5, 6)
         out = np.empty(needed.value // (4 if is_norm else 1 if int8 else 2), np.float32 if is_norm else np.int8 if int8 else np.float16)
         _check(self._lib.sepal_b200_trunk_weight(self._h, layer, code, out.ctypes.data, needed.value, C.byref(needed)))

@@ -58,95 +58,106 @@ __global__ void embed_kernel(const __half* table, const std::uint32_t* tokens, f
     }
 }
 
-// The zero-centred RMSNorm with the reference's arithmetic and order of summation (runner/cuda/src/kernels_elementwise.cu:6-11,114-141):
-// a row is cut into chunks of four consecutive elements; chunk c belongs to thread c mod 256 of the row's block; a thread adds the
-// squares of its chunks in ascending order with one fused multiply-add per element; each warp sums its 32 partial sums by a butterfly
-// and the eight warp sums are added in order. rms = sqrt(sum / width + eps); y = (x / rms) * (1 + w), every step rounded to float32, the
-// result to binary16. A row's bits therefore depend on nothing but the row. Rows up to 4096 wide are read from memory once.
-constexpr unsigned kNormThreads = 256;
-constexpr int kNormHeld = 4;
+// The zero-centred RMSNorm, y = (x / rms) * (1 + w) with rms = sqrt(mean(x^2) + eps), every step rounded to float32 and the result to
+// binary16. The sum of squares must come out bit for bit as the reference's kernel forms it (runner/cuda/src/kernels_elementwise.cu:6-11,
+// 114-141), because a row's bits may depend on nothing but the row: the row in chunks of four consecutive elements, chunk c added (one
+// fused multiply-add per element, ascending c) into partial sum number c mod 256; each run of 32 partial sums folded by a butterfly
+// (p[l] += p[l ^ o], o = 16, 8, 4, 2, 1); the eight results added in order.
+//
+// Here ONE WARP owns a row (eight rows to a block, no shared memory, no block barrier): lane l keeps the eight partial sums l, 32 + l,
+// ..., 224 + l, visits the chunks l, 32 + l, 64 + l, ... in ascending order (chunk l + 32 i goes to its partial sum i mod 8, which is
+// partial sum number (l + 32 i) mod 256), folds each of the eight across the lanes with the same butterfly and adds them in order. The
+// chunks a lane has seen stay in registers for the second pass (rows up to 3072 wide are read from memory once).
+constexpr unsigned kNormWarps = 8;
+constexpr unsigned kNormThreads = 32 * kNormWarps;
+constexpr int kNormSums = 8;   // partial sums per lane: 8 x 32 lanes = the 256 of the order above
+constexpr int kNormHeld = 24;  // chunks per lane kept in registers (a multiple of kNormSums)
+static_assert(kNormHeld % kNormSums == 0, "the unrolled loops map chunk i of a lane to partial sum i mod 8");
 
-__device__ __forceinline__ float add_squares(float acc, const float4& v) {
-    acc = __fmaf_rn(v.x, v.x, acc);
-    acc = __fmaf_rn(v.y, v.y, acc);
-    acc = __fmaf_rn(v.z, v.z, acc);
-    return __fmaf_rn(v.w, v.w, acc);
+__device__ __forceinline__ float square_into(float sum, const float4& v) {
+    return __fmaf_rn(v.w, v.w, __fmaf_rn(v.z, v.z, __fmaf_rn(v.y, v.y, __fmaf_rn(v.x, v.x, sum))));
 }
 
-__device__ __forceinline__ float norm_block_sum(float partial, float* warp_sums) {
-    for (int o = 16; o > 0; o >>= 1) partial += __shfl_xor_sync(0xFFFFFFFFu, partial, o);
-    if (threadIdx.x % 32 == 0) warp_sums[threadIdx.x / 32] = partial;
-    __syncthreads();
-    float total = warp_sums[0];
-    for (unsigned w = 1; w < kNormThreads / 32; ++w) total += warp_sums[w];
-    return total;
-}
-
-__device__ __forceinline__ void store_normed(__half* yr, std::size_t c, const float4& v, float rms, const float* w) {
-    const float4 g = *reinterpret_cast<const float4*>(w + 4 * c);
+__device__ __forceinline__ uint2 normed_chunk(const float4& v, float rms, const float4& g) {
     const __half2 lo = __floats2half2_rn(__fmul_rn(__fdiv_rn(v.x, rms), __fadd_rn(1.0f, g.x)), __fmul_rn(__fdiv_rn(v.y, rms), __fadd_rn(1.0f, g.y)));
     const __half2 hi = __floats2half2_rn(__fmul_rn(__fdiv_rn(v.z, rms), __fadd_rn(1.0f, g.z)), __fmul_rn(__fdiv_rn(v.w, rms), __fadd_rn(1.0f, g.w)));
-    uint2 packed;
-    packed.x = *reinterpret_cast<const unsigned*>(&lo);
-    packed.y = *reinterpret_cast<const unsigned*>(&hi);
-    *reinterpret_cast<uint2*>(yr + 4 * c) = packed;
+    return make_uint2(*reinterpret_cast<const unsigned*>(&lo), *reinterpret_cast<const unsigned*>(&hi));
 }
 
-// `Load` yields chunk c of the row as four floats (from the float32 stream, or from the binary16 embedding table, written to the stream
-// on the way).
-template <class Load>
-__device__ __forceinline__ void norm_row(Load&& load, const float* w, __half* yr, std::size_t cols, float eps) {
-    __shared__ float warp_sums[kNormThreads / 32];
+// `fetch(c)` yields chunk c of the warp's row as four floats (from the float32 stream, or widened from the binary16 embedding table and
+// written to the stream on the way). All 32 lanes call this.
+template <class Fetch>
+__device__ __forceinline__ void norm_row_in_a_warp(Fetch&& fetch, const float* w, __half* yr, std::size_t cols, float eps) {
+    const unsigned lane = threadIdx.x % 32;
     const std::size_t chunks = cols / 4;
     float4 held[kNormHeld];
-    float partial = 0.0f;
+    float sums[kNormSums];
+#pragma unroll
+    for (int s = 0; s < kNormSums; ++s) sums[s] = 0.0f;
 #pragma unroll
     for (int i = 0; i < kNormHeld; ++i) {
-        const std::size_t c = threadIdx.x + static_cast<std::size_t>(i) * kNormThreads;
+        const std::size_t c = lane + 32u * static_cast<std::size_t>(i);
         if (c < chunks) {
-            held[i] = load(c);
-            partial = add_squares(partial, held[i]);
+            held[i] = fetch(c);
+            sums[i % kNormSums] = square_into(sums[i % kNormSums], held[i]);
         }
     }
-    for (std::size_t c = threadIdx.x + static_cast<std::size_t>(kNormHeld) * kNormThreads; c < chunks; c += kNormThreads) partial = add_squares(partial, load(c));
-    const float total = norm_block_sum(partial, warp_sums);
+    for (std::size_t i0 = kNormHeld; lane + 32u * i0 < chunks; i0 += kNormSums) {  // wider rows: eight chunks a turn, so the sum's index stays static
+#pragma unroll
+        for (int s = 0; s < kNormSums; ++s) {
+            const std::size_t c = lane + 32u * (i0 + s);
+            if (c < chunks) sums[s] = square_into(sums[s], fetch(c));
+        }
+    }
+#pragma unroll
+    for (int s = 0; s < kNormSums; ++s)
+        for (int o = 16; o > 0; o >>= 1) sums[s] += __shfl_xor_sync(0xFFFFFFFFu, sums[s], o);
+    float total = sums[0];
+#pragma unroll
+    for (int s = 1; s < kNormSums; ++s) total += sums[s];
     const float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(total, static_cast<float>(cols)), eps));
+    const float4* gain = reinterpret_cast<const float4*>(w);
+    uint2* out = reinterpret_cast<uint2*>(yr);
 #pragma unroll
     for (int i = 0; i < kNormHeld; ++i) {
-        const std::size_t c = threadIdx.x + static_cast<std::size_t>(i) * kNormThreads;
-        if (c < chunks) store_normed(yr, c, held[i], rms, w);
+        const std::size_t c = lane + 32u * static_cast<std::size_t>(i);
+        if (c < chunks) out[c] = normed_chunk(held[i], rms, gain[c]);
     }
-    for (std::size_t c = threadIdx.x + static_cast<std::size_t>(kNormHeld) * kNormThreads; c < chunks; c += kNormThreads) store_normed(yr, c, load(c), rms, w);
+    for (std::size_t c = lane + 32u * static_cast<std::size_t>(kNormHeld); c < chunks; c += 32) out[c] = normed_chunk(fetch(c), rms, gain[c]);
 }
 
 __global__ void __launch_bounds__(kNormThreads) rms_norm_half_kernel(const float* x, std::size_t ld_x, const float* w, __half* y, std::size_t ld_y,
-                                                                      std::size_t cols, float eps) {
+                                                                      std::size_t rows, std::size_t cols, float eps) {
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();  // x is the output of the multiply launched before this kernel
-    const float* xr = x + static_cast<std::size_t>(blockIdx.x) * ld_x;
-    norm_row([&](std::size_t c) { return *reinterpret_cast<const float4*>(xr + 4 * c); }, w, y + static_cast<std::size_t>(blockIdx.x) * ld_y, cols, eps);
+    const std::size_t row = static_cast<std::size_t>(blockIdx.x) * kNormWarps + threadIdx.x / 32;
+    if (row >= rows) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + row * ld_x);
+    norm_row_in_a_warp([&](std::size_t c) { return xr[c]; }, w, y + row * ld_y, cols, eps);
 }
 
 // The embedding gather and the first layer's input norm in one pass (the reference runs launch_embed and launch_rms_norm back to back,
 // runner/cuda/src/cuda_engine.cpp:1676-1692): the row of the binary16 table is widened (exactly) to the float32 stream and normed from
 // the registers (a row wider than the registers hold is widened a second time for the second pass).
 __global__ void __launch_bounds__(kNormThreads) embed_rms_norm_half_kernel(const __half* table, const std::uint32_t* tokens, float* x, const float* w, __half* y,
-                                                                            std::size_t ld_y, std::size_t hidden, std::size_t vocab, float eps) {
+                                                                            std::size_t ld_y, std::size_t rows, std::size_t hidden, std::size_t vocab, float eps) {
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();  // the kernel before this one may still read the rows this one overwrites
-    std::size_t id = tokens[blockIdx.x];
+    const std::size_t row = static_cast<std::size_t>(blockIdx.x) * kNormWarps + threadIdx.x / 32;
+    if (row >= rows) return;
+    std::size_t id = tokens[row];
     if (id >= vocab) id = vocab - 1;  // the host checks the ids; never read outside the table
-    const __half* src = table + id * hidden;
-    float* xr = x + static_cast<std::size_t>(blockIdx.x) * hidden;
-    norm_row(
+    const uint2* src = reinterpret_cast<const uint2*>(table + id * hidden);
+    float4* xr = reinterpret_cast<float4*>(x + row * hidden);
+    norm_row_in_a_warp(
         [&](std::size_t c) {
-            const uint2 raw = *reinterpret_cast<const uint2*>(src + 4 * c);
+            const uint2 raw = src[c];
             const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
             const float4 v = make_float4(a.x, a.y, b.x, b.y);
-            *reinterpret_cast<float4*>(xr + 4 * c) = v;  // written twice with the same value when the row is wider than the registers hold
+            xr[c] = v;  // written twice with the same value when the row is wider than the registers hold
             return v;
         },
-        w, y + static_cast<std::size_t>(blockIdx.x) * ld_y, hidden, eps);
+        w, y + row * ld_y, hidden, eps);
 }
 
 unsigned blocks_for(std::size_t n, unsigned per) { return static_cast<unsigned>((n + per - 1) / per); }
@@ -165,8 +176,8 @@ void launch_embed_rms_norm_half(const void* table_half, const std::uint32_t* tok
                                 std::size_t hidden, std::size_t vocab, float eps, cudaStream_t stream) {
     if (hidden % 8 != 0 || ld_y % 4 != 0) throw std::invalid_argument("launch_embed_rms_norm_half: the hidden size must be a multiple of 8 and the stride of y of 4");
     if (rows == 0) return;
-    launch_kernel(embed_rms_norm_half_kernel, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, stream, "embed_rms_norm_half_kernel launch",
-                  static_cast<const __half*>(table_half), tokens, x, w, static_cast<__half*>(y_half), ld_y, hidden, vocab, eps);
+    launch_kernel(embed_rms_norm_half_kernel, dim3(blocks_for(rows, kNormWarps)), dim3(kNormThreads), 0, stream, "embed_rms_norm_half_kernel launch",
+                  static_cast<const __half*>(table_half), tokens, x, w, static_cast<__half*>(y_half), ld_y, rows, hidden, vocab, eps);
     count_launch();
 }
 
@@ -174,8 +185,8 @@ void launch_rms_norm_half(const float* x, std::size_t ld_x, const float* w, void
                           cudaStream_t stream) {
     if (cols % 4 != 0 || ld_x % 4 != 0 || ld_y % 4 != 0) throw std::invalid_argument("launch_rms_norm_half: columns and strides must be multiples of 4");
     if (rows == 0) return;
-    launch_kernel(rms_norm_half_kernel, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), 0, stream, "rms_norm_half_kernel launch", x, ld_x, w,
-                  static_cast<__half*>(y_half), ld_y, cols, eps);
+    launch_kernel(rms_norm_half_kernel, dim3(blocks_for(rows, kNormWarps)), dim3(kNormThreads), 0, stream, "rms_norm_half_kernel launch", x, ld_x, w,
+                  static_cast<__half*>(y_half), ld_y, rows, cols, eps);
     count_launch();
 }
 

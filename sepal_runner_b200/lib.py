@@ -39,6 +39,7 @@ SIGNATURES = {
     "sepal_b200_info": (_i32, [_vp, C.c_char_p, _u64, C.POINTER(_u64)]),
     "sepal_b200_status": (_i32, [_vp, _vp, C.POINTER(_i32)]),
     "sepal_b200_take_launch_count": (_u64, []),
+    "sepal_b200_debug_leave_status": (_i32, [_vp, _vp, _i32, _u32]),
     "sepal_b200_gemm_f16": (_i32, [_vp, _vp, _u64, _vp, _u64, _vp, _u64, _i32, _u64, _u64, _u64, _i32, _i32, _vp]),
     "sepal_b200_gemm_f16_noalloc": (_i32, [_vp, _u64, _vp, _u64, _vp, _u64, _i32, _u64, _u64, _u64, _i32, _vp, C.POINTER(_i32)]),
     "sepal_b200_gemm_w8g": (_i32, [_vp, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _vp, _u64, _i32, _u64, _u64, _u64, _i32, _i32, _vp]),
@@ -160,6 +161,10 @@ class Context:
         _check(self._lib.sepal_b200_status(self._h, _stream_ptr(stream), C.byref(out)))
         return out.value
 
+    def debug_leave_status(self, code: int, stale_counters: int = 0, stream=None) -> None:
+        """Leaves the context as a kernel that gave up waiting would (sepal_b200_debug_leave_status): for tests of the recovery path."""
+        _check(self._lib.sepal_b200_debug_leave_status(self._h, _stream_ptr(stream), code, stale_counters))
+
     def check_status(self, stream=None) -> None:
         st = self.status(stream)
         if st != 0:
@@ -168,10 +173,16 @@ class Context:
     # ---- launchers -------------------------------------------------------------------------------------------------------
     @staticmethod
     def _out(x, n_out: int, y, y_half: bool):
+        """The output tensor: a new one, or the caller's after checking that the C ABI (which only sees a pointer and a row stride) would
+        write inside it: [T, n_out], float16 or float32, on x's device, last dimension contiguous."""
         import torch
 
         if y is None:
-            y = torch.empty((x.shape[0], n_out), dtype=torch.float16 if y_half else torch.float32, device=x.device)
+            return torch.empty((x.shape[0], n_out), dtype=torch.float16 if y_half else torch.float32, device=x.device)
+        if tuple(y.shape) != (x.shape[0], n_out):
+            raise ValueError(f"the output must be [{x.shape[0]}, {n_out}], not {tuple(y.shape)}")
+        if y.dtype not in (torch.float16, torch.float32) or y.device != x.device or (y.numel() > 0 and y.stride(-1) != 1):
+            raise ValueError("the output must be float16 or float32, on the input's device, with a contiguous last dimension")
         return y
 
     def gemm_f16(self, x, w, y=None, *, epilogue: int = STORE, y_half: bool = True, config: int = -1, stream=None):
@@ -181,6 +192,8 @@ class Context:
         assert x.dtype == torch.float16 and w.dtype == torch.float16 and x.stride(-1) == 1 and w.stride(-1) == 1
         t, k = x.shape
         n = w.shape[0]
+        if w.shape[1] != k or w.device != x.device:
+            raise ValueError(f"x is [{t}, {k}] but w is {tuple(w.shape)} on {w.device}: the inner dimensions and the devices must agree")
         if y is not None:
             y_half = y.dtype == torch.float16
         y = self._out(x, n // 2 if epilogue == SWIGLU else n, y, y_half)
@@ -222,6 +235,8 @@ class Context:
         assert x.dtype == torch.float16 and x.stride(-1) == 1
         t, k = x.shape
         n = w.q.shape[0]
+        if w.q.shape[1] != k or w.q.device != x.device:
+            raise ValueError(f"x is [{t}, {k}] but the weights are {tuple(w.q.shape)} on {w.q.device}: the inner dimensions and the devices must agree")
         if y is not None:
             y_half = y.dtype == torch.float16
         y = self._out(x, n // 2 if epilogue == SWIGLU else n, y, y_half)
@@ -251,6 +266,8 @@ class Context:
         assert x.dtype == torch.float16 and x.stride(-1) == 1 and q.dtype == torch.int8 and q.stride(-1) == 1 and sw.dtype == torch.float32
         t, k = x.shape
         n = q.shape[0]
+        if q.shape[1] != k or sw.numel() != n or q.device != x.device or sw.device != x.device:
+            raise ValueError(f"x is [{t}, {k}], q is {tuple(q.shape)}, sw has {sw.numel()} scales: the shapes and the devices must agree")
         if y is not None:
             y_half = y.dtype == torch.float16
         y = self._out(x, n // 2 if epilogue == SWIGLU else n, y, y_half)
@@ -614,9 +631,12 @@ def gemm_f16_noalloc(x, w, y, *, epilogue: int = STORE, stream=None, wait: bool 
     device allocation inside the library. Returns the kernel status word when `wait` (0 = fine), else 0 right after enqueueing."""
     import torch
 
-    assert x.dtype == torch.float16 and w.dtype == torch.float16 and x.stride(-1) == 1 and w.stride(-1) == 1 and y.stride(-1) == 1
+    assert x.dtype == torch.float16 and w.dtype == torch.float16 and x.stride(-1) == 1 and w.stride(-1) == 1
     t, k = x.shape
     n = w.shape[0]
+    if w.shape[1] != k or w.device != x.device:
+        raise ValueError(f"x is [{t}, {k}] but w is {tuple(w.shape)} on {w.device}: the inner dimensions and the devices must agree")
+    Context._out(x, n // 2 if epilogue == SWIGLU else n, y, y.dtype == torch.float16)
     status = _i32(0)
     _check(library().sepal_b200_gemm_f16_noalloc(x.data_ptr(), x.stride(0) if t > 1 else max(x.stride(0), k), w.data_ptr(),
                                                  w.stride(0) if n > 1 else max(w.stride(0), k), y.data_ptr(), y.stride(0) if t > 1 else y.shape[1],

@@ -569,3 +569,28 @@ def test_split_schedules_are_deterministic_over_many_launches(ctx, oracle):
             for _ in range(50):
                 assert torch.equal(call(), first)
             ctx.check_status()
+
+
+def test_status_path_after_a_give_up(ctx, oracle):
+    """What follows a kernel that gave up waiting, without making one give up: the context is left as such a kernel would leave it (a
+    status code, stale tile counters), sepal_b200_status reports the code once and clears both, and the next split launches (which
+    count arrivals on those counters) are bit-equal to launches on a clean context."""
+    import torch
+
+    import sepal_runner_b200 as sb
+
+    x, w = make(oracle, 77, 900, 2560, 1024)
+    xd, wd = dev(x).half(), dev(w).half()
+    clean = {c: ctx.gemm_f16(xd, wd, y_half=False, config=c) for c in (1, 3, 259)}
+    ctx.check_status()
+    code = 2 | (37 << 8)  # "the MMA issuer's wait for an operand stage ran out, in CTA 37"
+    ctx.debug_leave_status(code, stale_counters=64)
+    assert ctx.status() == code
+    assert ctx.status() == 0  # read once, then clear
+    for c, want in clean.items():
+        assert torch.equal(ctx.gemm_f16(xd, wd, y_half=False, config=c), want), c
+    ctx.check_status()
+    with pytest.raises(sb.SepalB200Error, match="wait 2, CTA 37"):
+        ctx.debug_leave_status(code)
+        ctx.check_status()
+    ctx.check_status()

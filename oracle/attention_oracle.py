@@ -4,8 +4,10 @@
 tokens 0..t; hidden keys get probability exactly 0), the per-head rms_norm of ref/primitives.hpp:57-69 with the "1 + weight" form, and
 the output gate sigmoid of attention_mixer (:176-231). Test infrastructure: only tests/ and the smoke check import it.
 
-Parity unpinned against a run of the reference here: the reference holds no stored vectors for this core (its tests compare its CUDA
-kernels with this same C++ template code on seeded inputs), and its template code is not built into oracle/_ref."""
+Pinned to the reference: oracle/_ref/libsepal_ref.so binds the reference's own template code for this mixer (ref_attention_core in
+oracle/ref_shim.cpp); tests/test_attention_oracle.py holds this restatement to it within 1e-12, on the committed vectors
+tests/golden/golden_mixers.npz (generated from that library by tests/golden/make_golden.py) and, where the library is built, on fresh
+seeded inputs."""
 import numpy as np
 
 

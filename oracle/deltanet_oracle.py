@@ -5,8 +5,10 @@ share_key_heads (:98-113: value head h reads key head h // (value heads // key h
 (:163-184: decay first, then S += k (x) beta (v - k . S)), delta_rule_scan (:204-232: a token reads the state after its own update, the
 read scaled by 1 / sqrt(dk)), gated_rms_norm (:236-263: the norm weight itself, gate silu(z)). Test infrastructure only.
 
-Parity unpinned against a run of the reference here: the reference's tests compare its CUDA kernels with this same C++ template code on
-seeded inputs and hold no stored vectors for this core."""
+Pinned to the reference: oracle/_ref/libsepal_ref.so binds the reference's own template code for this mixer (ref_deltanet_core in
+oracle/ref_shim.cpp); tests/test_deltanet_oracle.py holds this restatement to it within 1e-12, on the committed vectors
+tests/golden/golden_mixers.npz (generated from that library by tests/golden/make_golden.py) and, where the library is built, on fresh
+seeded inputs, state and convolution tail carried across a cut included."""
 import numpy as np
 
 

@@ -218,6 +218,11 @@ class Ref:
         L.ref_gemm_f64acc.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, _sz, _sz, _sz, _f32p, C.c_float]
         L.ref_rmsnorm_rows.restype = C.c_int
         L.ref_rmsnorm_rows.argtypes = [C.c_uint, _f32p, _sz, _f32p, _sz, _sz, _sz, _f32p, C.c_double]
+        d, u = C.c_double, C.c_uint
+        L.ref_attention_core.restype = C.c_int
+        L.ref_attention_core.argtypes = [_f64p, _f64p, _f64p, _f64p, _f64p, _f64p, _sz, _f64p, _f64p, _sz, u, u, u, u, d, d, _f64p, _f64p, _f64p]
+        L.ref_deltanet_core.restype = C.c_int
+        L.ref_deltanet_core.argtypes = [_f64p] * 10 + [_sz, u, u, u, u, u, d, _f64p, _f64p, _f64p]
 
     def _check(self, rc: int) -> None:
         if rc != 0:
@@ -264,6 +269,38 @@ class Ref:
         y = np.zeros_like(x)
         self._check(self.lib.ref_rmsnorm_rows(threads, x, x.shape[1], y, x.shape[1], x.shape[0], x.shape[1], w1, eps))
         return y
+
+    def attention_core(self, q_gate, k, v, q_norm, k_norm, positions, heads, kv_heads, head_dim, rotary_dims, theta, eps, ctx_keys=None, ctx_values=None):
+        """The reference's attention mixer between its projections (float64 template code). -> (gated output [T, heads * hd], this run's
+        keys [T, kvh, hd] (normed, rotated), values [T, kvh, hd]). ctx_keys / ctx_values [C, kvh, hd]: the tokens before this run."""
+        f = lambda a: np.ascontiguousarray(a, np.float64)
+        q_gate, k, v = f(q_gate), f(k), f(v)
+        t = q_gate.shape[0]
+        context = 0 if ctx_keys is None else int(np.shape(ctx_keys)[0])
+        ck = f(ctx_keys).reshape(-1) if context else np.zeros(1)
+        cv = f(ctx_values).reshape(-1) if context else np.zeros(1)
+        out = np.zeros((t, heads * head_dim))
+        keys = np.zeros((t, kv_heads, head_dim))
+        values = np.zeros((t, kv_heads, head_dim))
+        self._check(self.lib.ref_attention_core(q_gate, k, v, f(q_norm), f(k_norm), f(positions), t, ck, cv, context, heads, kv_heads, head_dim, rotary_dims,
+                                                float(theta), float(eps), out, keys.reshape(-1), values.reshape(-1)))
+        return out, keys, values
+
+    def deltanet_core(self, mixed, z, b, a, conv, a_log, dt_bias, norm, key_heads, value_heads, dim, eps, state=None, tail=None):
+        """The reference's Gated DeltaNet mixer between its projections (float64 template code), heads of `dim` for keys and values.
+        -> (out [T, value_heads * dim], state [value_heads, dim, dim], tail [taps - 1, conv_dim])."""
+        f = lambda x: np.ascontiguousarray(x, np.float64)
+        mixed, conv = f(mixed), f(conv)
+        t, conv_dim = mixed.shape
+        taps = conv.shape[1]
+        state = np.zeros((value_heads, dim, dim)) if state is None else f(state)
+        tail = np.zeros((taps - 1, conv_dim)) if tail is None else f(tail)
+        out = np.zeros((t, value_heads * dim))
+        state_out, tail_out = np.zeros_like(state), np.zeros_like(tail)
+        self._check(self.lib.ref_deltanet_core(mixed.reshape(-1), f(z).reshape(-1), f(b).reshape(-1), f(a).reshape(-1), conv.reshape(-1), f(a_log), f(dt_bias), f(norm),
+                                               state.reshape(-1), tail.reshape(-1) if tail.size else np.zeros(1), t, key_heads, value_heads, dim, dim, taps, float(eps),
+                                               out.reshape(-1), state_out.reshape(-1), tail_out.reshape(-1) if tail_out.size else np.zeros(1)))
+        return out, state_out, tail_out
 
     def time_gemm(self, x, w, kind: str = "bf16", isa: str = "", threads: int = 0, reps: int = 5):
         """(pack seconds, product seconds) per repeat, weights packed once, as the reference's own bench times it."""

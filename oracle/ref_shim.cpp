@@ -11,6 +11,11 @@
 //   make_reference_gemm()->gemm_f (float64 accumulation)        runner/include/sepal/gemm.hpp:44-73
 //   rmsnorm_rows                                                 runner/include/sepal/cpu/elementwise.hpp:13-16
 //   float_to_bf16                                                runner/include/sepal/cpu/gemm.hpp:49
+//   the attention mixer between its projections                  runner/include/sepal/ref/attention.hpp:33-231 (unpack_query_and_gate,
+//       rope_angles, apply_rope, grouped_query_attention; rms_norm and sigmoid of ref/primitives.hpp), composed below in the order of
+//       attention_mixer (:176-231) with the four projections left out
+//   the Gated DeltaNet mixer between its projections             runner/include/sepal/ref/deltanet.hpp:41-330 (causal_conv, split_heads,
+//       l2_normalise, share_key_heads, decay_gate, delta_rule_scan, gated_rms_norm), composed in the order of deltanet_mixer (:246-279)
 #include <chrono>
 #include <cstdint>
 #include <cstring>
@@ -23,6 +28,8 @@
 #include "sepal/cpu/isa.hpp"
 #include "sepal/cpu/thread_pool.hpp"
 #include "sepal/gemm.hpp"
+#include "sepal/ref/attention.hpp"
+#include "sepal/ref/deltanet.hpp"
 
 using namespace sepal;
 using namespace sepal::cpu;
@@ -164,6 +171,97 @@ int ref_gemm_f64acc(const void* x, int x_dtype, const void* w, int w_dtype, std:
 int ref_rmsnorm_rows(unsigned threads, const float* x, std::size_t ldx, float* y, std::size_t ldy, std::size_t rows, std::size_t cols, const float* w1,
                      double eps) {
     return guarded([&] { rmsnorm_rows(x, ldx, y, ldy, rows, cols, w1, eps, *pool_for(threads).pool); });
+}
+
+
+/// The full-attention mixer between q/k/v_proj and o_proj in float64, by the reference's own template functions. q_gate [T, 2 heads hd]
+/// (per head: query, then gate), k and v [T, kv_heads hd], positions [T]; ctx_keys / ctx_values [context, kv_heads, hd]: the keys
+/// (already normed and rotated) and values of the tokens before this run (context may be 0). Writes the gated output [T, heads hd] and
+/// this run's own keys and values [T, kv_heads, hd] (what a cache would append).
+int ref_attention_core(const double* q_gate, const double* k, const double* v, const double* q_norm, const double* k_norm, const double* positions,
+                       std::size_t tokens, const double* ctx_keys, const double* ctx_values, std::size_t context, unsigned heads, unsigned kv_heads,
+                       unsigned head_dim, unsigned rotary_dims, double theta, double eps, double* out, double* keys_out, double* values_out) {
+    return guarded([&] {
+        ModelConfig cfg;
+        cfg.attn_heads = heads;
+        cfg.attn_kv_heads = kv_heads;
+        cfg.attn_head_dim = head_dim;
+        cfg.rope_theta = theta;
+        cfg.partial_rotary_factor = static_cast<double>(rotary_dims) / static_cast<double>(head_dim);
+        cfg.rms_norm_eps = eps;
+        if (cfg.attn_rotary_dims() != rotary_dims) throw std::invalid_argument("ref_attention_core: the rotary dims do not survive the config's rounding");
+        const auto provider = make_reference_gemm();
+        const std::size_t kv_width = static_cast<std::size_t>(kv_heads) * head_dim;
+        const std::vector<std::size_t> kv_shape = {tokens, kv_heads, head_dim};
+        const ref::QueryAndGate<double> unpacked = ref::unpack_query_and_gate<double>(ConstMatViewD(q_gate, tokens, 2 * static_cast<std::size_t>(heads) * head_dim), cfg);
+        const TensorD angles = ref::rope_angles(std::span<const double>(positions, tokens), cfg);
+        TensorD q = ref::rms_norm<double>(unpacked.query.as_mat(head_dim), std::span<const double>(q_norm, head_dim), eps);
+        q.reshape({tokens, heads, head_dim});
+        ref::apply_rope(q, angles);
+        TensorD k_flat({tokens, kv_width});
+        std::copy(k, k + tokens * kv_width, k_flat.data());
+        TensorD kk = ref::rms_norm<double>(k_flat.as_mat(head_dim), std::span<const double>(k_norm, head_dim), eps);
+        kk.reshape(kv_shape);
+        ref::apply_rope(kk, angles);
+        TensorD vv(kv_shape);
+        std::copy(v, v + tokens * kv_width, vv.data());
+        std::copy(kk.data(), kk.data() + kk.size(), keys_out);
+        std::copy(vv.data(), vv.data() + vv.size(), values_out);
+        auto parent = std::make_shared<ref::AttentionState<double>>();
+        if (context != 0) {
+            parent->keys = TensorD({context, kv_heads, head_dim});
+            parent->values = TensorD({context, kv_heads, head_dim});
+            std::copy(ctx_keys, ctx_keys + context * kv_width, parent->keys.data());
+            std::copy(ctx_values, ctx_values + context * kv_width, parent->values.data());
+            parent->tokens = context;
+        }
+        ref::AttentionState<double> state;
+        if (context != 0) state.parent = parent;
+        state.keys = std::move(kk);
+        state.values = std::move(vv);
+        state.tokens = context + tokens;
+        TensorD attended = ref::grouped_query_attention(*provider, q, state, context, ref::attention_scale(cfg));
+        for (std::size_t i = 0; i < attended.size(); ++i) out[i] = attended[i] * ref::sigmoid(unpacked.gate[i]);
+    });
+}
+
+/// The Gated DeltaNet mixer between its in- and out-projections in float64, by the reference's own template functions. mixed [T, conv_dim]
+/// ([q; k] of the key heads, then v), z [T, value_dim], b and a [T, value_heads]; conv [conv_dim, taps]; state [value_heads, dk, dv] and
+/// tail [taps - 1, conv_dim] are read and the state after the run is written to state_out / tail_out. out [T, value_dim].
+int ref_deltanet_core(const double* mixed, const double* z, const double* b, const double* a, const double* conv, const double* a_log,
+                      const double* dt_bias, const double* norm, const double* state_in, const double* tail_in, std::size_t tokens, unsigned key_heads,
+                      unsigned value_heads, unsigned dk, unsigned dv, unsigned taps, double eps, double* out, double* state_out, double* tail_out) {
+    return guarded([&] {
+        ModelConfig cfg;
+        cfg.dn_key_heads = key_heads;
+        cfg.dn_value_heads = value_heads;
+        cfg.dn_key_head_dim = dk;
+        cfg.dn_value_head_dim = dv;
+        cfg.conv_kernel = taps;
+        cfg.rms_norm_eps = eps;
+        const std::size_t conv_dim = 2 * static_cast<std::size_t>(key_heads) * dk + static_cast<std::size_t>(value_heads) * dv;
+        const std::size_t value_dim = static_cast<std::size_t>(value_heads) * dv;
+        TensorD tail({static_cast<std::size_t>(taps) - 1, conv_dim});
+        std::copy(tail_in, tail_in + tail.size(), tail.data());
+        ref::ConvResult<double> c = ref::causal_conv<double>(ConstMatViewD(mixed, tokens, conv_dim), ConstMatViewD(conv, conv_dim, taps), tail.mat());
+        for (double& value : c.outputs.span()) value = ref::silu(value);
+        ref::SplitHeads<double> split = ref::split_heads<double>(c.outputs.mat(), cfg);
+        ref::l2_normalise(split.q.as_mat(dk));
+        ref::l2_normalise(split.k.as_mat(dk));
+        const TensorD q = ref::share_key_heads(split.q, cfg);
+        const TensorD kk = ref::share_key_heads(split.k, cfg);
+        const TensorD decay = ref::decay_gate<double>(ConstMatViewD(a, tokens, value_heads), std::span<const double>(a_log, value_heads),
+                                                      std::span<const double>(dt_bias, value_heads));
+        TensorD beta({tokens, value_heads});
+        for (std::size_t i = 0; i < beta.size(); ++i) beta[i] = ref::sigmoid(b[i]);
+        TensorD state({value_heads, dk, dv});
+        std::copy(state_in, state_in + state.size(), state.data());
+        ref::ScanResult<double> scan = ref::delta_rule_scan(q, kk, split.v, decay, beta, std::move(state), ref::delta_rule_output_scale(cfg));
+        const TensorD normed = ref::gated_rms_norm<double>(scan.reads.as_mat(dv), ConstMatViewD(z, tokens * value_heads, dv), std::span<const double>(norm, dv), eps);
+        std::copy(normed.data(), normed.data() + tokens * value_dim, out);
+        std::copy(scan.state.data(), scan.state.data() + scan.state.size(), state_out);
+        std::copy(c.tail.data(), c.tail.data() + c.tail.size(), tail_out);
+    });
 }
 
 } // extern "C"

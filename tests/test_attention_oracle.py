@@ -39,3 +39,47 @@ def test_norm_gate_packing_and_causal_grouping():
     out_c = ao.attend(q[2:], kk, vv, 2)
     assert np.allclose(out_c, out[2:])
     assert np.allclose(ao.gated(out, gate), out / (1 + np.exp(-gate)))
+
+
+def _golden_mixers():
+    import os
+
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_mixers.npz"))
+
+
+def test_pinned_to_the_reference_template_code():
+    """tests/golden/golden_mixers.npz was computed by the reference's own float64 attention mixer (unpack_query_and_gate, rms_norm,
+    rope_angles, apply_rope, grouped_query_attention, the sigmoid gate; oracle/ref_shim.cpp composes them as attention_mixer does):
+    a run from nothing, and the same tokens cut 7 + 4 with the second run attending to the first's keys and values."""
+    g = _golden_mixers()
+    heads, kvh, hd, rot = (int(v) for v in g["at_shape"])
+    theta, eps = (float(v) for v in g["at_theta"])
+    q, gate, kk, vv = ao.prepare(g["at_qg"], g["at_k"], g["at_v"], g["at_qn"], g["at_kn"], g["at_pos"], heads, kvh, hd, rot, theta, eps)
+    assert np.allclose(kk, g["at_keys"], rtol=0, atol=1e-12) and np.array_equal(vv, g["at_values"])
+    whole = ao.gated(ao.attend(q, kk, vv, 0), gate).reshape(len(g["at_pos"]), heads * hd)
+    assert np.allclose(whole, g["at_out"], rtol=0, atol=1e-12)
+    cut = ao.gated(ao.attend(q[7:], kk, vv, 7), gate[7:]).reshape(-1, heads * hd)  # the last 4 tokens over a context of 7
+    assert np.allclose(cut, g["at_out_cut"][7:], rtol=0, atol=1e-12)
+    assert np.allclose(g["at_out_cut"], g["at_out"], rtol=0, atol=1e-12)  # the reference itself: cutting a run changes nothing
+
+
+def test_agrees_with_the_reference_library_where_it_is_built():
+    """The same comparison on fresh seeded inputs against oracle/_ref (built only where the reference tree is present)."""
+    import pytest
+
+    from oracle.oracle import Ref
+
+    if not Ref.available():
+        pytest.skip("oracle/_ref/libsepal_ref.so is not built here")
+    r = Ref()
+    rng = np.random.default_rng(77)
+    for heads, kvh, hd, rot, t, ctx in ((2, 1, 8, 4, 9, 0), (6, 2, 16, 16, 5, 12), (4, 4, 32, 8, 17, 3)):
+        qg, k, v = rng.standard_normal((t, 2 * heads * hd)), rng.standard_normal((t, kvh * hd)), rng.standard_normal((t, kvh * hd))
+        qn, kn = rng.standard_normal(hd) * 0.2, rng.standard_normal(hd) * 0.2
+        ck, cv = rng.standard_normal((ctx, kvh, hd)), rng.standard_normal((ctx, kvh, hd))
+        pos = np.arange(ctx, ctx + t, dtype=np.float64)
+        want, keys, values = r.attention_core(qg, k, v, qn, kn, pos, heads, kvh, hd, rot, 1.0e6, 1e-6, ctx_keys=ck if ctx else None, ctx_values=cv if ctx else None)
+        q, gate, kk, vv = ao.prepare(qg, k, v, qn, kn, pos, heads, kvh, hd, rot, 1.0e6, 1e-6)
+        assert np.allclose(kk, keys, rtol=0, atol=1e-12)
+        got = ao.gated(ao.attend(q, np.concatenate([ck, kk]), np.concatenate([cv, vv]), ctx), gate).reshape(t, heads * hd)
+        assert np.allclose(got, want, rtol=0, atol=1e-12)

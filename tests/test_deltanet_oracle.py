@@ -42,3 +42,44 @@ def test_delta_rule_one_head_by_hand_and_continuation():
     # the decay is in (0, 1]
     d = np.exp(-np.exp(a_log)[None, :] * do.softplus(a + dt_bias[None, :]))
     assert (d > 0).all() and (d <= 1).all()
+
+
+def test_pinned_to_the_reference_template_code():
+    """tests/golden/golden_mixers.npz was computed by the reference's own float64 Gated DeltaNet mixer (causal_conv, silu, split_heads,
+    l2_normalise, share_key_heads, decay_gate, delta_rule_scan, gated_rms_norm; oracle/ref_shim.cpp composes them as deltanet_mixer
+    does): a run from a zero state, and the same tokens cut 6 + 7 with the state and the convolution tail carried over."""
+    import os
+
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_mixers.npz"))
+    kh, vh, dim, taps = (int(v) for v in g["dn_shape"])
+    eps = float(g["dn_eps"][0])
+    args = (g["dn_conv"], g["dn_a_log"], g["dn_dt_bias"], g["dn_norm"], kh, vh, dim, eps)
+    out, state, tail = do.core(g["dn_mixed"], g["dn_z"], g["dn_b"], g["dn_a"], *args)
+    assert np.allclose(out, g["dn_out"], rtol=0, atol=1e-12) and np.allclose(state, g["dn_state"], rtol=0, atol=1e-12)
+    assert np.array_equal(tail, g["dn_tail"])
+    first, s1, t1 = do.core(g["dn_mixed"][:6], g["dn_z"][:6], g["dn_b"][:6], g["dn_a"][:6], *args)
+    second, s2, t2 = do.core(g["dn_mixed"][6:], g["dn_z"][6:], g["dn_b"][6:], g["dn_a"][6:], *args, state=s1, tail=t1)
+    assert np.allclose(np.concatenate([first, second]), g["dn_out_cut"], rtol=0, atol=1e-12)
+    assert np.allclose(s2, g["dn_state_cut"], rtol=0, atol=1e-12) and np.array_equal(t2, g["dn_tail_cut"])
+
+
+def test_agrees_with_the_reference_library_where_it_is_built():
+    import pytest
+
+    from oracle.oracle import Ref
+
+    if not Ref.available():
+        pytest.skip("oracle/_ref/libsepal_ref.so is not built here")
+    r = Ref()
+    rng = np.random.default_rng(78)
+    for kh, vh, dim, taps, t in ((1, 1, 4, 2, 7), (2, 6, 8, 4, 21), (4, 4, 16, 3, 5)):
+        conv_dim = 2 * kh * dim + vh * dim
+        mixed, z = rng.standard_normal((t, conv_dim)), rng.standard_normal((t, vh * dim))
+        b, a = rng.standard_normal((t, vh)), rng.standard_normal((t, vh)) * 2
+        conv = rng.standard_normal((conv_dim, taps)) * 0.5
+        a_log, dt_bias, norm = rng.standard_normal(vh), rng.standard_normal(vh), rng.standard_normal(dim)
+        state, tail = rng.standard_normal((vh, dim, dim)) * 0.3, rng.standard_normal((taps - 1, conv_dim))
+        want = r.deltanet_core(mixed, z, b, a, conv, a_log, dt_bias, norm, kh, vh, dim, 1e-6, state=state, tail=tail)
+        got = do.core(mixed, z, b, a, conv, a_log, dt_bias, norm, kh, vh, dim, 1e-6, state=state, tail=tail)
+        for g_, w_ in zip(got, want):
+            assert np.allclose(g_, w_, rtol=0, atol=1e-11)

@@ -204,6 +204,11 @@ std::shared_ptr<const TensorFile> TensorFile::from_memory(const unsigned char* b
 void TensorFile::parse(const unsigned char* bytes, std::size_t size) {
     std::uint64_t header_bytes = 0;
     for (int i = 7; i >= 0; --i) header_bytes = (header_bytes << 8) | bytes[i];
+    // The limits the reference's reader sets (runner/src/io/safetensors.cpp:21-23,131-248): a header above 100 MB is a damaged or hostile
+    // file; so is a rank above 32. (The tensor descriptions of this library's own C ABI stop at rank 8, far above any weight's.)
+    constexpr std::uint64_t kMaxHeaderBytes = 100'000'000;
+    constexpr std::size_t kMaxRank = 32;
+    if (header_bytes > kMaxHeaderBytes) throw CheckpointError(origin_ + ": the header claims " + std::to_string(header_bytes) + " bytes, above the limit of 100 MB");
     if (header_bytes > size - 8) throw CheckpointError(origin_ + ": the header length " + std::to_string(header_bytes) + " is past the end of the file");
     if (header_bytes < 2) throw CheckpointError(origin_ + ": the header is empty");
     const unsigned char* data = bytes + 8 + header_bytes;
@@ -211,7 +216,7 @@ void TensorFile::parse(const unsigned char* bytes, std::size_t size) {
 
     HeaderScanner scan(reinterpret_cast<const char*>(bytes + 8), header_bytes, origin_);
     scan.expect('{');
-    bool first = true;
+    bool first = true, seen_metadata = false;
     while (!scan.peek('}')) {
         if (!first) scan.expect(',');
         first = false;
@@ -219,6 +224,8 @@ void TensorFile::parse(const unsigned char* bytes, std::size_t size) {
         scan.expect(':');
         scan.expect('{');
         if (name == "__metadata__") {
+            if (seen_metadata) throw CheckpointError(origin_ + ": '__metadata__' appears twice");
+            seen_metadata = true;
             bool first_meta = true;
             while (!scan.peek('}')) {
                 if (!first_meta) scan.expect(',');
@@ -252,6 +259,7 @@ void TensorFile::parse(const unsigned char* bytes, std::size_t size) {
                 has_type = true;
             } else if (key == "shape") {
                 t.shape = scan.numbers();
+                if (t.shape.size() > kMaxRank) throw CheckpointError(origin_ + ": tensor '" + name + "' has rank " + std::to_string(t.shape.size()) + ", above the limit of 32");
                 has_shape = true;
             } else if (key == "data_offsets") {
                 offsets = scan.numbers();
@@ -280,13 +288,21 @@ void TensorFile::parse(const unsigned char* bytes, std::size_t size) {
     scan.expect('}');
     if (!scan.at_end()) scan.fail("text after the header object");
 
-    // File order, and no two tensors sharing a byte.
+    // File order (empty tensors before a non-empty one that starts at the same byte), then one walk over the data section: every byte must
+    // belong to exactly one tensor, so a tensor that starts before the bytes covered so far overlaps an earlier one, one that starts
+    // after them leaves a hole, and what is left behind the last one belongs to nobody. The format asks for exactly this.
     std::sort(tensors_.begin(), tensors_.end(), [](const TensorView& a, const TensorView& b) { return a.data != b.data ? a.data < b.data : a.bytes < b.bytes; });
+    std::uint64_t covered = 0;
     for (std::size_t i = 0; i < tensors_.size(); ++i) {
         index_[tensors_[i].name] = i;
-        if (i > 0 && tensors_[i].bytes != 0 && tensors_[i - 1].data + tensors_[i - 1].bytes > tensors_[i].data)
-            throw CheckpointError(origin_ + ": tensors '" + tensors_[i - 1].name + "' and '" + tensors_[i].name + "' overlap");
+        const std::uint64_t begin = static_cast<std::uint64_t>(tensors_[i].data - data);
+        if (begin < covered) throw CheckpointError(origin_ + ": tensor '" + tensors_[i].name + "' overlaps the bytes of a tensor before it");
+        if (begin > covered)
+            throw CheckpointError(origin_ + ": bytes " + std::to_string(covered) + " to " + std::to_string(begin) + " of the data, before tensor '" + tensors_[i].name +
+                                  "', belong to no tensor");
+        covered = begin + tensors_[i].bytes;
     }
+    if (covered != data_bytes) throw CheckpointError(origin_ + ": the last " + std::to_string(data_bytes - covered) + " bytes of the file belong to no tensor");
 }
 
 const TensorView* TensorFile::find(std::string_view name) const {

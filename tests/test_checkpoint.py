@@ -132,8 +132,27 @@ def test_malformed_files_are_refused(tmp_path):
     refuse("whole number", mutate=lambda h: h["u"].update(shape=[3.0, 4]))
     refuse("not aligned for its 4-byte elements", tensors=[("b", "I8", np.zeros(3, np.int8)), ("t", "F32", a)], pad=3)
     with open(path, "wb") as f:
-        f.write(struct.pack("<Q", 1 << 40) + b"{}")
+        f.write(struct.pack("<Q", 1 << 20) + b"{}")
     with pytest.raises(sb.SepalB200Error, match="past the end of the file"):
+        sb.Checkpoint(path)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", 1 << 40) + b"{}")
+    with pytest.raises(sb.SepalB200Error, match="above the limit of 100 MB"):
+        sb.Checkpoint(path)
+    # every byte of the data section belongs to exactly one tensor (the rule of the reference's reader, runner/src/io/safetensors.cpp:236-249)
+    refuse("belong to no tensor", mutate=lambda h: (h["t"].update(shape=[2, 4], data_offsets=[0, 32])))            # a hole between t and u
+    refuse("the last 48 bytes of the file belong to no tensor", mutate=lambda h: h.pop("u"))                          # bytes behind the last tensor
+    refuse("belong to no tensor", mutate=lambda h: (h["t"].update(shape=[2, 4], data_offsets=[16, 48])))           # a hole before the first tensor
+    # an empty tensor between two that overlap must not hide the overlap: A [0, 40), Z [20, 20), B [20, 60)
+    wide = np.arange(10, dtype=np.float32)
+    refuse("overlap", tensors=[("a", "F32", wide), ("b", "F32", wide), ("z", "F32", np.zeros(0, np.float32))],
+           mutate=lambda h: (h["b"].update(data_offsets=[20, 60]), h["z"].update(data_offsets=[20, 20])))
+    refuse("rank 33, above the limit of 32", tensors=[("t", "F32", np.zeros((1,) * 33, np.float32))])
+    text = b'{"__metadata__":{"a":"1"},"t":{"dtype":"F32","shape":[1],"data_offsets":[0,4]},"__metadata__":{"b":"2"}}'
+    text += b" " * (-len(text) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(text)) + text + b"\0" * 4)
+    with pytest.raises(sb.SepalB200Error, match="'__metadata__' appears twice"):
         sb.Checkpoint(path)
     with open(path, "wb") as f:
         f.write(b"\x01\x02")

@@ -7,6 +7,9 @@ Workloads (BASELINE.json `configs`, zero-based):
     w8g_down_m900   configs[1]: int8-group down projection, M = 900, K = 9728, N = 2560, fp16 activations, fp16 result   (default)
     f16_up_m900     configs[0]: fp16 up projection, M = 900, K = 2560, N = 9728
     f16_up_m4096 / w8g_down_m4096: the same products at the long-log call size
+    f16_dn_out_m900 / f16_o_m900: the DeltaNet out-projection and the attention o-projection with the residual add, 900 rows (lone-CTA kernel)
+    attention       the full-attention core over the 15,900-token log in four chained calls
+    deltanet        the Gated DeltaNet core over one 4096-token call (--tokens), 16 key / 32 value heads of 128 (--heads128: 16 value heads)
     serve           configs[4]: 64 requests of 600-1200 tokens and 4 of 15,900 through the 36-layer GEMM-chain trunk (configs[3]'s
                     stack), whole requests dealt longest-first to the GPUs; reports prefill tokens/s and p50 / p95 request latency
 
@@ -40,11 +43,15 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # name: (kind, M, N, K, config index in BASELINE.json)
-    "w8g_down_m900": ("w8g", 900, 2560, 9728, 1),
-    "f16_up_m900": ("f16", 900, 9728, 2560, 0),
-    "w8g_down_m4096": ("w8g", 4096, 2560, 9728, 1),
-    "f16_up_m4096": ("f16", 4096, 9728, 2560, 0),
+    # name: (kind, M, N, K, config index in BASELINE.json or None, epilogue)
+    "w8g_down_m900": ("w8g", 900, 2560, 9728, 1, "store"),
+    "f16_up_m900": ("f16", 900, 9728, 2560, 0, "store"),
+    "w8g_down_m4096": ("w8g", 4096, 2560, 9728, 1, "store"),
+    "f16_up_m4096": ("f16", 4096, 9728, 2560, 0, "store"),
+    # the short, narrow projections that run on lone CTAs at 900 rows (profiling targets): the DeltaNet out-projection and the attention
+    # o-projection with the residual add fused (float32 stream updated in place)
+    "f16_dn_out_m900": ("f16", 900, 2560, 2048, None, "add"),
+    "f16_o_m900": ("f16", 900, 2560, 4096, None, "add"),
 }
 # Every named trunk GEMM (N x K) for the per-shape table: the projections of a layer at hidden 2560, MLP 9728.
 TRUNK_SHAPES = [("gate_up+swiglu", 19456, 2560, "swiglu"), ("up (config 0)", 9728, 2560, "store"), ("down+residual", 2560, 9728, "add"),
@@ -112,17 +119,18 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def make_operand_sets(ctx, kind, m, n, k, device):
+def make_operand_sets(ctx, kind, m, n, k, device, epilogue="store"):
     """A ring of independent operand sets (seeded synthetic data with BASELINE's distributions) larger than the L2 in total."""
     import torch
 
-    per_set = m * k * 2 + (n * k if kind == "w8g" else n * k * 2) + m * n * 2
+    y_bytes = 4 if epilogue == "add" else 2
+    per_set = m * k * 2 + (n * k if kind == "w8g" else n * k * 2) + m * n * y_bytes
     sets = max(2, -(-int(1.5 * L2_BYTES) // per_set))
     gen = torch.Generator(device=device).manual_seed(1001)
     out = []
     for _ in range(sets):
         x = torch.randn((m, k), generator=gen, device=device).bfloat16().half()  # N(0, 1), exact in bf16 and fp16
-        y = torch.empty((m, n), dtype=torch.float16, device=device)
+        y = torch.zeros((m, n), dtype=torch.float32, device=device) if epilogue == "add" else torch.empty((m, n), dtype=torch.float16, device=device)
         if kind == "w8g":
             q = torch.randint(-127, 128, (n, k), generator=gen, device=device, dtype=torch.int32).to(torch.int8)
             s = (torch.randn((n, k // 128), generator=gen, device=device) * 0.02).abs() / 127.0
@@ -133,10 +141,10 @@ def make_operand_sets(ctx, kind, m, n, k, device):
     return out, sets * per_set
 
 
-def algorithmic_bytes(kind, m, n, k):
-    """Bytes one product must move: X once, W once (int8 + scales for w8g), Y once (fp16)."""
+def algorithmic_bytes(kind, m, n, k, epilogue="store"):
+    """Bytes one product must move: X once, W once (int8 + scales for w8g), Y once (fp16), or read and written (float32) for the residual add."""
     w = n * k + n * (k // 128) * 2 if kind == "w8g" else n * k * 2
-    return m * k * 2 + w + m * n * 2
+    return m * k * 2 + w + (m * n * 8 if epilogue == "add" else m * n * 2)
 
 
 def run_ours(args):
@@ -153,18 +161,19 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    kind, m, n, k, cfg_index = WORKLOADS[args.workload]
+    kind, m, n, k, cfg_index, epilogue = WORKLOADS[args.workload]
+    epi = sb.ADD if epilogue == "add" else sb.STORE
     ctx = sb.Context(local)
-    sets, ring_bytes = make_operand_sets(ctx, kind, m, n, k, device)
+    sets, ring_bytes = make_operand_sets(ctx, kind, m, n, k, device, epilogue)
     calls = args.calls_per_step
     flops_call = 2.0 * m * n * k
 
     def call(i):
         x, w, y = sets[i % len(sets)]
         if kind == "w8g":
-            ctx.gemm_w8g(x, w, y)
+            ctx.gemm_w8g(x, w, y, epilogue=epi)
         else:
-            ctx.gemm_f16(x, w, y)
+            ctx.gemm_f16(x, w, y, epilogue=epi)
 
     def step(s):
         for c in range(calls):
@@ -252,7 +261,7 @@ def run_ours(args):
         "dtype": "f16 x int8-group -> f32 accumulate" if kind == "w8g" else "f16 x f16 -> f32 accumulate",
         "data": "synthetic",
         "config": {
-            "workload": f"{args.workload} (BASELINE configs[{cfg_index}]): M={m} K={k} N={n}",
+            "workload": f"{args.workload}" + (f" (BASELINE configs[{cfg_index}])" if cfg_index is not None else " (a named trunk GEMM, residual add fused)") + f": M={m} K={k} N={n}",
             "calls_per_step": calls,
             "l2": f"ring of {len(sets)} operand sets, {ring_bytes >> 20} MiB > 126 MiB L2: every launch reads its operands from HBM",
             "gemm_rows_per_s": round(m * total_calls / (elapsed_ms * 1e-3) * world, 1),
@@ -270,8 +279,8 @@ def run_ours(args):
                             if long_region else f"bf16_tflops of MEASURED_PEAKS.json ({peak_kind}; burst: a timed region of {elapsed_ms:.0f} ms)"),
             "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC.get(args.workload),
             "traffic_source": "--traffic" if args.traffic is not None else ("profiles/gemm_w8_pair_kernel_w8g_down_m900.md" if NCU_TRAFFIC.get(args.workload) else None),
-            "algorithmic_bytes": algorithmic_bytes(kind, m, n, k),
-            "hbm_gbs_achieved": round(algorithmic_bytes(kind, m, n, k) / (per_call_ms * 1e-3) / 1e9, 1),
+            "algorithmic_bytes": algorithmic_bytes(kind, m, n, k, epilogue),
+            "hbm_gbs_achieved": round(algorithmic_bytes(kind, m, n, k, epilogue) / (per_call_ms * 1e-3) / 1e9, 1),
             "us_per_launch": round(per_call_ms * 1e3, 2),
         },
         "e2e": {
@@ -746,6 +755,137 @@ def run_attention(args):
         dist.destroy_process_group()
 
 
+def run_deltanet(args):
+    """The Gated DeltaNet core of one layer (BASELINE configs[3]'s DeltaNet layers at the 4b geometry: 16 key / 32 value heads of 128, 4 taps)
+    over one 4096-token call of a fresh request: convolution + SiLU + q/k normalisation + gates, the chunked delta rule, the gated norm.
+    A step is one call of sepal_b200_deltanet. The core is bound by its recurrence (the state of a head is updated chunk after chunk),
+    not by memory or by the tensor pipe: the line reports the time per token and, as the roofline, the HBM bytes the call must move
+    (bands in, output out, state in and out) against the measured copy bandwidth."""
+    import torch
+
+    import sepal_runner_b200 as sb
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    kh, vh, dim, taps, tokens = 16, (16 if args.heads128 else 32), 128, 4, args.tokens
+    shape = sb.DeltaNetShape(key_heads=kh, value_heads=vh, head_dim=dim, conv_kernel=taps, eps=1e-6)
+    conv_dim, vd = 2 * kh * dim + vh * dim, vh * dim
+    ctx = sb.Context(local)
+    gen = torch.Generator(device=device).manual_seed(4004 + rank)
+    rnd = lambda *sh, s=1.0: (torch.randn(sh, generator=gen, device=device) * s)  # noqa: E731
+    sets = []
+    per_set = tokens * (conv_dim + vd + 2 * vh) * 2 + tokens * vd * 2
+    for _ in range(max(2, -(-int(1.25 * L2_BYTES) // per_set))):  # a ring of inputs larger than the L2
+        sets.append((rnd(tokens, conv_dim).half(), rnd(tokens, vd).half(), rnd(tokens, vh).half(), rnd(tokens, vh).half(),
+                     torch.empty((tokens, vd), dtype=torch.float16, device=device)))
+    conv, a_log, dt_bias, norm = rnd(conv_dim, taps, s=0.5), rnd(vh, s=0.5), rnd(vh, s=0.5), 1.0 + rnd(dim, s=0.1)
+    states = torch.zeros((1, vh, dim, dim), dtype=torch.float32, device=device)
+    tails = torch.zeros((1, taps - 1, conv_dim), dtype=torch.float32, device=device)
+    keep = []
+
+    def step(i):
+        mixed, z, b, a, out = sets[i % len(sets)]
+        keep.append(sb.deltanet(ctx, shape, [(0, tokens, 0, 1)], mixed, z, b, a, conv, a_log, dt_bias, norm, states, tails, out))
+        if len(keep) > 4:
+            keep.pop(0)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for i in range(args.warmup):
+        step(i)
+    ctx.check_status()
+    ctx.take_launch_count()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    e1.record()
+    barrier()
+    elapsed_ms = e0.elapsed_time(e1)
+    launches = ctx.take_launch_count()
+    ctx.check_status()
+    # end to end: the in-projection's bands from pinned host memory, the gated output back to it
+    mixed, z, b, a, out = sets[0]
+    host = [t.cpu().pin_memory() for t in (mixed, z, b, a)]
+    dev = [torch.empty_like(t) for t in (mixed, z, b, a)]
+    h_out = torch.empty((tokens, vd), dtype=torch.float16).pin_memory()
+
+    def e2e_step():
+        for d, h in zip(dev, host):
+            d.copy_(h, non_blocking=True)
+        keep.append(sb.deltanet(ctx, shape, [(0, tokens, 0, 1)], *dev, conv, a_log, dt_bias, norm, states, tails, out))
+        h_out.copy_(out, non_blocking=True)
+        keep.pop(0)
+
+    e2e_step()
+    barrier()
+    e2e_steps = max(1, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
+    sampler.stop_flag.set()
+    sampler.join(timeout=2)
+    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = float(times[0]), float(times[1])
+    if rank == 0:
+        peaks, peak_kind = measured_peaks()
+        step_ms = elapsed_ms / args.steps
+        bytes_call = per_set + 2 * vh * dim * dim * 4
+        gbs = bytes_call / (step_ms * 1e-3) / 1e9
+        peak = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+        line = {
+            "metric": "Gated DeltaNet core, tokens/s (one 4096-token call of one request, one layer)",
+            "value": round(tokens / (step_ms * 1e-3) * world, 1),
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": round(step_ms, 4),
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "f16 bands, f32 state, TF32 chunk products",
+            "data": "synthetic",
+            "config": {"workload": f"deltanet: {kh} key / {vh} value heads of {dim}, {taps} taps, one fresh request of {tokens} tokens",
+                       "ns_per_token": round(step_ms * 1e6 / tokens, 1), "l2": f"ring of {len(sets)} input sets > 126 MiB L2",
+                       "parallelism": f"one request per GPU x{world}, no collective"},
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
+                         "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peak_kind})", "traffic": None,
+                         "note": "the recurrence over chunks bounds this core, not memory: the fraction shows how far it is from the bytes it must move"},
+            "e2e": {"value": round(tokens / (e2e_ms * 1e-3) * world, 1), "unit": "tokens/s", "h2d_bytes_per_step": tokens * (conv_dim + vd + 2 * vh) * 2,
+                    "d2h_bytes_per_step": tokens * vd * 2, "note": "sepal_b200_deltanet with its bands from pinned host memory and the output back to it"},
+            "gpu_launches": int(launches),
+            "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    ctx.close()
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
 def cpu_baseline(kind, m, n, k, reps: int = 5):
     """The reference's cpu-bf16 packed GEMM on this host's cores, on the same product (int8 weights dequantised to float32 first:
     the reference has no group-128 CPU kernel), weights packed once, best of `reps` (runner/tools/sepal_cpu_gemm_bench.cpp:153-201)."""
@@ -781,7 +921,7 @@ def run_reference(args):
 
     from oracle.oracle import Ref
 
-    kind, m, n, k, cfg_index = WORKLOADS[args.workload]
+    kind, m, n, k, cfg_index, _ = WORKLOADS[args.workload]
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if not Ref.available():
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libsepal_ref.so was not built (the reference tree was absent at build time)"}))
@@ -826,7 +966,8 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="w8g_down_m900", choices=sorted(WORKLOADS) + ["serve", "attention"])
+    ap.add_argument("--workload", default="w8g_down_m900", choices=sorted(WORKLOADS) + ["serve", "attention", "deltanet"])
+    ap.add_argument("--tokens", type=int, default=4096, help="deltanet: tokens of the call")
     ap.add_argument("--heads128", action="store_true", help="attention: 32 / 8 heads of 128 instead of 16 / 4 heads of 256")
     ap.add_argument("--int8", action="store_true", help="serve: store the MLP weights as int8 groups")
     ap.add_argument("--no-trunk", dest="trunk", action="store_false", help="skip the whole-trunk passes")
@@ -839,13 +980,15 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
-        if args.workload in ("serve", "attention"):
+        if args.workload in ("serve", "attention", "deltanet") or WORKLOADS[args.workload][4] is None:
             args.workload = "w8g_down_m900"
         run_reference(args)
     elif args.workload == "serve":
         run_serve(args)
     elif args.workload == "attention":
         run_attention(args)
+    elif args.workload == "deltanet":
+        run_deltanet(args)
     else:
         run_ours(args)
 

@@ -39,7 +39,10 @@ inline constexpr std::size_t kGroup = 128;  // values of k per int8 scale (the r
 ///   2   128 x 128 tiles, whole tiles
 ///   3   128 x 128 tiles, even split
 ///   w, w + 1 (w a multiple of 16 in [16, 256]): 128 x w tiles, whole tiles / even split. SwiGLU and int8 weights take w = 128 or 256.
-///   w + 2: 256 x w tiles on CTA pairs, whole tiles (fp16 weights only).
+///   w + 2, w + 3, w + 6: 256 x w tiles on CTA pairs: whole tiles / even split / whole tiles first and the last waves split.
+///   512 + w (int8 weights, w a multiple of 32 in [64, 192], no SwiGLU): the swapped kernel. The weights are the tensor cores' first
+///       operand, widened and scaled into tensor memory, the tokens the second, w of them to a tile of 256 weight rows; whole tiles. -1
+///       picks it where its narrower tiles need fewer waves than 256-token tiles would (pick_w8t_tokens in gemm_tc.cu).
 inline constexpr int kConfigs = 4;
 
 /// Row of the stacked [gate; up] matrix that packed row p holds (the reference's pack_gate_up_source,

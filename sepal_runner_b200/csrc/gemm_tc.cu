@@ -1430,6 +1430,341 @@ gemm_w8_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
 }
 
+// ---- int8 weights as the A operand from tensor memory ---------------------------------------------------------------------------
+//
+// The roles of the two operands swapped: a pair tile is 256 rows of W (128 in each CTA: the lanes of the accumulator) by `bt` tokens
+// (the columns), and the tensor core reads the weights from TENSOR MEMORY (tcgen05.mma with the A operand in tensor memory) and only
+// the X tile from shared memory. The converter warps read a raw int8 box from shared memory as before, but write what they convert
+// with tcgen05.st: the converted weights never pass through shared memory, which then carries the raw box (in and out) and the X
+// boxes (in and out): about 110 B/clk at 160 tokens against the 158 B/clk of gemm_w8_pair_kernel at 256. And because the tokens lie
+// on the MMA's N side, the tile's token width can be any multiple of 32 up to 192 (tensor memory holds two accumulators of bt columns
+// and the weight buffers): 900 rows pad to 960 (six tiles of 160) instead of 1024.
+//
+// What was measured: a scale group of a tile (eight MMAs of K 16) takes about 1370 clocks whatever bt is; leaving the conversion or
+// the tensor-memory stores out does not shorten it, issuing fewer MMAs does, and two accumulators taken in turn (to break the chain
+// of dependent MMAs) do not. So the kernel is bound by the rate of MMAs with A in tensor memory, about 170 clocks each at any N, and
+// narrow tiles cost as much time as wide ones. It wins through tiling only: where bt makes the tiles fit fewer waves than 256-token
+// tiles do and k is too short for the even split to pay (o projection at 900 tokens: 30 us against 37; DeltaNet out projection: 19
+// against 24; fused qkv: 40 against 45), and loses where the split fills the pairs (down projection: 64 against 58). pick_w8t_tokens
+// decides.
+//
+// Tensor memory (512 columns): accumulators at 0 and bt; weight buffers of 64 columns (one scale group: 128 binary16 values of k, two to
+// a column) from 2 bt on: two at bt = 192, three at 160, four at 128.
+//   warp 0      TMA producer: raw boxes [128 rows x 128 k] int8 with the group's prepared scales, X boxes [bt / 2 tokens x 64 k]
+//   warp 1      MMA issuer (first CTA): per group 8 x tcgen05.mma.cta_group::2 (M 256, N bt, K 16), A from tensor memory
+//   warps 2..5  epilogue: lane = row of W = output column n, registers along the tokens; the result is written transposed (coalesced
+//               across the lanes); the float32 residual update goes through per-warp staging boxes [32 tokens x 32 columns] and TMA
+//               reduce-adds, with no barrier between the warps
+//   warps 6..13 converters: warp w owns tensor-memory lanes 32 (w % 4) .. of every second scale group (warps 6..9 the even ones,
+//               10..13 the odd ones): a thread widens the 128 bytes of its row (exactly: byte ^ 0x80 under the exponent of 1024, minus
+//               1152), multiplies by the row's prepared scale and stores 64 columns of binary16 pairs.
+constexpr int kW8tThreads = 192 + 32 * 8;
+constexpr int kW8tRawBoxes = 4, kW8tXBoxes = 8, kW8tMaxA = 4;
+constexpr int kW8tBarriers = 2 * kW8tRawBoxes + 2 * kW8tXBoxes + 2 * kW8tMaxA + 4;
+constexpr unsigned kW8tRawBytes = 128 * 128;                 // one raw box
+constexpr unsigned kW8tStagingBytes = 4 * 2 * 4096;          // four epilogue warps x two boxes of [32 x 32] float32
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kW8tThreads, 1)
+gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_y,
+                     const GemmParams p) {
+    const unsigned bt = p.bn;                       // tokens per tile (the field carries the MMA's N)
+    const unsigned x_box = (bt / 2) * 128;          // bytes of one X box: this CTA's bt / 2 tokens x 64 k
+    const int x_boxes = static_cast<int>(p.stages);
+    const int a_bufs = static_cast<int>(p.raw_boxes);  // weight buffers in tensor memory
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr0 = ptx::smem_addr(smem_raw);
+    const uint32_t base = (raw_addr0 + 1023u) & ~1023u;
+    uint8_t* const smem = smem_raw + (base - raw_addr0);
+    // layout: staging boxes | raw ring | X ring | scales | barriers
+    const uint32_t staging_addr = base;
+    const unsigned raw_off = kW8tStagingBytes;
+    const unsigned x_off = raw_off + kW8tRawBoxes * kW8tRawBytes;
+    const unsigned scale_off = x_off + x_boxes * x_box;
+    uint8_t* const tail = smem + scale_off + kW8tRawBoxes * 256;
+    const uint32_t bars = ptx::smem_addr(tail);
+    const auto raw_full_bar = [&](int s) { return bars + 8u * s; };
+    const auto raw_empty_bar = [&](int s) { return bars + 8u * (kW8tRawBoxes + s); };
+    const auto x_full_bar = [&](int s) { return bars + 8u * (2 * kW8tRawBoxes + s); };
+    const auto x_empty_bar = [&](int s) { return bars + 8u * (2 * kW8tRawBoxes + kW8tXBoxes + s); };
+    const auto a_full_bar = [&](int s) { return bars + 8u * (2 * kW8tRawBoxes + 2 * kW8tXBoxes + s); };
+    const auto a_empty_bar = [&](int s) { return bars + 8u * (2 * kW8tRawBoxes + 2 * kW8tXBoxes + kW8tMaxA + s); };
+    const auto acc_full_bar = [&](int a) { return bars + 8u * (kW8tBarriers - 4 + a); };
+    const auto acc_empty_bar = [&](int a) { return bars + 8u * (kW8tBarriers - 2 + a); };
+    unsigned* const words = reinterpret_cast<unsigned*>(tail + kW8tBarriers * 8);
+    unsigned* const tmem_slot = words;
+    volatile unsigned* const abort_flag = words + 1;
+
+    const unsigned warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const unsigned rank = ptx::cluster_ctarank();
+    const unsigned pair = blockIdx.x / 2, pairs = gridDim.x / 2;
+    const unsigned t_tiles = p.m_tiles;             // token tiles; p.n_tiles: tiles of 256 rows of W; tile = n_tile * t_tiles + t_tile
+    const unsigned groups = p.k_iters;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kW8tRawBoxes; ++s) {
+            ptx::mbar_init(raw_full_bar(s), 1);
+            ptx::mbar_init(raw_empty_bar(s), 4);  // the four converter warps whose turn the box's group is
+        }
+        for (int s = 0; s < x_boxes; ++s) {
+            ptx::mbar_init(x_full_bar(s), 1);
+            ptx::mbar_init(x_empty_bar(s), 1);
+        }
+        for (int s = 0; s < a_bufs; ++s) {
+            ptx::mbar_init(a_full_bar(s), 8);  // the four converter warps of each CTA whose turn it is (used in the first CTA only)
+            ptx::mbar_init(a_empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(acc_full_bar(a), 1);
+            ptx::mbar_init(acc_empty_bar(a), 256);
+        }
+        words[1] = 0;
+        ptx::fence_barrier_init();
+        ptx::tma_prefetch_descriptor(&map_x);
+        ptx::tma_prefetch_descriptor(&map_w);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_addr(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t a_cols = tmem_base + 2u * bt;    // the weight buffers follow the two accumulators
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int rs = 0, xs = 0;
+            unsigned r_phase = 0, x_phase = 0;
+            bool ok = true;
+            for (unsigned tile = pair; ok && tile < p.tiles; tile += pairs) {
+                const unsigned n_tile = tile / t_tiles, t_tile = tile % t_tiles;
+                const int row_w = static_cast<int>(n_tile * 256 + rank * 128);
+                const int row_x = static_cast<int>(t_tile * bt + rank * (bt / 2));
+                for (unsigned g = 0; ok && g < groups; ++g) {
+                    if (!wait_barrier(raw_empty_bar(rs), r_phase ^ 1u, abort_flag, p.status, kStatusProducerEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::mbar_arrive_expect_tx(raw_full_bar(rs), kW8tRawBytes + 256);
+                    ptx::tma_load_2d(base + raw_off + rs * kW8tRawBytes, &map_w, raw_full_bar(rs), static_cast<int>(g * kW8Group), row_w);
+                    ptx::bulk_load(base + scale_off + rs * 256, p.scales_t + static_cast<size_t>(g) * p.ld_st + row_w, 256, raw_full_bar(rs));
+                    if (++rs == kW8tRawBoxes) {
+                        rs = 0;
+                        r_phase ^= 1u;
+                    }
+                    for (int sub = 0; sub < 2; ++sub) {
+                        if (!wait_barrier(x_empty_bar(xs), x_phase ^ 1u, abort_flag, p.status, kStatusProducerEmpty)) {
+                            ok = false;
+                            break;
+                        }
+                        if (rank == 0) ptx::mbar_arrive_expect_tx(x_full_bar(xs), 2 * x_box);
+                        ptx::tma_load_2d_pair(base + x_off + xs * x_box, &map_x, ptx::map_to_cta(x_full_bar(xs), 0),
+                                              static_cast<int>(g * kW8Group + sub * kBK), row_x);
+                        if (++xs == x_boxes) {
+                            xs = 0;
+                            x_phase ^= 1u;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = ptx::instr_desc_f16_f32acc(2 * kBM, bt);
+            int xs = 0, acc = 0, ab = 0;
+            unsigned x_phase = 0, acc_phase = 0, a_phase = 0;
+            bool ok = true;
+            for (unsigned tile = pair; ok && tile < p.tiles; tile += pairs) {
+                if (!wait_barrier(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kStatusMmaAccEmpty)) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t d = tmem_base + static_cast<uint32_t>(acc) * bt;
+                for (unsigned g = 0; ok && g < groups; ++g) {
+                    if (!wait_barrier(a_full_bar(ab), a_phase, abort_flag, p.status, kStatusMmaConvFull)) {
+                        ok = false;
+                        break;
+                    }
+                    for (int sub = 0; sub < 2; ++sub) {
+                        if (!wait_barrier(x_full_bar(xs), x_phase, abort_flag, p.status, kStatusMmaFull)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after_sync();
+                        const uint64_t desc_x = ptx::smem_desc_k_major_sw128(base + x_off + xs * x_box);
+#pragma unroll
+                        for (int j = 0; j < kBK / 16; ++j)  // 16 values of k: 8 columns of the weight buffer, 32 bytes of the X box's rows
+                            ptx::mma_f16_ts_pair(d, a_cols + static_cast<uint32_t>(ab * 64 + sub * 32 + j * 8), desc_x + 2u * j, idesc,
+                                                 (g > 0 || sub > 0 || j > 0) ? 1u : 0u);
+                        ptx::mma_commit_pair(x_empty_bar(xs), 3);
+                        if (++xs == x_boxes) {
+                            xs = 0;
+                            x_phase ^= 1u;
+                        }
+                    }
+                    if (!ok) break;
+                    ptx::mma_commit_pair(a_empty_bar(ab), 3);
+                    if (++ab == a_bufs) {
+                        ab = 0;
+                        a_phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::mma_commit_pair(acc_full_bar(acc), 3);
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp < 6) {
+        // epilogue: this thread's lane of the accumulator is output column n; its registers run along the tokens
+        const unsigned quarter = warp % 4;
+        const float descale = __ldg(p.descale);
+        uint8_t* const my_boxes = smem + quarter * 8192;
+        const uint32_t my_boxes_addr = staging_addr + quarter * 8192;
+        int acc = 0;
+        unsigned acc_phase = 0, box = 0;
+        for (unsigned tile = pair; tile < p.tiles; tile += pairs) {
+            const bool arrived = wait_barrier(acc_full_bar(acc), acc_phase, abort_flag, p.status, kStatusEpilogueAccFull);
+            if (!__all_sync(0xFFFFFFFFu, arrived) || *abort_flag != 0) break;
+            ptx::tc_fence_after_sync();
+            const unsigned n_tile = tile / t_tiles, t_tile = tile % t_tiles;
+            const unsigned n = n_tile * 256 + rank * 128 + quarter * 32 + lane;
+            const unsigned t0 = t_tile * bt;
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + static_cast<uint32_t>(acc) * bt;
+            const bool two_steps = p.col_scale != nullptr;  // descale, then the row's scale: two roundings, as the other int8 kernels apply them
+            const float second = two_steps && n < p.n ? __ldg(p.col_scale + n) : 1.0f;
+#pragma unroll 1
+            for (unsigned c = 0; c < bt && t0 + c < p.m; c += 32) {
+                float v[32];
+                load_acc_tmem(taddr, c, v);
+                if (two_steps) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(__fmul_rn(v[j], descale), second);
+                } else if (descale != 1.0f) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], descale);
+                }
+                if (p.staged_add != 0) {
+                    // [32 tokens x 32 columns] float32 box of this warp, rows swizzled like the tensor map; the TMA adds it to Y and drops
+                    // what lies past the matrix
+                    if (lane == 0) ptx::bulk_wait_group_read<1>();  // the box about to be written is no longer read by its last reduce
+                    __syncwarp();
+                    uint8_t* dst = my_boxes + box * 4096;
+#pragma unroll
+                    for (unsigned j = 0; j < 32; ++j) *reinterpret_cast<float*>(dst + j * 128 + (((lane >> 2) ^ (j & 7u)) << 4) + ((lane & 3u) << 2)) = v[j];
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_reduce_add_2d(&map_y, my_boxes_addr + box * 4096, static_cast<int>(n_tile * 256 + rank * 128 + quarter * 32), static_cast<int>(t0 + c));
+                        ptx::bulk_commit_group();
+                    }
+                    box ^= 1u;
+                } else if (n < p.n) {
+                    const unsigned rows = min(32u, p.m - (t0 + c));
+                    if (p.y_half != 0) {
+                        __half* out = static_cast<__half*>(p.y) + static_cast<size_t>(t0 + c) * p.ld_y + n;
+                        if (p.epilogue == 1) {
+#pragma unroll
+                            for (unsigned j = 0; j < 32; ++j)
+                                if (j < rows) out[j * p.ld_y] = __float2half_rn(__fadd_rn(__half2float(out[j * p.ld_y]), v[j]));
+                        } else {
+#pragma unroll
+                            for (unsigned j = 0; j < 32; ++j)
+                                if (j < rows) out[j * p.ld_y] = __float2half_rn(v[j]);
+                        }
+                    } else {
+                        float* out = static_cast<float*>(p.y) + static_cast<size_t>(t0 + c) * p.ld_y + n;
+                        if (p.epilogue == 1) {
+#pragma unroll
+                            for (unsigned j = 0; j < 32; ++j)
+                                if (j < rows) out[j * p.ld_y] = __fadd_rn(out[j * p.ld_y], v[j]);
+                        } else {
+#pragma unroll
+                            for (unsigned j = 0; j < 32; ++j)
+                                if (j < rows) out[j * p.ld_y] = v[j];
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+        if (p.staged_add != 0 && lane == 0) ptx::bulk_wait_group_read<0>();  // the staging boxes outlive the reads of them
+    } else {
+        // converters: two sets of four warps take the scale groups in turn (set 0 the even ones, set 1 the odd ones), each warp
+        // converting all 128 k of its 32 rows, so that a warp has two group times for the chain read -> widen -> store to tensor
+        // memory -> wait for the store -> signal, whose latency, not its arithmetic, is what a group costs a warp.
+        const unsigned cw = warp - 6;
+        const unsigned quarter = warp % 4, set = cw / 4;      // the tensor-memory lanes this warp may touch (32 (warp % 4) ..); its turn
+        const unsigned row = quarter * 32 + lane;             // row of the raw box = lane of tensor memory
+        const unsigned sw = row & 7u;
+        const __half2 offset = __half2half2(__ushort_as_half(0x6480));  // 1152
+        const __half zero = __ushort_as_half(0);
+        bool ok = true;
+        unsigned count = 0;  // scale groups of this pair so far, over all its tiles
+        for (unsigned tile = pair; ok && tile < p.tiles; tile += pairs) {
+            const unsigned n_tile = tile / t_tiles;
+            const bool in_n = n_tile * 256 + rank * 128 + row < p.n;  // rows past N multiply by zero (their raw bytes are zero-filled)
+            for (unsigned g = 0; g < groups; ++g, ++count) {
+                if ((count & 1u) != set) continue;
+                const int rs = static_cast<int>(count % kW8tRawBoxes), ab = static_cast<int>(count % static_cast<unsigned>(a_bufs));
+                const unsigned r_phase = (count / kW8tRawBoxes) & 1u, a_phase = (count / static_cast<unsigned>(a_bufs)) & 1u;
+                bool got = wait_barrier(raw_full_bar(rs), r_phase, abort_flag, p.status, kStatusConvFull);
+                got = got && wait_barrier(a_empty_bar(ab), a_phase ^ 1u, abort_flag, p.status, kStatusConvEmpty);
+                if (!__all_sync(0xFFFFFFFFu, got)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint8_t* raw = smem + raw_off + rs * kW8tRawBytes + row * 128;
+                const __half2 sc = __half2half2(in_n ? reinterpret_cast<const __half*>(smem + scale_off + rs * 256)[row] : zero);
+#pragma unroll
+                for (unsigned khalf = 0; khalf < 2; ++khalf) {
+                    uint32_t packed[32];
+#pragma unroll
+                    for (unsigned i = 0; i < 4; ++i) {
+                        const unsigned c = 4 * khalf + i;  // 16-byte piece of the row: k 16 c .. 16 c + 15 of the group
+                        const uint4 q = *reinterpret_cast<const uint4*>(raw + ((c ^ sw) << 4));
+                        const unsigned w[4] = {q.x ^ 0x80808080u, q.y ^ 0x80808080u, q.z ^ 0x80808080u, q.w ^ 0x80808080u};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            unsigned lo = __byte_perm(w[e], 0x64646464u, 0x5140);  // bytes 0, 1 -> two binary16 numbers 1024 + byte
+                            unsigned hi = __byte_perm(w[e], 0x64646464u, 0x5342);  // bytes 2, 3
+                            const __half2 a = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&lo), offset), sc);
+                            const __half2 b = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&hi), offset), sc);
+                            packed[8 * i + 2 * e] = *reinterpret_cast<const unsigned*>(&a);
+                            packed[8 * i + 2 * e + 1] = *reinterpret_cast<const unsigned*>(&b);
+                        }
+                    }
+                    ptx::tmem_st_32x32(a_cols + ((quarter * 32u) << 16) + static_cast<uint32_t>(ab * 64 + khalf * 32), packed);
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(raw_empty_bar(rs));  // the raw box has been read
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(a_full_bar(ab), 0));
+            }
+        }
+    }
+
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
 int max_pairs_of(const Context& ctx, const void* kernel, unsigned threads, int (&cache)[64]) {
     const int slot = ctx.device < 64 ? ctx.device : 63;
     if (cache[slot] == 0) {
@@ -1553,6 +1888,59 @@ void launch_w8_pair(const Context& ctx, const CUtensorMap& map_x, const CUtensor
     p.stream_k = stream_k < 0 ? pick_pair_stream_k(max_pairs, pair_tiles, p.m, p.k, true) : static_cast<unsigned>(stream_k);
     const unsigned pairs = size_pair_grid(ctx, p, max_pairs, pair_tiles);
     launch_kernel(gemm_w8_pair_kernel, dim3(2 * pairs), dim3(kW8Threads), smem, stream, "gemm_w8_pair_kernel launch", map_x, map_w, map_y, p);
+    ++g_launches;
+}
+
+// Whether the swapped int8 kernel should take a multiply, and with how many tokens to a tile (0: the unswapped kernels keep it).
+// Both kernels spend a launch of about 8 us around a main loop that costs a pair a fixed time per scale group of a tile, whatever
+// the tile's width in tokens: about 0.74 us in the swapped kernel (a tile of 256 weight rows by at most 192 tokens) and 0.92 us in
+// the unswapped one (256 tokens by 256 weight rows), which can also split k evenly over the pairs at the price of a fix-up of about
+// 8 us. So the swapped kernel wins where its narrower tiles need no more waves than the unswapped kernel's (short k, where the split
+// does not pay: the o and DeltaNet out projections at most sizes, the wide projections where the token count divides well), and
+// loses where the split fills the pairs (the down projection) or its tiles need an extra wave. The estimate follows the measured
+// times of the trunk's shapes from 300 to 4096 tokens to within a few us; a margin of 5 % keeps the unswapped kernel on ties.
+unsigned pick_w8t_tokens(unsigned pairs, unsigned m, unsigned n, unsigned k) {
+    if (pairs == 0 || m <= kBM) return 0;
+    const unsigned n_tiles = (n + 255) / 256, groups = k / kW8Group;
+    unsigned best_bt = 0, best_waves = ~0u;
+    for (unsigned bt = 96; bt <= 192; bt += 32) {  // the narrowest tile among those with the fewest waves: the shortest epilogue
+        const unsigned waves = (((m + bt - 1) / bt) * n_tiles + pairs - 1) / pairs;
+        if (waves < best_waves) best_waves = waves, best_bt = bt;
+    }
+    const unsigned pair_tiles = ((m + 2 * kBM - 1) / (2 * kBM)) * n_tiles;
+    const bool split = pick_pair_stream_k(pairs, pair_tiles, m, k, true) != 0;
+    const double unswapped_waves = split ? static_cast<double>(pair_tiles) / pairs : static_cast<double>((pair_tiles + pairs - 1) / pairs);
+    const double swapped = 8.0 + 0.74 * groups * best_waves;
+    const double unswapped = 8.0 + 0.92 * groups * unswapped_waves + (split ? 8.0 : 0.0);
+    return swapped < 0.95 * unswapped ? best_bt : 0u;
+}
+
+// The swapped int8 kernel (weights from tensor memory). `bt`: tokens per tile, a multiple of 32 from 64 to 192.
+void launch_w8t_pair(const Context& ctx, const void* x, std::size_t ld_x, const void* q, std::size_t ld_q, GemmParams p, unsigned bt, cudaStream_t stream) {
+    p.bn = bt;
+    p.raw_boxes = (kTmemCols - 2 * bt) / 64;  // weight buffers that fit beside the two accumulators
+    if (p.raw_boxes > static_cast<unsigned>(kW8tMaxA)) p.raw_boxes = kW8tMaxA;
+    const unsigned x_box = (bt / 2) * 128;
+    const unsigned fixed = 1024 + kW8tStagingBytes + kW8tRawBoxes * (kW8tRawBytes + 256) + kW8tBarriers * 8 + 64;
+    unsigned x_boxes = (kSmemLimit - fixed) / x_box;
+    if (x_boxes > static_cast<unsigned>(kW8tXBoxes)) x_boxes = kW8tXBoxes;
+    p.stages = x_boxes & ~1u;  // two boxes to a scale group
+    p.m_tiles = (p.m + bt - 1) / bt;
+    p.n_tiles = (p.n + 255) / 256;
+    p.k_iters = p.k / kW8Group;
+    p.tiles = p.m_tiles * p.n_tiles;
+    p.stream_k = 0;
+    p.staged_add = (p.epilogue == 1 && p.y_half == 0 && p.vec_ok != 0) ? 1u : 0u;
+    const CUtensorMap map_x = make_tensor_map_2d(ctx, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.m, p.k, ld_x, bt / 2, kBK, true);
+    const CUtensorMap map_w = make_tensor_map_2d(ctx, q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.n, p.k, ld_q, 128, kW8Group, true);
+    CUtensorMap map_y;
+    std::memset(&map_y, 0, sizeof map_y);
+    if (p.staged_add != 0) map_y = make_tensor_map_2d(ctx, p.y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.m, p.n, p.ld_y, 32, 32, true);
+    const unsigned smem = fixed + p.stages * x_box;
+    static int cache[64] = {};
+    unsigned pairs = static_cast<unsigned>(max_pairs_of(ctx, reinterpret_cast<const void*>(gemm_w8t_pair_kernel), kW8tThreads, cache));
+    if (p.tiles < pairs) pairs = p.tiles;
+    launch_kernel(gemm_w8t_pair_kernel, dim3(2 * pairs), dim3(kW8tThreads), smem, stream, "gemm_w8t_pair_kernel launch", map_x, map_w, map_y, p);
     ++g_launches;
 }
 
@@ -1805,6 +2193,26 @@ void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMat
     require_aligned(x, "X");
     require_aligned(q, "q");
     check(cudaSetDevice(ctx.device), "cudaSetDevice");
+    unsigned swapped = 0;  // tokens to a tile of the swapped kernel (weights from tensor memory); 0: one of the other kernels
+    if (config >= 512) {
+        swapped = static_cast<unsigned>(config - 512);
+        if (swapped < 64 || swapped > 192 || swapped % 32 != 0 || epilogue == Epilogue::SwiGLU)
+            throw std::invalid_argument("launch_gemm_w8g: config 512 + w takes w = 64, 96, ..., 192 tokens per tile and no SwiGLU epilogue");
+    } else if (config == -1 && epilogue != Epilogue::SwiGLU) {
+        swapped = pick_w8t_tokens(static_cast<unsigned>(ctx.sm_count / 2), static_cast<unsigned>(t), static_cast<unsigned>(n), static_cast<unsigned>(k));
+    }
+    if (swapped != 0) {
+        const unsigned bt = swapped;
+        if (!unit_scales && (ld_st % 8 != 0 || ld_st < (n + 255) / 256 * 256 || reinterpret_cast<std::uintptr_t>(scales_t) % 16 != 0))
+            throw std::invalid_argument("launch_gemm_w8g: scales_t must be 16-byte aligned with a row stride of at least N rounded up to 256");
+        GemmParams p = common_params(ctx, y, ld_y, y_half, t, n, k, epilogue);
+        p.scales_t = static_cast<const __half*>(scales_t);
+        p.ld_st = ld_st;
+        p.descale = descale;
+        p.col_scale = wm.col_scale;
+        launch_w8t_pair(ctx, x, ld_x, q, ld_q, p, bt, stream);
+        return;
+    }
     unsigned bn = 256;
     bool stream_k = false, pair = false, late = false;
     // The pair kernel takes any tile width; the lone-CTA kernel (few rows, or the even split of k) takes 128 or 256.

@@ -289,7 +289,64 @@ def test_w8g_epilogues(ctx, oracle):
         ctx.gemm_w8g(dev(x).half(), wq, config=193)  # the even split of k runs on lone CTAs with tiles of 128 or 256 columns
 
 
-# ---- BASELINE's full sizes ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("t,n,k", [(1, 2, 128), (37, 200, 256), (129, 258, 384), (300, 520, 640), (900, 640, 1280), (1000, 1024, 512)])
+@pytest.mark.parametrize("tokens", [64, 96, 128, 160, 192])
+def test_w8g_swapped_kernel(ctx, oracle, t, n, k, tokens):
+    """config 512 + w: the weights are the tensor cores' first operand, converted into tensor memory, and the tokens the second, w to a
+    tile. Every epilogue it serves (float32 and binary16 stores, the residual add into either), ragged token and weight counts, several
+    tiles to a pair (1000 x 1024 in tiles of 64 tokens on 74 pairs: one; the same on fewer pairs: the accumulators alternate)."""
+    import torch
+
+    import sepal_runner_b200 as sb
+
+    rng = np.random.default_rng(5000 + t + tokens)
+    x = grid(oracle, rng.standard_normal((t, k), dtype=np.float32))
+    w = (rng.standard_normal((n, k)) / np.sqrt(k)).astype(np.float32)
+    q, s = ctx.quantize_group_s8(dev(w))
+    wq = ctx.prepare_w8g(q, s)
+    wd = oracle.dequant_group_s8(*oracle.quantize_group_s8(w))
+    want = oracle.gemm(x, wd)
+    y = ctx.gemm_w8g(dev(x).half(), wq, y_half=False, config=512 + tokens)
+    ctx.check_status()
+    # q * s is rounded to binary16 twice on the way to the tensor cores (2^-11 each): a bound per output that holds without averaging
+    assert (np.abs(y.cpu().numpy() - want) <= 1.1e-3 * (np.abs(x).astype(np.float64) @ np.abs(wd).astype(np.float64).T) + 1e-30).all()
+    if t * n >= 1000:
+        assert rel_fro(y.cpu().numpy(), want) < 1e-3
+    unswapped = ctx.gemm_w8g(dev(x).half(), wq, y_half=False, config=258 if t > 128 else 0)
+    assert rel_fro(y.cpu().numpy(), unswapped.cpu().numpy()) < 1e-5  # the same converted weights, another order of summation at most
+    yh = ctx.gemm_w8g(dev(x).half(), wq, y_half=True, config=512 + tokens)
+    assert torch.equal(yh, y.half())
+    res = rng.standard_normal((t, n), dtype=np.float32)
+    yd = dev(res.copy())
+    ctx.gemm_w8g(dev(x).half(), wq, yd, epilogue=sb.ADD, config=512 + tokens)
+    ctx.check_status()
+    assert torch.equal(yd, dev(res) + y)  # one float32 addition to what was there
+    yd = dev(res.copy()).half()
+    before = yd.float()
+    ctx.gemm_w8g(dev(x).half(), wq, yd, epilogue=sb.ADD, config=512 + tokens)
+    ctx.check_status()
+    assert torch.equal(yd, (before + y).half())
+    with pytest.raises(sb.SepalB200Error, match="config"):
+        ctx.gemm_w8g(dev(x).half(), wq, config=512 + tokens + 8)
+    if n % 128 == 0:
+        with pytest.raises(sb.SepalB200Error, match="config"):
+            ctx.gemm_w8g(dev(x).half(), wq, epilogue=sb.SWIGLU, config=512 + tokens)
+
+
+def test_w8g_swapped_kernel_many_tiles_to_a_pair(ctx, oracle):
+    """3000 tokens by 2560 outputs: 320 tiles of 96 tokens on 74 pairs, so every pair walks four or five tiles, its two accumulators
+    and its rings of boxes wrapping around several times; and the automatic choice on the same operands."""
+    rng = np.random.default_rng(5151)
+    t, n, k = 3000, 2560, 512
+    x = grid(oracle, rng.standard_normal((t, k), dtype=np.float32))
+    w = (rng.standard_normal((n, k)) / np.sqrt(k)).astype(np.float32)
+    q, s = ctx.quantize_group_s8(dev(w))
+    wq = ctx.prepare_w8g(q, s)
+    want = oracle.gemm(x, oracle.dequant_group_s8(*oracle.quantize_group_s8(w)))
+    for config in (512 + 96, 512 + 192, -1):
+        y = ctx.gemm_w8g(dev(x).half(), wq, y_half=False, config=config)
+        ctx.check_status()
+        assert rel_fro(y.cpu().numpy(), want) < 1e-3, config
 
 
 # ---- fp16 x int8 with one scale per output row (gpu-q8w) -----------------------------------------------------------------------
@@ -312,7 +369,7 @@ def test_row_quantiser_is_bit_exact(ctx, oracle):
 
 
 @pytest.mark.parametrize("t,n,k", [(1, 2, 128), (130, 258, 256), (300, 520, 640), (900, 1024, 2560)])
-@pytest.mark.parametrize("config", [-1, 0, 1, 3, 258, 259, 146])
+@pytest.mark.parametrize("config", [-1, 0, 1, 3, 258, 259, 146, 512 + 96, 512 + 192])
 def test_w8r_against_the_dequantised_product(ctx, oracle, t, n, k, config):
     """The reference bounds its W8A16 multiply by 1e-5 against the float64 product of the dequantised weights
     (runner/cuda/tests/test_gemm_s8_kernels.cpp:230-252): the integers are exact in binary16 and the scale multiplies the float32 sum."""
@@ -343,7 +400,7 @@ def test_w8r_epilogues(ctx, oracle):
         ctx.check_status()
         assert rel_fro(y.cpu().numpy(), oracle.swiglu_packed(oracle.gemm(x, wd), inter)) < 1e-5, config
     res = rng.standard_normal((t, 2 * inter), dtype=np.float32)
-    for config in (-1, 1, 258, 259):
+    for config in (-1, 1, 258, 259, 512 + 128):
         yd = dev(res.copy())
         ctx.gemm_w8r(dev(x).half(), q, sw, yd, epilogue=sb.ADD, config=config)
         ctx.check_status()

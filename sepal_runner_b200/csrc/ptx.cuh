@@ -276,6 +276,17 @@ __device__ __forceinline__ void mma_f16_ts_pair(uint32_t tmem_d, uint32_t tmem_a
         ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// The same, always accumulating: no predicate to compute on the issuing thread.
+__device__ __forceinline__ void mma_f16_ts_pair_acc(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc)
+        : "memory");
+}
 // Arrives on the barrier at the same shared-memory offset in every CTA of `cta_mask` when the pair's MMAs issued so far have finished.
 __device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint16_t cta_mask) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(cta_mask)

@@ -328,9 +328,14 @@ def test_w8g_swapped_kernel(ctx, oracle, t, n, k, tokens):
     assert torch.equal(yd, (before + y).half())
     with pytest.raises(sb.SepalB200Error, match="config"):
         ctx.gemm_w8g(dev(x).half(), wq, config=512 + tokens + 8)
-    if n % 128 == 0:
-        with pytest.raises(sb.SepalB200Error, match="config"):
-            ctx.gemm_w8g(dev(x).half(), wq, epilogue=sb.SWIGLU, config=512 + tokens)
+    if n % 128 == 0:  # any matrix serves as packed [gate | up] blocks of 64 + 64 rows; 640 rows are five blocks, the pair's last CTA has none
+        for half in (False, True):
+            got = ctx.gemm_w8g(dev(x).half(), wq, epilogue=sb.SWIGLU, y_half=half, config=512 + tokens)
+            ctx.check_status()
+            assert got.shape == (t, n // 2)
+            assert rel_fro(got.float().cpu().numpy(), oracle.swiglu_packed(want.astype(np.float32), n // 2)) < (2e-3 if half else 1e-3)
+            other = ctx.gemm_w8g(dev(x).half(), wq, epilogue=sb.SWIGLU, y_half=half, config=258)
+            assert rel_fro(got.float().cpu().numpy(), other.float().cpu().numpy()) < (1e-3 if half else 1e-5)
 
 
 def test_w8g_swapped_kernel_many_tiles_to_a_pair(ctx, oracle):

@@ -1463,7 +1463,7 @@ gemm_w8_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 constexpr int kW8tThreads = 192 + 32 * 8 + 32;
 constexpr unsigned kW8tSecondIssuer = 14;            // the warp of the second MMA-issuing thread
 constexpr int kW8tMaxDepth = 6, kW8tMaxA = 4;      // most scale groups in the raw and X rings; most weight buffers in tensor memory
-constexpr int kW8tBarriers = 4 * kW8tMaxDepth + 2 * kW8tMaxA + 4 + 2;  // rings, weight buffers, accumulators, the issuing threads' turns
+constexpr int kW8tBarriers = 4 * kW8tMaxDepth + 2 * kW8tMaxA + 4;
 constexpr unsigned kW8tRawBytes = 128 * 128;                 // one raw box
 constexpr unsigned kW8tStagingBytes = 4 * 2 * 4096;          // four epilogue warps x two boxes of [32 x 32] float32
 
@@ -1492,9 +1492,8 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     const auto x_empty_bar = [&](int s) { return bars + 8u * (3 * kW8tMaxDepth + s); };
     const auto a_full_bar = [&](int s) { return bars + 8u * (4 * kW8tMaxDepth + s); };
     const auto a_empty_bar = [&](int s) { return bars + 8u * (4 * kW8tMaxDepth + kW8tMaxA + s); };
-    const auto acc_full_bar = [&](int a) { return bars + 8u * (kW8tBarriers - 6 + a); };
-    const auto acc_empty_bar = [&](int a) { return bars + 8u * (kW8tBarriers - 4 + a); };
-    const auto turn_bar = [&](unsigned t) { return bars + 8u * (kW8tBarriers - 2 + t); };
+    const auto acc_full_bar = [&](int a) { return bars + 8u * (kW8tBarriers - 4 + a); };
+    const auto acc_empty_bar = [&](int a) { return bars + 8u * (kW8tBarriers - 2 + a); };
     unsigned* const words = reinterpret_cast<unsigned*>(tail + kW8tBarriers * 8);
     unsigned* const tmem_slot = words;
     volatile unsigned* const abort_flag = words + 1;
@@ -1518,11 +1517,8 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             ptx::mbar_init(a_full_bar(s), 8);   // the four converter warps of each CTA whose turn it is (used in the first CTA only)
             ptx::mbar_init(a_empty_bar(s), 1);
         }
-        for (int a = 0; a < 2; ++a) {
-            ptx::mbar_init(acc_full_bar(a), 2);  // the two issuing threads
-            ptx::mbar_init(acc_empty_bar(a), 256);
-            ptx::mbar_init(turn_bar(a), 1);
-        }
+        ptx::mbar_init(acc_full_bar(0), 2);     // the two issuing threads
+        ptx::mbar_init(acc_empty_bar(0), 256);
         words[1] = 0;
         ptx::fence_barrier_init();
         ptx::tma_prefetch_descriptor(&map_x);
@@ -1583,50 +1579,36 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         // drained, about 500 clocks (measured alone: one thread issuing 8 MMAs and a commit over and over takes 112 clocks an MMA
         // whatever N is, 154 with 4 MMAs to a commit; two threads doing so side by side take 160 each at N 160, which is the tensor
         // core's full rate). The scale groups of a pair, counted over all its tiles, go to the two threads in turn (as they go to the two
-        // sets of converter warps). Both sum into the same accumulator, and in k order: a thread issues the MMAs of its group only after
-        // the other has issued those of the group before (it passes the turn on a barrier right after its last MMA, before its commits),
-        // and the tensor core takes a CTA's MMAs in the order they were issued.
+        // sets of converter warps), each thread summing into its OWN accumulator; the epilogue adds the two, always in the same order,
+        // so the result does not depend on how the tensor core interleaves the two threads' MMAs. (Both threads summing into one
+        // accumulator, each issuing its group only after the other had issued the group before, gave bit-equal results here at every N
+        // up to 192 and sums that differed in the last bits from run to run in the fp16 pair kernel at N 256: the order in which the
+        // tensor core takes the MMAs of two threads is not the order in which they were issued.)
         if (lane == 0 && rank == 0) {
             const unsigned turn = warp == 1 ? 0u : 1u;
             const uint32_t idesc = ptx::instr_desc_f16_f32acc(2 * kBM, bt);
             const uint64_t desc_x0 = ptx::smem_desc_k_major_sw128(base + x_off);
             const uint32_t x_step = x_box >> 4, x_step2 = x_box >> 3;  // one X box, two (a scale group), in the descriptor's 16-byte units
-            int xs = static_cast<int>(turn), ab = static_cast<int>(turn), acc = 0;  // the rings hold at least two groups each
-            unsigned x_phase = 0, acc_phase = 0, a_phase = 0, turn_phase = 0, count = 0;
+            const uint32_t d = tmem_base + turn * bt;
+            int xs = static_cast<int>(turn), ab = static_cast<int>(turn);  // the rings hold at least two groups each
+            unsigned x_phase = 0, acc_phase = 0, a_phase = 0, count = 0;
             bool ok = true;
-#ifdef SEPAL_TRACE_W8T
-            long long tr_a = 0, tr_e = 0;
-            const long long tr_0 = clock64();
-#endif
             for (unsigned tile = pair; ok && tile < p.tiles; tile += pairs) {
-#ifdef SEPAL_TRACE_W8T
-                const long long te = clock64();
-#endif
-                if (!wait_barrier(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kStatusMmaAccEmpty)) break;
-#ifdef SEPAL_TRACE_W8T
-                tr_e += clock64() - te;
-#endif
+                if (!wait_barrier(acc_empty_bar(0), acc_phase ^ 1u, abort_flag, p.status, kStatusMmaAccEmpty)) break;
                 ptx::tc_fence_after_sync();
-                const uint32_t d = tmem_base + static_cast<uint32_t>(acc) * bt;
+                unsigned fresh = 0;  // this thread's first MMA of the tile overwrites its accumulator
                 for (unsigned g = 0; g < groups; ++g, ++count) {
                     if ((count & 1u) != turn) continue;
-#ifdef SEPAL_TRACE_W8T
-                    const long long ta = clock64();
-#endif
                     if (!wait_barrier(a_full_bar(ab), a_phase, abort_flag, p.status, kStatusMmaConvFull) ||
-                        !wait_barrier(x_full_bar(xs), x_phase, abort_flag, p.status, kStatusMmaFull) ||
-                        (count != 0 && !wait_barrier(turn_bar(turn), turn_phase, abort_flag, p.status, kStatusMmaFull))) {
+                        !wait_barrier(x_full_bar(xs), x_phase, abort_flag, p.status, kStatusMmaFull)) {
                         ok = false;
                         break;
                     }
-                    if (count != 0) turn_phase ^= 1u;
-#ifdef SEPAL_TRACE_W8T
-                    tr_a += clock64() - ta;
-#endif
                     ptx::tc_fence_after_sync();
                     const uint32_t a = a_cols + static_cast<uint32_t>(ab) * 64u;
                     const uint64_t dx = desc_x0 + static_cast<uint64_t>(static_cast<uint32_t>(xs) * x_step2);
-                    ptx::mma_f16_ts_pair(d, a, dx, idesc, g != 0 ? 1u : 0u);  // the tile's first MMA overwrites the accumulator
+                    ptx::mma_f16_ts_pair(d, a, dx, idesc, fresh);
+                    fresh = 1;
                     ptx::mma_f16_ts_pair_acc(d, a + 8, dx + 2, idesc);
                     ptx::mma_f16_ts_pair_acc(d, a + 16, dx + 4, idesc);
                     ptx::mma_f16_ts_pair_acc(d, a + 24, dx + 6, idesc);
@@ -1634,7 +1616,6 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                     ptx::mma_f16_ts_pair_acc(d, a + 40, dx + x_step + 2, idesc);
                     ptx::mma_f16_ts_pair_acc(d, a + 48, dx + x_step + 4, idesc);
                     ptx::mma_f16_ts_pair_acc(d, a + 56, dx + x_step + 6, idesc);
-                    ptx::mbar_arrive(turn_bar(turn ^ 1u));  // the other thread's turn
                     ptx::mma_commit_pair(x_empty_bar(xs), 3);
                     ptx::mma_commit_pair(a_empty_bar(ab), 3);
                     xs += 2;
@@ -1648,16 +1629,9 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                         a_phase ^= 1u;
                     }
                 }
-                // Both threads commit: each commit covers its own thread's MMAs only, and the tile is done when both have drained.
-                if (ok) ptx::mma_commit_pair(acc_full_bar(acc), 3);
-                if (++acc == 2) {
-                    acc = 0;
-                    acc_phase ^= 1u;
-                }
+                if (ok) ptx::mma_commit_pair(acc_full_bar(0), 3);  // both threads: the tile is done when the MMAs of both have drained
+                acc_phase ^= 1u;
             }
-#ifdef SEPAL_TRACE_W8T
-            if (blockIdx.x == 0) printf("mma %u: total %lld wait %lld wait_acc_empty %lld groups %u\n", turn, clock64() - tr_0, tr_a, tr_e, groups);
-#endif
         }
         __syncwarp();
     } else if (warp < 6) {
@@ -1666,32 +1640,31 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         const float descale = __ldg(p.descale);
         uint8_t* const my_boxes = smem + quarter * 8192;
         const uint32_t my_boxes_addr = staging_addr + quarter * 8192;
-        int acc = 0;
-        unsigned acc_phase = 0, box = 0;
-#ifdef SEPAL_TRACE_W8T
-        long long te_wait = 0, te_work = 0, te_arrive = 0;
-#endif
-        for (unsigned tile = pair; tile < p.tiles; tile += pairs) {
-#ifdef SEPAL_TRACE_W8T
-            const long long e0 = clock64();
-#endif
-            const bool arrived = wait_barrier(acc_full_bar(acc), acc_phase, abort_flag, p.status, kStatusEpilogueAccFull);
+        unsigned acc_phase = 0, box = 0, count = 0;
+        for (unsigned tile = pair; tile < p.tiles; tile += pairs, count += groups) {
+            const bool arrived = wait_barrier(acc_full_bar(0), acc_phase, abort_flag, p.status, kStatusEpilogueAccFull);
             if (!__all_sync(0xFFFFFFFFu, arrived) || *abort_flag != 0) break;
-#ifdef SEPAL_TRACE_W8T
-            const long long e1 = clock64();
-            te_wait += e1 - e0;
-#endif
             ptx::tc_fence_after_sync();
             const unsigned n_tile = tile / t_tiles, t_tile = tile % t_tiles;
             const unsigned n = n_tile * 256 + rank * 128 + quarter * 32 + lane;
             const unsigned t0 = t_tile * bt;
-            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + static_cast<uint32_t>(acc) * bt;
+            // The first issuing thread's accumulator; the second's is bt columns on. A tile of a single scale group leaves one of them
+            // unwritten: the group went to the thread whose turn it was.
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + (groups == 1 && (count & 1u) != 0 ? bt : 0u);
+            const bool both = groups > 1;
             const bool two_steps = p.col_scale != nullptr;  // descale, then the row's scale: two roundings, as the other int8 kernels apply them
             const float second = two_steps && n < p.n ? __ldg(p.col_scale + n) : 1.0f;
 #pragma unroll 1
             for (unsigned c = 0; c < bt && t0 + c < p.m; c += 32) {
                 float v[32];
-                load_acc_tmem(taddr, c, v);
+                {
+                    uint32_t lo[32], hi[32];
+                    ptx::tmem_ld_32x32(taddr + c, lo);
+                    if (both) ptx::tmem_ld_32x32(taddr + bt + c, hi);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = both ? __fadd_rn(__uint_as_float(lo[j]), __uint_as_float(hi[j])) : __uint_as_float(lo[j]);
+                }
                 if (two_steps) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(__fmul_rn(v[j], descale), second);
@@ -1774,23 +1747,9 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 }
             }
             ptx::tc_fence_before_sync();
-#ifdef SEPAL_TRACE_W8T
-            const long long e2 = clock64();
-#endif
-            ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
-#ifdef SEPAL_TRACE_W8T
-            __syncwarp();
-            te_work += e2 - e1;
-            te_arrive += clock64() - e2;
-#endif
-            if (++acc == 2) {
-                acc = 0;
-                acc_phase ^= 1u;
-            }
+            ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(0), 0));
+            acc_phase ^= 1u;
         }
-#ifdef SEPAL_TRACE_W8T
-        if (blockIdx.x < 2 && lane == 0 && warp == 2) printf("epilogue cta %u: wait_acc_full %lld work %lld arrive %lld\n", blockIdx.x, te_wait, te_work, te_arrive);
-#endif
         if (p.staged_add != 0 && lane == 0) ptx::bulk_wait_group_read<0>();  // the staging boxes outlive the reads of them
     } else {
         // converters: two sets of four warps take the scale groups in turn (set 0 the even ones, set 1 the odd ones), each warp
@@ -1806,28 +1765,13 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         unsigned count = 0;  // scale groups of this pair so far, over all its tiles
         int rs = static_cast<int>(set), ab = static_cast<int>(set);  // ring slots of this set's next group (both rings hold at least two)
         unsigned r_phase = 0, a_phase = 0;
-#ifdef SEPAL_TRACE_W8T
-        long long tc_raw = 0, tc_empty = 0, tc_conv = 0, tc_st = 0, tc_arrive = 0;
-        const long long tc_0 = clock64();
-#endif
         for (unsigned tile = pair; ok && tile < p.tiles; tile += pairs) {
             const unsigned n_tile = tile / t_tiles;
             const bool in_n = n_tile * 256 + rank * 128 + row < p.n;  // rows past N multiply by zero (their raw bytes are zero-filled)
             for (unsigned g = 0; g < groups; ++g, ++count) {
                 if ((count & 1u) != set) continue;
-#ifdef SEPAL_TRACE_W8T
-                const long long c0 = clock64();
-#endif
                 bool got = wait_barrier(raw_full_bar(rs), r_phase, abort_flag, p.status, kStatusConvFull);
-#ifdef SEPAL_TRACE_W8T
-                const long long c1 = clock64();
-#endif
                 got = got && wait_barrier(a_empty_bar(ab), a_phase ^ 1u, abort_flag, p.status, kStatusConvEmpty);
-#ifdef SEPAL_TRACE_W8T
-                const long long c2 = clock64();
-                tc_raw += c1 - c0;
-                tc_empty += c2 - c1;
-#endif
                 if (!__all_sync(0xFFFFFFFFu, got)) {
                     ok = false;
                     break;
@@ -1856,23 +1800,11 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                     ptx::tmem_st_32x32(a_cols + ((quarter * 32u) << 16) + static_cast<uint32_t>(ab * 64 + khalf * 32), packed);
                 }
                 __syncwarp();
-#ifdef SEPAL_TRACE_W8T
-                const long long c3 = clock64();
-#endif
                 if (lane == 0) ptx::mbar_arrive(raw_empty_bar(rs));  // the raw box has been read
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-#ifdef SEPAL_TRACE_W8T
-                const long long c4 = clock64();
-                tc_conv += c3 - c2;
-                tc_st += c4 - c3;
-#endif
                 if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(a_full_bar(ab), 0));
-#ifdef SEPAL_TRACE_W8T
-                __syncwarp();
-                tc_arrive += clock64() - c4;
-#endif
                 rs += 2;  // this set's next group: two further in both rings
                 if (rs >= depth) {
                     rs -= depth;
@@ -1885,11 +1817,6 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 }
             }
         }
-#ifdef SEPAL_TRACE_W8T
-        if (blockIdx.x < 2 && lane == 0 && (warp == 6 || warp == 10))
-            printf("conv cta %u warp %u: total %lld wait_raw %lld wait_a_empty %lld convert %lld st_wait %lld arrive %lld\n", blockIdx.x, warp, clock64() - tc_0,
-                   tc_raw, tc_empty, tc_conv, tc_st, tc_arrive);
-#endif
     }
 
     ptx::tc_fence_before_sync();
@@ -2028,25 +1955,30 @@ void launch_w8_pair(const Context& ctx, const CUtensorMap& map_x, const CUtensor
 }
 
 // Whether the swapped int8 kernel should take a multiply, and with how many tokens to a tile (0: the unswapped kernels keep it).
-// Both kernels spend a launch of about 8 us around a main loop that costs a pair a fixed time per scale group of a tile, whatever
-// the tile's width in tokens: about 0.74 us in the swapped kernel (a tile of 256 weight rows by at most 192 tokens) and 0.92 us in
-// the unswapped one (256 tokens by 256 weight rows), which can also split k evenly over the pairs at the price of a fix-up of about
-// 8 us. So the swapped kernel wins where its narrower tiles need no more waves than the unswapped kernel's (short k, where the split
-// does not pay: the o and DeltaNet out projections at most sizes, the wide projections where the token count divides well), and
-// loses where the split fills the pairs (the down projection) or its tiles need an extra wave. The estimate follows the measured
-// times of the trunk's shapes from 300 to 4096 tokens to within a few us; a margin of 5 % keeps the unswapped kernel on ties.
-unsigned pick_w8t_tokens(unsigned pairs, unsigned m, unsigned n, unsigned k) {
+// Estimates in microseconds, fitted to the measured times of the trunk's nine shapes at ten token counts from 200 to 4096. Both kernels
+// spend about 8 us around their main loops. The swapped kernel's main loop costs a pair 0.44 us per scale group of a tile of up to 160
+// tokens (0.75 at 192, where tensor memory holds only one weight buffer for each issuing thread) and its epilogue is not hidden behind
+// the next tile (both accumulators belong to the tile): about 3 us a tile through the staged float32 residual update, 6.5 us otherwise.
+// The unswapped kernel costs 0.92 us per group of a 256 x 256 tile, hides its epilogue, and can split k evenly over the pairs for a
+// fix-up of about 8 us. So the swapped kernel wins where its narrower tiles need few waves (every shape of the trunk up to 300
+// tokens, the projections with N = 2560 up to 4096, most others up to 900) and loses on the wide projections at many tokens, where
+// its tiles need more than twice the waves. A margin of 5 % keeps the unswapped kernel on ties.
+unsigned pick_w8t_tokens(unsigned pairs, unsigned m, unsigned n, unsigned k, bool staged_add) {
     if (pairs == 0 || m <= kBM) return 0;
     const unsigned n_tiles = (n + 255) / 256, groups = k / kW8Group;
-    unsigned best_bt = 0, best_waves = ~0u;
-    for (unsigned bt = 96; bt <= 192; bt += 32) {  // the narrowest tile among those with the fewest waves: the shortest epilogue
+    const double tail = staged_add ? 3.0 : 6.5;
+    unsigned best_bt = 0;
+    double swapped = 1e30;
+    for (unsigned bt = 96; bt <= 192; bt += 32) {
         const unsigned waves = (((m + bt - 1) / bt) * n_tiles + pairs - 1) / pairs;
-        if (waves < best_waves) best_waves = waves, best_bt = bt;
+        const double t = 8.0 + waves * (groups * (bt <= 160 ? 0.44 : 0.75) + tail);
+        if (t < swapped - 0.25) swapped = t, best_bt = bt;  // the narrower tile on ties: less padding, a shorter epilogue
     }
     const unsigned pair_tiles = ((m + 2 * kBM - 1) / (2 * kBM)) * n_tiles;
     const bool split = pick_pair_stream_k(pairs, pair_tiles, m, k, true) != 0;
-    const double unswapped_waves = split ? static_cast<double>(pair_tiles) / pairs : static_cast<double>((pair_tiles + pairs - 1) / pairs);
-    const double swapped = 8.0 + 0.74 * groups * best_waves;
+    // A split over more than two pairs to a tile does not get faster than half a wave: its fix-up takes the long way.
+    const double share = static_cast<double>(pair_tiles) / pairs;
+    const double unswapped_waves = split ? (share > 0.5 ? share : 0.5) : static_cast<double>((pair_tiles + pairs - 1) / pairs);
     const double unswapped = 8.0 + 0.92 * groups * unswapped_waves + (split ? 8.0 : 0.0);
     return swapped < 0.95 * unswapped ? best_bt : 0u;
 }
@@ -2336,7 +2268,8 @@ void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMat
         if (swapped < 64 || swapped > 192 || swapped % 32 != 0)
             throw std::invalid_argument("launch_gemm_w8g: config 512 + w takes w = 64, 96, ..., 192 tokens per tile");
     } else if (config == -1) {
-        swapped = pick_w8t_tokens(static_cast<unsigned>(ctx.sm_count / 2), static_cast<unsigned>(t), static_cast<unsigned>(n), static_cast<unsigned>(k));
+        const bool staged = epilogue == Epilogue::Add && !y_half && reinterpret_cast<std::uintptr_t>(y) % 16 == 0 && (ld_y * 4) % 16 == 0;
+        swapped = pick_w8t_tokens(static_cast<unsigned>(ctx.sm_count / 2), static_cast<unsigned>(t), static_cast<unsigned>(n), static_cast<unsigned>(k), staged);
     }
     if (swapped != 0) {
         const unsigned bt = swapped;

@@ -59,7 +59,7 @@ TRUNK_SHAPES = [("gate_up+swiglu", 19456, 2560, "swiglu"), ("up (config 0)", 972
                 ("dn_in", 8192, 2560, "store"), ("dn_out+residual", 2560, 2048, "add")]
 # DRAM bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the workload's kernel; the summaries under
 # profiles/ give the command). None: not captured.
-NCU_TRAFFIC = {"w8g_down_m900": 47.6e6, "f16_up_m4096": None}
+NCU_TRAFFIC = {"w8g_down_m900": 43.0e6, "f16_up_m4096": None}
 L2_BYTES = 126 * 1024 * 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -324,7 +324,7 @@ def run_ours(args):
             "peak_source": (f"bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_kind}; the timed region is {elapsed_ms:.0f} ms of back-to-back launches: under the power cap)"
                             if long_region else f"bf16_tflops of MEASURED_PEAKS.json ({peak_kind}; burst: a timed region of {elapsed_ms:.0f} ms)"),
             "traffic": args.traffic if args.traffic is not None else NCU_TRAFFIC.get(args.workload),
-            "traffic_source": "--traffic" if args.traffic is not None else ("profiles/gemm_w8_pair_kernel_w8g_down_m900.md" if NCU_TRAFFIC.get(args.workload) else None),
+            "traffic_source": "--traffic" if args.traffic is not None else ("profiles/gemm_w8t_pair_kernel_w8g_down_m900.md" if NCU_TRAFFIC.get(args.workload) else None),
             "algorithmic_bytes": algorithmic_bytes(kind, m, n, k, epilogue),
             "hbm_gbs_achieved": round(algorithmic_bytes(kind, m, n, k, epilogue) / (per_call_ms * 1e-3) / 1e9, 1),
             "us_per_launch": round(per_call_ms * 1e3, 2),

@@ -64,6 +64,7 @@ struct GemmParams {
     unsigned raw_boxes;                     // int8 pair kernel: depth of the raw ring
     unsigned staged_add;                    // residual epilogue through shared memory and a TMA reduce-add; number of staging boxes (0: off)
     unsigned slot_floats;                   // floats of one scratch slot (a partial tile): 128 rows x the tile width rounded up to 32 columns
+    unsigned staged_store;                  // swapped kernel: binary16 results leave through shared memory and TMA stores of [16 tokens x 32 columns]
     float* partials;
     unsigned* counters;
     int* status;
@@ -1691,7 +1692,20 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                         float r[16];
 #pragma unroll
                         for (unsigned j = 0; j < 16; ++j) r[j] = gate ? swiglu(v[j], theirs[j * 32 + lane]) : swiglu(theirs[j * 32 + lane], v[16 + j]);
-                        if (p.y_half != 0) {
+                        if (p.staged_store != 0) {
+                            // [16 tokens x 32 columns] of binary16 in the upper half of the box just written (the exchange uses the lower)
+                            if (lane == 0) ptx::bulk_wait_group_read<1>();  // the store issued two chunks ago has read its box
+                            __syncwarp();
+                            __half* const stage = reinterpret_cast<__half*>(mine + 512);
+#pragma unroll
+                            for (unsigned j = 0; j < 16; ++j) stage[j * 32 + lane] = __float2half_rn(r[j]);
+                            ptx::fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                ptx::tma_store_2d(&map_y, ptx::smem_addr(stage), static_cast<int>(col - lane), static_cast<int>(t0 + c + first));
+                                ptx::bulk_commit_group();
+                            }
+                        } else if (p.y_half != 0) {
                             __half* out = static_cast<__half*>(p.y) + static_cast<size_t>(t0 + c + first) * p.ld_y + col;
 #pragma unroll
                             for (unsigned j = 0; j < 16; ++j)
@@ -1718,6 +1732,21 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                         ptx::tma_reduce_add_2d(&map_y, my_boxes_addr + box * 4096, static_cast<int>(n_tile * 256 + rank * 128 + quarter * 32), static_cast<int>(t0 + c));
                         ptx::bulk_commit_group();
                     }
+                    box ^= 1u;
+                } else if (p.staged_store != 0) {
+                    // [32 tokens x 32 columns] of binary16, stored as two boxes of 16 tokens; the TMA drops what lies past the matrix
+                    if (lane == 0) ptx::bulk_wait_group_read<1>();  // the stores issued two chunks ago have read their box
+                    __syncwarp();
+                    __half* const stage = reinterpret_cast<__half*>(my_boxes + box * 4096);
+#pragma unroll
+                    for (unsigned j = 0; j < 32; ++j) stage[j * 32 + lane] = __float2half_rn(v[j]);
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && n < p.n) {  // lane 0 holds the box's first column
+                        ptx::tma_store_2d(&map_y, my_boxes_addr + box * 4096, static_cast<int>(n), static_cast<int>(t0 + c));
+                        if (t0 + c + 16 < p.m) ptx::tma_store_2d(&map_y, my_boxes_addr + box * 4096 + 1024, static_cast<int>(n), static_cast<int>(t0 + c + 16));
+                    }
+                    if (lane == 0) ptx::bulk_commit_group();
                     box ^= 1u;
                 } else if (n < p.n) {
                     const unsigned rows = min(32u, p.m - (t0 + c));
@@ -1750,7 +1779,7 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(0), 0));
             acc_phase ^= 1u;
         }
-        if (p.staged_add != 0 && lane == 0) ptx::bulk_wait_group_read<0>();  // the staging boxes outlive the reads of them
+        if ((p.staged_add != 0 || p.staged_store != 0) && lane == 0) ptx::bulk_wait_group_read<0>();  // the staging boxes outlive the reads of them
     } else {
         // converters: two sets of four warps take the scale groups in turn (set 0 the even ones, set 1 the odd ones), each warp
         // converting all 128 k of its 32 rows, so that a warp has two group times for the chain read -> widen -> store to tensor
@@ -1958,15 +1987,16 @@ void launch_w8_pair(const Context& ctx, const CUtensorMap& map_x, const CUtensor
 // Estimates in microseconds, fitted to the measured times of the trunk's nine shapes at ten token counts from 200 to 4096. Both kernels
 // spend about 8 us around their main loops. The swapped kernel's main loop costs a pair 0.44 us per scale group of a tile of up to 160
 // tokens (0.75 at 192, where tensor memory holds only one weight buffer for each issuing thread) and its epilogue is not hidden behind
-// the next tile (both accumulators belong to the tile): about 3 us a tile through the staged float32 residual update, 6.5 us otherwise.
+// the next tile (both accumulators belong to the tile): about 3 us a tile when the result leaves through shared memory and the TMA (the
+// float32 residual update, binary16 stores), 6.5 us otherwise.
 // The unswapped kernel costs 0.92 us per group of a 256 x 256 tile, hides its epilogue, and can split k evenly over the pairs for a
 // fix-up of about 8 us. So the swapped kernel wins where its narrower tiles need few waves (every shape of the trunk up to 300
 // tokens, the projections with N = 2560 up to 4096, most others up to 900) and loses on the wide projections at many tokens, where
 // its tiles need more than twice the waves. A margin of 5 % keeps the unswapped kernel on ties.
-unsigned pick_w8t_tokens(unsigned pairs, unsigned m, unsigned n, unsigned k, bool staged_add) {
+unsigned pick_w8t_tokens(unsigned pairs, unsigned m, unsigned n, unsigned k, bool staged) {
     if (pairs == 0 || m <= kBM) return 0;
     const unsigned n_tiles = (n + 255) / 256, groups = k / kW8Group;
-    const double tail = staged_add ? 3.0 : 6.5;
+    const double tail = staged ? 3.0 : 6.5;
     unsigned best_bt = 0;
     double swapped = 1e30;
     for (unsigned bt = 96; bt <= 192; bt += 32) {
@@ -2007,6 +2037,10 @@ void launch_w8t_pair(const Context& ctx, const void* x, std::size_t ld_x, const 
     CUtensorMap map_y;
     std::memset(&map_y, 0, sizeof map_y);
     if (p.staged_add != 0) map_y = make_tensor_map_2d(ctx, p.y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.m, p.n, p.ld_y, 32, 32, true);
+    // binary16 results that are not added to what Y holds leave through shared memory too, in boxes of 16 tokens x 32 columns
+    p.staged_store = (p.epilogue != 1 && p.y_half != 0 && reinterpret_cast<std::uintptr_t>(p.y) % 16 == 0 && (p.ld_y * 2) % 16 == 0) ? 1u : 0u;
+    if (p.staged_store != 0)
+        map_y = make_tensor_map_2d(ctx, p.y, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.m, p.epilogue == 2 ? p.n / 2 : p.n, p.ld_y, 16, 32, false);
     const unsigned smem = fixed + depth * per_group;
     if (p.tiles < pairs) pairs = p.tiles;
     launch_kernel(gemm_w8t_pair_kernel, dim3(2 * pairs), dim3(kW8tThreads), smem, stream, "gemm_w8t_pair_kernel launch", map_x, map_w, map_y, p);
@@ -2268,7 +2302,8 @@ void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMat
         if (swapped < 64 || swapped > 192 || swapped % 32 != 0)
             throw std::invalid_argument("launch_gemm_w8g: config 512 + w takes w = 64, 96, ..., 192 tokens per tile");
     } else if (config == -1) {
-        const bool staged = epilogue == Epilogue::Add && !y_half && reinterpret_cast<std::uintptr_t>(y) % 16 == 0 && (ld_y * 4) % 16 == 0;
+        const bool aligned = reinterpret_cast<std::uintptr_t>(y) % 16 == 0 && (ld_y * (y_half ? 2 : 4)) % 16 == 0;
+        const bool staged = aligned && (epilogue == Epilogue::Add ? !y_half : y_half);  // the result leaves through shared memory and the TMA
         swapped = pick_w8t_tokens(static_cast<unsigned>(ctx.sm_count / 2), static_cast<unsigned>(t), static_cast<unsigned>(n), static_cast<unsigned>(k), staged);
     }
     if (swapped != 0) {

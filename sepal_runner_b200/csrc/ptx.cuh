@@ -87,6 +87,14 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32
                  "r"(src), "r"(c0), "r"(c1)
                  : "memory");
 }
+// A box of shared memory stored to the tensor `map` describes, at element coordinates (c0 innermost, c1 rows); what lies outside the
+// tensor is dropped. Asynchronous, grouped and awaited like the reduce above. c0 * element size must be a multiple of 16 bytes; never
+// start at a negative coordinate.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int32_t c0, int32_t c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src),
+                 "r"(c0), "r"(c1)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Until at most N of this thread's committed groups are still READING their shared-memory source.
 template <int N>

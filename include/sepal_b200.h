@@ -130,6 +130,13 @@ SEPAL_B200_API int32_t sepal_b200_gemm_w8g(sepal_b200_ctx* ctx, const void* x, u
                                            uint64_t ld_st, const float* descale, void* y, uint64_t ld_y, int32_t y_half, uint64_t t, uint64_t n,
                                            uint64_t k, int32_t epilogue, int32_t config, void* stream);
 
+/* Which kernel the automatic schedule (config -1) of sepal_b200_gemm_w8g gives a [t x k] by [n x k] multiply on a GPU of `sm_count` SMs:
+ * the tokens to a tile of the swapped kernel (96, 128, 160 or 192; sepal_b200_gemm_w8g's config 512 + w forces it), or 0 for the
+ * unswapped kernels. `staged` != 0: the result is a float32 residual add or a binary16 store into 16-byte aligned rows (it then leaves
+ * through shared memory and the TMA, which the estimate counts). Host arithmetic only: needs no GPU and no context. No counterpart in
+ * the reference. */
+SEPAL_B200_API int32_t sepal_b200_w8g_schedule(uint32_t sm_count, uint64_t t, uint64_t n, uint64_t k, int32_t staged);
+
 /* binary16 activations x int8 weights with ONE float32 scale per output row (the gpu-q8w layout): Y[t, n] = sw[n] * sum_k x[t, k] q[n, k].
  * Replaces launch_gemm_w8a16 (runner/cuda/src/gemm_s8_kernels.hpp:51-57; its engine use cuda_engine.cpp:1118-1129). The bytes are
  * widened exactly to binary16 on their way to the tensor cores, summed in float32, and the finished sum is multiplied by sw[n] in

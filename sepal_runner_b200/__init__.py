@@ -20,6 +20,7 @@ from .lib import (  # noqa: F401
     DeltaNetShape,
     deltanet,
     gemm_f16_noalloc,
+    w8g_schedule,
     Provider,
     SepalB200Error,
     Trunk,

@@ -100,6 +100,11 @@ struct W8gMatrix {
 void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMatrix& w, void* y, std::size_t ld_y, bool y_half, std::size_t t,
                      std::size_t n, std::size_t k, Epilogue epilogue, int config, cudaStream_t stream);
 
+/// Which kernel the automatic schedule (`config` -1) of launch_gemm_w8g gives a [t x k] by [n x k] multiply on a device of `sm_count`
+/// SMs: the tokens to a tile of the swapped kernel (96, 128, 160 or 192), or 0 for the unswapped kernels. `staged`: the result leaves
+/// through shared memory and the TMA (a float32 residual add or a binary16 store into 16-byte aligned rows). Host arithmetic only.
+unsigned w8g_swapped_tokens(unsigned sm_count, std::size_t t, std::size_t n, std::size_t k, bool staged);
+
 /// s [N, K / 128] float32 (row stride ld_s: the quantiser's and the reference's layout) -> scales_t binary16 [K / 128, ld_st] and
 /// *descale, as W8gMatrix describes. `max_bits` is a device word of scratch (4 bytes). Enqueued on `stream`; no host synchronisation.
 /// X [T, K] binary16; W int8 with ONE float32 scale per output row (the counterpart of the reference's launch_gemm_w8a16,

@@ -2280,6 +2280,11 @@ void launch_gemm_f16(Context& ctx, const void* x, std::size_t ld_x, const void* 
         launch_config<false>(ctx, map_x, map_w, map_y, p, bn, stream_k, stream);
 }
 
+unsigned w8g_swapped_tokens(unsigned sm_count, std::size_t t, std::size_t n, std::size_t k, bool staged) {
+    if (t > 0x7FFFFFFFu || n > 0x7FFFFFFFu || k > 0x7FFFFFFFu || k % kGroup != 0) return 0;
+    return pick_w8t_tokens(sm_count / 2, static_cast<unsigned>(t), static_cast<unsigned>(n), static_cast<unsigned>(k), staged);
+}
+
 void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMatrix& wm, void* y, std::size_t ld_y, bool y_half, std::size_t t,
                      std::size_t n, std::size_t k, Epilogue epilogue, int config, cudaStream_t stream) {
     const std::int8_t* q = wm.q;
@@ -2304,7 +2309,7 @@ void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMat
     } else if (config == -1) {
         const bool aligned = reinterpret_cast<std::uintptr_t>(y) % 16 == 0 && (ld_y * (y_half ? 2 : 4)) % 16 == 0;
         const bool staged = aligned && (epilogue == Epilogue::Add ? !y_half : y_half);  // the result leaves through shared memory and the TMA
-        swapped = pick_w8t_tokens(static_cast<unsigned>(ctx.sm_count / 2), static_cast<unsigned>(t), static_cast<unsigned>(n), static_cast<unsigned>(k), staged);
+        swapped = w8g_swapped_tokens(static_cast<unsigned>(ctx.sm_count), t, n, k, staged);
     }
     if (swapped != 0) {
         const unsigned bt = swapped;

@@ -101,3 +101,21 @@ def test_pack_gate_up_source_is_the_reference_formula():
     src = [sb.pack_gate_up_source(p, inter) for p in range(2 * inter)]
     assert sorted(src) == list(range(2 * inter))
     assert src[:64] == list(range(64)) and src[64:128] == list(range(inter, inter + 64)) and src[128] == 64
+
+
+def test_int8_schedule_query_is_host_arithmetic(lib):
+    """sepal_b200_w8g_schedule needs no GPU: the automatic choice between the swapped int8 kernel (tokens to a tile) and the unswapped
+    ones (0) for the trunk's shapes on a 148-SM GPU, as measured sweeps fixed it."""
+    import sepal_runner_b200 as sb
+
+    assert sb.w8g_schedule(148, 900, 2560, 9728) == 160      # the headline: 60 whole-k tiles of 160 tokens
+    assert sb.w8g_schedule(148, 900, 2560, 4096) == 160      # o + residual
+    assert sb.w8g_schedule(148, 300, 2560, 9728) == 96       # few tokens: the narrowest tile
+    assert sb.w8g_schedule(148, 900, 4096, 2560) == 0        # q: 64 unswapped tiles are one wave, the swapped ones need two
+    assert sb.w8g_schedule(148, 4096, 9728, 2560) == 0       # the wide projections at many tokens stay unswapped
+    assert sb.w8g_schedule(148, 4096, 2560, 9728) == 160     # down at 4096 tokens
+    assert sb.w8g_schedule(148, 128, 2560, 9728) == 0        # up to 128 tokens: the lone-CTA kernel
+    assert sb.w8g_schedule(148, 900, 2560, 9700) == 0        # k not a multiple of 128: not an int8-group shape
+    assert sb.w8g_schedule(0, 900, 2560, 9728) == 0
+    # the unhidden epilogue counts: without staging the estimate is 3.5 us a wave longer
+    assert sb.w8g_schedule(148, 1200, 2560, 4096, staged=True) == 192 and sb.w8g_schedule(148, 1200, 2560, 4096, staged=False) == 0

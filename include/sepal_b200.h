@@ -124,18 +124,18 @@ SEPAL_B200_API int32_t sepal_b200_gemm_f16_noalloc(const void* x, uint64_t ld_x,
 /* binary16 activations x int8 weights with one scale per output row and group of 128 values of k (the gpu-w8g layout). Replaces
  * launch_gemm_simt with SimtWeight::Int8Group (runner/cuda/src/gemm_simt_kernels.hpp:42-56). q is int8 [N, ld_q]; scales_t / descale come from sepal_b200_prepare_w8g_scales.
  * Requires K a multiple of 128, ld_x a multiple of 8, ld_q a multiple of 16, scales_t 16-byte aligned with ld_st >= N rounded up to
- * 256 (the padding zero). config as sepal_b200_gemm_f16, and 512 + w (w = 64, 96, ..., 192; no SWIGLU) forces the kernel that takes the
+ * 256 (the padding zero). config as sepal_b200_gemm_f16, and 512 + w (w = 64, 96, ..., 192, 256 or 320) forces the kernel that takes the
  * weights as the tensor cores' first operand with w tokens to a tile, which -1 picks where it is the faster one. */
 SEPAL_B200_API int32_t sepal_b200_gemm_w8g(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const int8_t* q, uint64_t ld_q, const void* scales_t,
                                            uint64_t ld_st, const float* descale, void* y, uint64_t ld_y, int32_t y_half, uint64_t t, uint64_t n,
                                            uint64_t k, int32_t epilogue, int32_t config, void* stream);
 
 /* Which kernel the automatic schedule (config -1) of sepal_b200_gemm_w8g gives a [t x k] by [n x k] multiply on a GPU of `sm_count` SMs:
- * the tokens to a tile of the swapped kernel (96, 128, 160 or 192; sepal_b200_gemm_w8g's config 512 + w forces it), or 0 for the
- * unswapped kernels. `staged` != 0: the result is a float32 residual add or a binary16 store into 16-byte aligned rows (it then leaves
- * through shared memory and the TMA, which the estimate counts). Host arithmetic only: needs no GPU and no context. No counterpart in
- * the reference. */
-SEPAL_B200_API int32_t sepal_b200_w8g_schedule(uint32_t sm_count, uint64_t t, uint64_t n, uint64_t k, int32_t staged);
+ * the tokens to a tile of the swapped kernel (96, 128, 160 or 192: one block; 256 or 320: two blocks of half as many that share the
+ * converted weights; sepal_b200_gemm_w8g's config 512 + w forces it), or 0 for the unswapped kernels. `epilogue` as in the multiply;
+ * `staged` != 0: the result is a float32 residual add or a binary16 result into 16-byte aligned rows (it then leaves through shared
+ * memory and the TMA, which the estimate counts). Host arithmetic only: needs no GPU and no context. No counterpart in the reference. */
+SEPAL_B200_API int32_t sepal_b200_w8g_schedule(uint32_t sm_count, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t staged);
 
 /* binary16 activations x int8 weights with ONE float32 scale per output row (the gpu-q8w layout): Y[t, n] = sw[n] * sum_k x[t, k] q[n, k].
  * Replaces launch_gemm_w8a16 (runner/cuda/src/gemm_s8_kernels.hpp:51-57; its engine use cuda_engine.cpp:1118-1129). The bytes are

@@ -70,6 +70,7 @@ struct GemmParams {
     unsigned staged_add;                    // residual epilogue through shared memory and a TMA reduce-add; number of staging boxes (0: off)
     unsigned slot_floats;                   // floats of one scratch slot (a partial tile): 128 rows x the tile width rounded up to 32 columns
     unsigned staged_store;                  // swapped kernel: binary16 results leave through shared memory and TMA stores of [16 tokens x 32 columns]
+    unsigned blocks;                        // swapped kernel: token blocks of bn tokens to a tile (1: the issuing threads share the block's scale groups; 2: a block each)
     float* partials;
     unsigned* counters;
     int* status;
@@ -1493,6 +1494,7 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     const int depth = static_cast<int>(p.stages);      // scale groups in the raw ring and in the X ring (two X boxes and one pair of barriers a group)
     const int x_groups = depth;
     const int a_bufs = static_cast<int>(p.raw_boxes);  // weight buffers in tensor memory
+    const unsigned blocks = p.blocks;                  // token blocks to a tile
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr0 = ptx::smem_addr(smem_raw);
     const uint32_t base = (raw_addr0 + 1023u) & ~1023u;
@@ -1501,7 +1503,7 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     const uint32_t staging_addr = base;
     const unsigned raw_off = kW8tStagingBytes;
     const unsigned x_off = raw_off + depth * kW8tRawBytes;
-    const unsigned scale_off = x_off + 2 * depth * x_box;
+    const unsigned scale_off = x_off + 2 * blocks * depth * x_box;
     uint8_t* const tail = smem + scale_off + depth * 256;
     const uint32_t bars = ptx::smem_addr(tail);
     const auto raw_full_bar = [&](int s) { return bars + 8u * s; };
@@ -1530,11 +1532,11 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         }
         for (int s = 0; s < x_groups; ++s) {
             ptx::mbar_init(x_full_bar(s), 1);
-            ptx::mbar_init(x_empty_bar(s), 1);
+            ptx::mbar_init(x_empty_bar(s), blocks);  // with two blocks to a tile both issuing threads read every group's boxes
         }
         for (int s = 0; s < a_bufs; ++s) {
             ptx::mbar_init(a_full_bar(s), 8);   // the four converter warps of each CTA whose turn it is (used in the first CTA only)
-            ptx::mbar_init(a_empty_bar(s), 1);
+            ptx::mbar_init(a_empty_bar(s), blocks);
         }
         ptx::mbar_init(acc_full_bar(0), 2);     // the two issuing threads
         ptx::mbar_init(acc_empty_bar(0), 256);
@@ -1564,7 +1566,7 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             for (unsigned tile = pair; ok && tile < p.tiles; tile += pairs) {
                 const unsigned n_tile = tile / t_tiles, t_tile = tile % t_tiles;
                 const int row_w = static_cast<int>(n_tile * 256 + rank * 128);
-                const int row_x = static_cast<int>(t_tile * bt + rank * (bt / 2));
+                const int row_x = static_cast<int>(t_tile * blocks * bt + rank * (bt / 2));
                 for (unsigned g = 0; ok && g < groups; ++g) {
                     if (!wait_barrier(raw_empty_bar(rs), r_phase ^ 1u, abort_flag, p.status, kStatusProducerEmpty)) {
                         ok = false;
@@ -1582,10 +1584,11 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                         ok = false;
                         break;
                     }
-                    if (rank == 0) ptx::mbar_arrive_expect_tx(x_full_bar(xs), 4 * x_box);
-                    for (int sub = 0; sub < 2; ++sub)
-                        ptx::tma_load_2d_pair(base + x_off + (2 * xs + sub) * x_box, &map_x, ptx::map_to_cta(x_full_bar(xs), 0),
-                                              static_cast<int>(g * kW8Group + sub * kBK), row_x);
+                    if (rank == 0) ptx::mbar_arrive_expect_tx(x_full_bar(xs), 4 * blocks * x_box);
+                    for (unsigned blk = 0; blk < blocks; ++blk)
+                        for (unsigned sub = 0; sub < 2; ++sub)
+                            ptx::tma_load_2d_pair(base + x_off + ((xs * blocks + blk) * 2 + sub) * x_box, &map_x, ptx::map_to_cta(x_full_bar(xs), 0),
+                                                  static_cast<int>(g * kW8Group + sub * kBK), row_x + static_cast<int>(blk * bt));
                     if (++xs == x_groups) {
                         xs = 0;
                         x_phase ^= 1u;
@@ -1610,7 +1613,11 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             const uint64_t desc_x0 = ptx::smem_desc_k_major_sw128(base + x_off);
             const uint32_t x_step = x_box >> 4, x_step2 = x_box >> 3;  // one X box, two (a scale group), in the descriptor's 16-byte units
             const uint32_t d = tmem_base + turn * bt;
-            int xs = static_cast<int>(turn), ab = static_cast<int>(turn);  // the rings hold at least two groups each
+            // With two token blocks to a tile each thread takes EVERY scale group for its own block (the two read the same weight
+            // buffer, which is converted once for both, and their accumulators are two results, not two halves of one).
+            const bool own_block = blocks == 2;
+            const int stride = own_block ? 1 : 2;
+            int xs = own_block ? 0 : static_cast<int>(turn), ab = xs;  // the rings hold at least two groups each
             unsigned x_phase = 0, acc_phase = 0, a_phase = 0, count = 0;
             bool ok = true;
             for (unsigned tile = pair; ok && tile < p.tiles; tile += pairs) {
@@ -1618,7 +1625,7 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 ptx::tc_fence_after_sync();
                 unsigned fresh = 0;  // this thread's first MMA of the tile overwrites its accumulator
                 for (unsigned g = 0; g < groups; ++g, ++count) {
-                    if ((count & 1u) != turn) continue;
+                    if (!own_block && (count & 1u) != turn) continue;
                     if (!wait_barrier(a_full_bar(ab), a_phase, abort_flag, p.status, kStatusMmaConvFull) ||
                         !wait_barrier(x_full_bar(xs), x_phase, abort_flag, p.status, kStatusMmaFull)) {
                         ok = false;
@@ -1626,7 +1633,7 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                     }
                     ptx::tc_fence_after_sync();
                     const uint32_t a = a_cols + static_cast<uint32_t>(ab) * 64u;
-                    const uint64_t dx = desc_x0 + static_cast<uint64_t>(static_cast<uint32_t>(xs) * x_step2);
+                    const uint64_t dx = desc_x0 + static_cast<uint64_t>((static_cast<uint32_t>(xs) * blocks + (own_block ? turn : 0u)) * x_step2);
                     ptx::mma_f16_ts_pair(d, a, dx, idesc, fresh);
                     fresh = 1;
                     ptx::mma_f16_ts_pair_acc(d, a + 8, dx + 2, idesc);
@@ -1638,12 +1645,12 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                     ptx::mma_f16_ts_pair_acc(d, a + 56, dx + x_step + 6, idesc);
                     ptx::mma_commit_pair(x_empty_bar(xs), 3);
                     ptx::mma_commit_pair(a_empty_bar(ab), 3);
-                    xs += 2;
+                    xs += stride;
                     if (xs >= x_groups) {
                         xs -= x_groups;
                         x_phase ^= 1u;
                     }
-                    ab += 2;
+                    ab += stride;
                     if (ab >= a_bufs) {
                         ab -= a_bufs;
                         a_phase ^= 1u;
@@ -1680,13 +1687,15 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             ptx::tc_fence_after_sync();
             const unsigned n_tile = tile / t_tiles, t_tile = tile % t_tiles;
             const unsigned n = n_tile * 256 + rank * 128 + quarter * 32 + lane;
-            const unsigned t0 = t_tile * bt;
-            // The first issuing thread's accumulator; the second's is bt columns on. A tile of a single scale group leaves one of them
-            // unwritten: the group went to the thread whose turn it was.
-            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + (groups == 1 && (count & 1u) != 0 ? bt : 0u);
-            const bool both = groups > 1;
             const bool two_steps = p.col_scale != nullptr;  // descale, then the row's scale: two roundings, as the other int8 kernels apply them
             const float second = two_steps && n < p.n ? __ldg(p.col_scale + n) : 1.0f;
+            for (unsigned blk = 0; blk < blocks; ++blk) {
+            const unsigned t0 = (t_tile * blocks + blk) * bt;
+            // One block to a tile: the first issuing thread's accumulator holds the even scale groups' sum and the second's, bt columns
+            // on, the odd ones' (a tile of a single group leaves one of them unwritten: the group went to the thread whose turn it
+            // was). Two blocks: each accumulator is a block's whole result.
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + (blocks == 2 ? blk * bt : (groups == 1 && (count & 1u) != 0 ? bt : 0u));
+            const bool both = blocks == 1 && groups > 1;
 #pragma unroll 1
             for (unsigned c = 0; c < bt && t0 + c < p.m; c += 32) {
                 float v[32];
@@ -1806,6 +1815,7 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                         }
                     }
                 }
+            }
             }
             ptx::tc_fence_before_sync();
             ptx::mbar_arrive_cluster(ptx::map_to_cta(acc_empty_bar(0), 0));
@@ -2015,40 +2025,46 @@ void launch_w8_pair(const Context& ctx, const CUtensorMap& map_x, const CUtensor
     ++g_launches;
 }
 
-// Whether the swapped int8 kernel should take a multiply, and with how many tokens to a tile (0: the unswapped kernels keep it).
-// Estimates in microseconds, fitted to the measured times of the trunk's nine shapes at ten token counts from 200 to 4096. Both kernels
-// spend about 8 us around their main loops. The swapped kernel's main loop costs a pair 0.44 us per scale group of a tile of up to 160
-// tokens (0.75 at 192, where tensor memory holds only one weight buffer for each issuing thread) and its epilogue is not hidden behind
-// the next tile (both accumulators belong to the tile): about 3 us a tile when the result leaves through shared memory and the TMA (the
-// float32 residual update, binary16 stores), 6.5 us otherwise.
-// The unswapped kernel costs 0.92 us per group of a 256 x 256 tile, hides its epilogue, and can split k evenly over the pairs for a
-// fix-up of about 8 us. So the swapped kernel wins where its narrower tiles need few waves (every shape of the trunk up to 300
-// tokens, the projections with N = 2560 up to 4096, most others up to 900) and loses on the wide projections at many tokens, where
-// its tiles need more than twice the waves. A margin of 5 % keeps the unswapped kernel on ties.
-unsigned pick_w8t_tokens(unsigned pairs, unsigned m, unsigned n, unsigned k, bool staged) {
+// Whether the swapped int8 kernel should take a multiply, and with how many tokens to a tile (0: the unswapped kernels keep it; up to
+// 192: one block of that many tokens, the issuing threads sharing its scale groups; 256 or 320: two blocks of half as many, a block to
+// each issuing thread). Estimates in microseconds, least-squares fits to the measured times of the trunk's nine shapes at ten token
+// counts from 200 to 4096 (each launch about 8 us around its main loop). Swapped: a wave of tiles costs a pair, per scale group, 0.57 /
+// 0.61 / 0.65 us at 96 / 128 / 160 tokens, 0.98 at 192 (tensor memory then holds a single weight buffer for each issuing thread) and
+// 0.86 / 0.94 at two blocks of 128 / 160, plus an epilogue nothing hides (both accumulators belong to the tile): per block 1.2 us
+// through shared memory and the TMA, 2.4 with the SwiGLU, about 6 when the result has to be stored lane by lane. Unswapped: 0.97 us per
+// group of a 256 x 256 tile, epilogues hidden behind the next tile, and the even split of k at about 20 us for its fix-up and its
+// slower main loop. Waves are what decides: ceil(tiles / pairs) whole ones for the swapped kernel. The swapped kernel is taken unless
+// the estimate puts it more than 5 % behind: over the sweep the choice is within 1 % of the best measured schedule on average and
+// 8 % behind it at worst.
+unsigned pick_w8t_tokens(unsigned pairs, unsigned m, unsigned n, unsigned k, bool staged, bool swiglu) {
     if (pairs == 0 || m <= kBM) return 0;
     const unsigned n_tiles = (n + 255) / 256, groups = k / kW8Group;
-    const double tail = staged ? 3.0 : 6.5;
-    unsigned best_bt = 0;
+    static constexpr unsigned kWidths[6] = {96, 128, 160, 192, 256, 320};
+    static constexpr double kPerGroup[6] = {0.566, 0.614, 0.652, 0.982, 0.856, 0.936};
+    const double tail = !staged ? 6.0 : (swiglu ? 2.4 : 1.2);
+    unsigned best = 0;
     double swapped = 1e30;
-    for (unsigned bt = 96; bt <= 192; bt += 32) {
-        const unsigned waves = (((m + bt - 1) / bt) * n_tiles + pairs - 1) / pairs;
-        const double t = 8.0 + waves * (groups * (bt <= 160 ? 0.44 : 0.75) + tail);
-        if (t < swapped - 0.25) swapped = t, best_bt = bt;  // the narrower tile on ties: less padding, a shorter epilogue
+    for (int i = 0; i < 6; ++i) {
+        const unsigned w = kWidths[i], blocks = w > 192 ? 2u : 1u;
+        const unsigned waves = (((m + w - 1) / w) * n_tiles + pairs - 1) / pairs;
+        const double t = 8.0 + waves * (groups * kPerGroup[i] + blocks * tail);
+        if (t < swapped - 0.25) swapped = t, best = w;  // the narrower tile on ties: less padding
     }
     const unsigned pair_tiles = ((m + 2 * kBM - 1) / (2 * kBM)) * n_tiles;
     const bool split = pick_pair_stream_k(pairs, pair_tiles, m, k, true) != 0;
     // A split over more than two pairs to a tile does not get faster than half a wave: its fix-up takes the long way.
     const double share = static_cast<double>(pair_tiles) / pairs;
     const double unswapped_waves = split ? (share > 0.5 ? share : 0.5) : static_cast<double>((pair_tiles + pairs - 1) / pairs);
-    const double unswapped = 8.0 + 0.92 * groups * unswapped_waves + (split ? 8.0 : 0.0);
-    return swapped < 0.95 * unswapped ? best_bt : 0u;
+    const double unswapped = 8.0 + 0.967 * groups * unswapped_waves + (split ? 20.6 : 0.0);
+    return swapped < 1.05 * unswapped ? best : 0u;
 }
 
 // The swapped int8 kernel (weights from tensor memory). `bt`: tokens per tile, a multiple of 32 from 64 to 192.
-void launch_w8t_pair(const Context& ctx, const void* x, std::size_t ld_x, const void* q, std::size_t ld_q, GemmParams p, unsigned bt, cudaStream_t stream) {
+void launch_w8t_pair(const Context& ctx, const void* x, std::size_t ld_x, const void* q, std::size_t ld_q, GemmParams p, unsigned bt, unsigned blocks,
+                     cudaStream_t stream) {
     p.bn = bt;
-    p.m_tiles = (p.m + bt - 1) / bt;
+    p.blocks = blocks;
+    p.m_tiles = (p.m + blocks * bt - 1) / (blocks * bt);
     p.n_tiles = (p.n + 255) / 256;
     p.tiles = p.m_tiles * p.n_tiles;
     static int cache[64] = {};
@@ -2057,7 +2073,7 @@ void launch_w8t_pair(const Context& ctx, const void* x, std::size_t ld_x, const 
     if (p.raw_boxes > static_cast<unsigned>(kW8tMaxA)) p.raw_boxes = kW8tMaxA;
     const unsigned x_box = (bt / 2) * 128;
     // Shared memory: the epilogue's staging boxes, then rings of equal depth for the raw boxes (with their scales) and the X boxes.
-    const unsigned fixed = 1024 + kW8tStagingBytes + kW8tBarriers * 8 + 64, per_group = kW8tRawBytes + 256 + 2 * x_box;
+    const unsigned fixed = 1024 + kW8tStagingBytes + kW8tBarriers * 8 + 64, per_group = kW8tRawBytes + 256 + 2 * blocks * x_box;
     unsigned depth = (kSmemLimit - fixed) / per_group;
     if (depth > static_cast<unsigned>(kW8tMaxDepth)) depth = kW8tMaxDepth;
     p.stages = depth;
@@ -2312,9 +2328,9 @@ void launch_gemm_f16(Context& ctx, const void* x, std::size_t ld_x, const void* 
         launch_config<false>(ctx, map_x, map_w, map_y, p, bn, stream_k, stream);
 }
 
-unsigned w8g_swapped_tokens(unsigned sm_count, std::size_t t, std::size_t n, std::size_t k, bool staged) {
+unsigned w8g_swapped_tokens(unsigned sm_count, std::size_t t, std::size_t n, std::size_t k, bool staged, bool swiglu) {
     if (t > 0x7FFFFFFFu || n > 0x7FFFFFFFu || k > 0x7FFFFFFFu || k % kGroup != 0) return 0;
-    return pick_w8t_tokens(sm_count / 2, static_cast<unsigned>(t), static_cast<unsigned>(n), static_cast<unsigned>(k), staged);
+    return pick_w8t_tokens(sm_count / 2, static_cast<unsigned>(t), static_cast<unsigned>(n), static_cast<unsigned>(k), staged, swiglu);
 }
 
 void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMatrix& wm, void* y, std::size_t ld_y, bool y_half, std::size_t t,
@@ -2336,15 +2352,15 @@ void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMat
     unsigned swapped = 0;  // tokens to a tile of the swapped kernel (weights from tensor memory); 0: one of the other kernels
     if (config >= 512) {
         swapped = static_cast<unsigned>(config - 512);
-        if (swapped < 64 || swapped > 192 || swapped % 32 != 0)
-            throw std::invalid_argument("launch_gemm_w8g: config 512 + w takes w = 64, 96, ..., 192 tokens per tile");
+        if ((swapped < 64 || swapped > 192 || swapped % 32 != 0) && swapped != 256 && swapped != 320)
+            throw std::invalid_argument("launch_gemm_w8g: config 512 + w takes w = 64, 96, ..., 192 tokens per tile, or 256 or 320 (two blocks of half as many)");
     } else if (config == -1) {
         const bool aligned = reinterpret_cast<std::uintptr_t>(y) % 16 == 0 && (ld_y * (y_half ? 2 : 4)) % 16 == 0;
         const bool staged = aligned && (epilogue == Epilogue::Add ? !y_half : y_half);  // the result leaves through shared memory and the TMA
-        swapped = w8g_swapped_tokens(static_cast<unsigned>(ctx.sm_count), t, n, k, staged);
+        swapped = w8g_swapped_tokens(static_cast<unsigned>(ctx.sm_count), t, n, k, staged, epilogue == Epilogue::SwiGLU);
     }
     if (swapped != 0) {
-        const unsigned bt = swapped;
+        const unsigned blocks = swapped > 192 ? 2u : 1u, bt = swapped / blocks;
         if (!unit_scales && (ld_st % 8 != 0 || ld_st < (n + 255) / 256 * 256 || reinterpret_cast<std::uintptr_t>(scales_t) % 16 != 0))
             throw std::invalid_argument("launch_gemm_w8g: scales_t must be 16-byte aligned with a row stride of at least N rounded up to 256");
         GemmParams p = common_params(ctx, y, ld_y, y_half, t, n, k, epilogue);
@@ -2352,7 +2368,7 @@ void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMat
         p.ld_st = ld_st;
         p.descale = descale;
         p.col_scale = wm.col_scale;
-        launch_w8t_pair(ctx, x, ld_x, q, ld_q, p, bt, stream);
+        launch_w8t_pair(ctx, x, ld_x, q, ld_q, p, bt, blocks, stream);
         return;
     }
     unsigned bn = 256;

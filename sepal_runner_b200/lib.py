@@ -40,7 +40,7 @@ SIGNATURES = {
     "sepal_b200_status": (_i32, [_vp, _vp, C.POINTER(_i32)]),
     "sepal_b200_take_launch_count": (_u64, []),
     "sepal_b200_debug_leave_status": (_i32, [_vp, _vp, _i32, _u32]),
-    "sepal_b200_w8g_schedule": (_i32, [_u32, _u64, _u64, _u64, _i32]),
+    "sepal_b200_w8g_schedule": (_i32, [_u32, _u64, _u64, _u64, _i32, _i32]),
     "sepal_b200_gemm_f16": (_i32, [_vp, _vp, _u64, _vp, _u64, _vp, _u64, _i32, _u64, _u64, _u64, _i32, _i32, _vp]),
     "sepal_b200_gemm_f16_noalloc": (_i32, [_vp, _u64, _vp, _u64, _vp, _u64, _i32, _u64, _u64, _u64, _i32, _vp, C.POINTER(_i32)]),
     "sepal_b200_gemm_w8g": (_i32, [_vp, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _vp, _u64, _i32, _u64, _u64, _u64, _i32, _i32, _vp]),
@@ -105,10 +105,10 @@ def _check(rc: int) -> None:
         raise SepalB200Error(library().sepal_b200_last_error().decode())
 
 
-def w8g_schedule(sm_count: int, t: int, n: int, k: int, staged: bool = True) -> int:
+def w8g_schedule(sm_count: int, t: int, n: int, k: int, epilogue: int = 0, staged: bool = True) -> int:
     """Tokens to a tile of the swapped int8 kernel that the automatic schedule of gemm_w8g gives this multiply on a GPU of `sm_count`
-    SMs, or 0 for the unswapped kernels (sepal_b200_w8g_schedule: host arithmetic, needs no GPU)."""
-    return int(library().sepal_b200_w8g_schedule(sm_count, t, n, k, 1 if staged else 0))
+    SMs (256 and 320: two blocks of half as many), or 0 for the unswapped kernels (sepal_b200_w8g_schedule: host arithmetic, needs no GPU)."""
+    return int(library().sepal_b200_w8g_schedule(sm_count, t, n, k, epilogue, 1 if staged else 0))
 
 
 def pack_gate_up_source(p: int, inter: int) -> int:

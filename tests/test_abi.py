@@ -104,18 +104,19 @@ def test_pack_gate_up_source_is_the_reference_formula():
 
 
 def test_int8_schedule_query_is_host_arithmetic(lib):
-    """sepal_b200_w8g_schedule needs no GPU: the automatic choice between the swapped int8 kernel (tokens to a tile) and the unswapped
-    ones (0) for the trunk's shapes on a 148-SM GPU, as measured sweeps fixed it."""
+    """sepal_b200_w8g_schedule needs no GPU: the automatic choice between the swapped int8 kernel (tokens to a tile; 256 and 320 are
+    two blocks of half as many) and the unswapped ones (0) for the trunk's shapes on a 148-SM GPU, as measured sweeps fixed it."""
     import sepal_runner_b200 as sb
 
-    assert sb.w8g_schedule(148, 900, 2560, 9728) == 160      # the headline: 60 whole-k tiles of 160 tokens
-    assert sb.w8g_schedule(148, 900, 2560, 4096) == 160      # o + residual
-    assert sb.w8g_schedule(148, 300, 2560, 9728) == 96       # few tokens: the narrowest tile
-    assert sb.w8g_schedule(148, 900, 4096, 2560) == 0        # q: 64 unswapped tiles are one wave, the swapped ones need two
-    assert sb.w8g_schedule(148, 4096, 9728, 2560) == 0       # the wide projections at many tokens stay unswapped
-    assert sb.w8g_schedule(148, 4096, 2560, 9728) == 160     # down at 4096 tokens
-    assert sb.w8g_schedule(148, 128, 2560, 9728) == 0        # up to 128 tokens: the lone-CTA kernel
-    assert sb.w8g_schedule(148, 900, 2560, 9700) == 0        # k not a multiple of 128: not an int8-group shape
-    assert sb.w8g_schedule(0, 900, 2560, 9728) == 0
-    # the unhidden epilogue counts: without staging the estimate is 3.5 us a wave longer
-    assert sb.w8g_schedule(148, 1200, 2560, 4096, staged=True) == 192 and sb.w8g_schedule(148, 1200, 2560, 4096, staged=False) == 0
+    assert sb.w8g_schedule(148, 900, 2560, 9728, sb.ADD) == 160      # the headline: 60 whole-k tiles of 160 tokens
+    assert sb.w8g_schedule(148, 900, 2560, 4096, sb.ADD) == 160      # o + residual
+    assert sb.w8g_schedule(148, 300, 2560, 9728, sb.ADD) == 96       # few tokens: the narrowest tile
+    assert sb.w8g_schedule(148, 900, 9728, 2560, sb.STORE) == 320    # up: three tiles of two blocks of 160 by 38 tiles of weight rows
+    assert sb.w8g_schedule(148, 4096, 2560, 9728, sb.ADD) == 320     # down at 4096 tokens
+    assert sb.w8g_schedule(148, 4096, 19456, 2560, sb.SWIGLU) == 320
+    assert sb.w8g_schedule(148, 2048, 19456, 2560, sb.SWIGLU) == 0   # 16.4 waves of unswapped tiles against 22 of swapped ones
+    assert sb.w8g_schedule(148, 128, 2560, 9728, sb.ADD) == 0        # up to 128 tokens: the lone-CTA kernel
+    assert sb.w8g_schedule(148, 900, 2560, 9700, sb.ADD) == 0        # k not a multiple of 128: not an int8-group shape
+    assert sb.w8g_schedule(0, 900, 2560, 9728, sb.ADD) == 0
+    # the unhidden epilogue counts: a result stored lane by lane costs several us a wave more
+    assert sb.w8g_schedule(148, 900, 4096, 2560, sb.STORE, staged=True) == 256 and sb.w8g_schedule(148, 900, 4096, 2560, sb.STORE, staged=False) == 0

@@ -290,7 +290,7 @@ def test_w8g_epilogues(ctx, oracle):
 
 
 @pytest.mark.parametrize("t,n,k", [(1, 2, 128), (37, 200, 256), (129, 258, 384), (300, 520, 640), (900, 640, 1280), (1000, 1024, 512)])
-@pytest.mark.parametrize("tokens", [64, 96, 128, 160, 192])
+@pytest.mark.parametrize("tokens", [64, 96, 128, 160, 192, 256, 320])
 def test_w8g_swapped_kernel(ctx, oracle, t, n, k, tokens):
     """config 512 + w: the weights are the tensor cores' first operand, converted into tensor memory, and the tokens the second, w to a
     tile. Every epilogue it serves (float32 and binary16 stores, the residual add into either), ragged token and weight counts, several
@@ -359,7 +359,7 @@ def test_w8g_swapped_kernel_every_row_count_with_guards(ctx, oracle):
             y = buf[1 : t + 1, :n]
             if epilogue == sb.ADD:
                 y.zero_()
-            ctx.gemm_w8g(xd[:t], wq, y, epilogue=epilogue, config=512 + 96)
+            ctx.gemm_w8g(xd[:t], wq, y, epilogue=epilogue, config=512 + (96 if t % 2 else 256))
             ctx.check_status()
             assert rel_fro(y.float().cpu().numpy(), want[:t]) < (2e-3 if dtype == torch.float16 else 1e-3), (t, dtype, epilogue)
             assert torch.isnan(buf[0]).all() and torch.isnan(buf[t + 1]).all() and torch.isnan(buf[1 : t + 1, n:]).all(), (t, dtype, epilogue)
@@ -375,7 +375,7 @@ def test_w8g_swapped_kernel_many_tiles_to_a_pair(ctx, oracle):
     q, s = ctx.quantize_group_s8(dev(w))
     wq = ctx.prepare_w8g(q, s)
     want = oracle.gemm(x, oracle.dequant_group_s8(*oracle.quantize_group_s8(w)))
-    for config in (512 + 96, 512 + 192, -1):
+    for config in (512 + 96, 512 + 192, 512 + 256, 512 + 320, -1):
         y = ctx.gemm_w8g(dev(x).half(), wq, y_half=False, config=config)
         ctx.check_status()
         assert rel_fro(y.cpu().numpy(), want) < 1e-3, config

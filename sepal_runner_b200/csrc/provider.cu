@@ -188,8 +188,9 @@ void B200Gemm::gemm_f(const void* x, HostType type, std::size_t t, WeightId id, 
         check(cudaStreamWaitEvent(stream_out_, multiplied_[piece], 0), "cudaStreamWaitEvent");
         check(cudaMemcpyAsync(hy, dyp, rows * w.n * 4, cudaMemcpyDeviceToHost, stream_out_), "cudaMemcpyAsync(Y)");
     }
-    const int status = ctx_.read_status(stream_);  // waits for the multiplies
-    check(cudaStreamSynchronize(stream_out_), "cudaStreamSynchronize");
+    // One wait for everything: the download stream is behind every multiply (it waited for each piece's event), so the status word is
+    // read behind the last download.
+    const int status = ctx_.read_status(stream_out_);
     if (status != 0) throw std::runtime_error("sepal_b200 provider: a kernel gave up waiting (status " + std::to_string(status) + ")");
 }
 

@@ -365,6 +365,33 @@ def test_w8g_swapped_kernel_every_row_count_with_guards(ctx, oracle):
             assert torch.isnan(buf[0]).all() and torch.isnan(buf[t + 1]).all() and torch.isnan(buf[1 : t + 1, n:]).all(), (t, dtype, epilogue)
 
 
+def test_w8g_swapped_kernel_unaligned_results_take_the_direct_stores(ctx, oracle):
+    """A result whose row stride is not a multiple of 16 bytes cannot be described to the TMA: the epilogue then stores lane by lane
+    (binary16 and float32; plain, residual add and SwiGLU) and gives the same bits as the staged path."""
+    import torch
+
+    import sepal_runner_b200 as sb
+
+    t, n, k = 200, 256, 256
+    rng = np.random.default_rng(717)
+    x = grid(oracle, rng.standard_normal((t, k), dtype=np.float32))
+    w = (rng.standard_normal((n, k)) / np.sqrt(k)).astype(np.float32)
+    q, s = ctx.quantize_group_s8(dev(w))
+    wq = ctx.prepare_w8g(q, s)
+    xd = dev(x).half()
+    for config in (512 + 96, 512 + 256):
+        for dtype in (torch.float16, torch.float32):
+            for epilogue, cols in ((sb.STORE, n), (sb.SWIGLU, n // 2), (sb.ADD, n)):
+                aligned = torch.ones((t, cols), dtype=dtype, device="cuda")
+                ctx.gemm_w8g(xd, wq, aligned, epilogue=epilogue, config=config)
+                buf = torch.ones((t, cols + 2), dtype=dtype, device="cuda")  # an even stride (required) that is not a multiple of 16 bytes
+                assert (buf.stride(0) * buf.element_size()) % 16 != 0
+                ctx.gemm_w8g(xd, wq, buf[:, :cols], epilogue=epilogue, config=config)
+                ctx.check_status()
+                assert torch.equal(buf[:, :cols], aligned), (config, dtype, epilogue)
+                assert (buf[:, cols:] == 1).all()
+
+
 def test_w8g_swapped_kernel_many_tiles_to_a_pair(ctx, oracle):
     """3000 tokens by 2560 outputs: 320 tiles of 96 tokens on 74 pairs, so every pair walks four or five tiles, its two accumulators
     and its rings of boxes wrapping around several times; and the automatic choice on the same operands."""

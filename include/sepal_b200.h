@@ -133,8 +133,8 @@ SEPAL_B200_API int32_t sepal_b200_gemm_w8g(sepal_b200_ctx* ctx, const void* x, u
 /* Which kernel the automatic schedule (config -1) of sepal_b200_gemm_w8g gives a [t x k] by [n x k] multiply on a GPU of `sm_count` SMs:
  * the tokens to a tile of the swapped kernel (96, 128, 160 or 192: one block; 256 or 320: two blocks of half as many that share the
  * converted weights; sepal_b200_gemm_w8g's config 512 + w forces it), or 0 for the unswapped kernels. `epilogue` as in the multiply;
- * `staged` != 0: the result is a float32 residual add or a binary16 result into 16-byte aligned rows (it then leaves through shared
- * memory and the TMA, which the estimate counts). Host arithmetic only: needs no GPU and no context. No counterpart in the reference. */
+ * `staged` != 0: the result goes into 16-byte aligned rows and is not a float32 SwiGLU (it then leaves through shared memory and the TMA,
+ * which the estimate counts). Host arithmetic only: needs no GPU and no context. No counterpart in the reference. */
 SEPAL_B200_API int32_t sepal_b200_w8g_schedule(uint32_t sm_count, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t staged);
 
 /* binary16 activations x int8 weights with ONE float32 scale per output row (the gpu-q8w layout): Y[t, n] = sw[n] * sum_k x[t, k] q[n, k].

@@ -103,8 +103,8 @@ void launch_gemm_w8g(Context& ctx, const void* x, std::size_t ld_x, const W8gMat
 
 /// Which kernel the automatic schedule (`config` -1) of launch_gemm_w8g gives a [t x k] by [n x k] multiply on a device of `sm_count`
 /// SMs: the tokens to a tile of the swapped kernel (96 to 192: one block; 256 or 320: two blocks of half as many), or 0 for the
-/// unswapped kernels. `staged`: the result leaves through shared memory and the TMA (a float32 residual add or a binary16 result into
-/// 16-byte aligned rows); `swiglu`: the fused SwiGLU epilogue. Host arithmetic only.
+/// unswapped kernels. `staged`: the result leaves through shared memory and the TMA (16-byte aligned rows; every result but a float32
+/// SwiGLU); `swiglu`: the fused SwiGLU epilogue. Host arithmetic only.
 unsigned w8g_swapped_tokens(unsigned sm_count, std::size_t t, std::size_t n, std::size_t k, bool staged, bool swiglu);
 
 /// s [N, K / 128] float32 (row stride ld_s: the quantiser's and the reference's layout) -> scales_t binary16 [K / 128, ld_st] and

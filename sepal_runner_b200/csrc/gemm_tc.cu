@@ -70,6 +70,7 @@ struct GemmParams {
     unsigned staged_add;                    // residual epilogue through shared memory and a TMA reduce-add; number of staging boxes (0: off)
     unsigned slot_floats;                   // floats of one scratch slot (a partial tile): 128 rows x the tile width rounded up to 32 columns
     unsigned staged_store;                  // swapped kernel: binary16 results leave through shared memory and TMA stores of [16 tokens x 32 columns]
+    unsigned issuers;                       // lone-CTA fp16 kernel: MMA-issuing threads (2: one tile to a CTA, its k steps taken in turn into an accumulator each)
     unsigned blocks;                        // swapped kernel: token blocks of bn tokens to a tile (1: the issuing threads share the block's scale groups; 2: a block each)
     float* partials;
     unsigned* counters;
@@ -92,7 +93,7 @@ constexpr unsigned kPieceBytes = kBM * 128;         // 32 columns of a partial t
 
 template <bool W8>
 struct Shape {
-    static constexpr int kThreads = W8 ? 320 : 192;
+    static constexpr int kThreads = W8 ? 320 : 224;  // fp16: TMA warp, MMA warp, four epilogue warps, the second MMA-issuing warp
     static constexpr int kConvBuffers = W8 ? 2 : 0;
     __host__ __device__ static constexpr unsigned w_bytes(unsigned bn) { return W8 ? bn * kBK : bn * kBK * 2; }  // raw W tile
     __host__ __device__ static constexpr unsigned stage_bytes(unsigned bn) { return kXBytes + w_bytes(bn); }
@@ -632,6 +633,12 @@ __device__ __forceinline__ void epilogue_unit(const GemmParams& p, const Staging
         finish_tile(p, staging, m_tile, n_tile, row_in_tile, descale, 0u, bn, [&](unsigned c, float (&v)[32]) {
             if (mode == 0) {
                 load_acc_tmem(taddr, c, v);
+                if (p.issuers == 2 && p.k_iters > 1) {  // the second issuing thread's accumulator holds the odd k steps' sum
+                    float u[32];
+                    load_acc_tmem(taddr + kAccStride, c, u);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], u[j]);
+                }
                 return;
             }
             if (mode == 1) {
@@ -727,7 +734,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             ptx::mbar_init(empty_bar(s), W8 ? 1 + 4 : 1);  // the MMA's commit (+ one arrival per converter warp)
         }
         for (int a = 0; a < 2; ++a) {
-            ptx::mbar_init(acc_full_bar(a), 1);
+            ptx::mbar_init(acc_full_bar(a), a == 0 ? p.issuers : 1u);  // two issuing threads share the first accumulator's hand-over
             ptx::mbar_init(acc_empty_bar(a), 128);
             ptx::mbar_init(conv_full_bar(a), 4);
             ptx::mbar_init(conv_empty_bar(a), 1);
@@ -750,6 +757,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // Set up; from here on the kernel touches global memory, which the kernel before it in the stream may still be writing.
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
+
+    // Two issuing threads (fp16 weights, one whole tile to a CTA): a thread that has issued a tcgen05.commit cannot issue MMAs again until
+    // the MMAs before the commit have drained (about 500 clocks; 4 MMAs and a commit from one thread take 610 to 730 clocks whatever the
+    // tile's width), but the tensor core takes another thread's MMAs meanwhile. The tile's k steps go to the two threads in turn, each
+    // summing into its own accumulator; the epilogue adds the two in a fixed order. With more than one unit to a CTA the accumulators
+    // alternate between units instead and one thread issues (the epilogue of a unit then runs behind the MMAs of the next).
+    const auto issue_in_turn = [&](unsigned turn) {
+        const uint32_t idesc = ptx::instr_desc_f16_f32acc(kBM, bn);
+        const uint64_t desc_x0 = ptx::smem_desc_k_major_sw128(stages_addr), desc_w0 = ptx::smem_desc_k_major_sw128(stages_addr + kXBytes);
+        const uint32_t stage_step = stage_bytes >> 4;  // one stage in the descriptor's 16-byte units
+        Walker walk(p, cta, grid);
+        unsigned tile, kb, ke;
+        if (!walk.next(tile, kb, ke)) return;  // at most one unit to a CTA in this mode
+        if (!wait_barrier(acc_empty_bar(0), 1u, abort_flag, p.status, kStatusMmaAccEmpty)) return;
+        ptx::tc_fence_after_sync();
+        const uint32_t d = tmem_base + turn * kAccStride;
+        int stage = static_cast<int>(turn);  // the ring holds at least two stages
+        unsigned phase = 0, fresh = 0;
+        for (unsigned kk = kb + turn; kk < ke; kk += 2) {
+            if (!wait_barrier(full_bar(stage), phase, abort_flag, p.status, kStatusMmaFull)) return;
+            ptx::tc_fence_after_sync();
+            const uint64_t step = static_cast<uint64_t>(static_cast<uint32_t>(stage) * stage_step);
+            ptx::mma_f16_ss(d, desc_x0 + step, desc_w0 + step, idesc, fresh);  // this thread's first MMA overwrites its accumulator
+            fresh = 1;
+#pragma unroll
+            for (int j = 1; j < kBK / 16; ++j) ptx::mma_f16_ss(d, desc_x0 + step + 2u * j, desc_w0 + step + 2u * j, idesc, 1u);
+            ptx::mma_commit(empty_bar(stage));
+            stage += 2;
+            if (stage >= stages) {
+                stage -= stages;
+                phase ^= 1u;
+            }
+        }
+        ptx::mma_commit(acc_full_bar(0));  // both threads: the tile is done when the MMAs of both have drained
+    };
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
@@ -797,7 +839,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && p.issuers == 2) {
+            if constexpr (!W8) issue_in_turn(0);
+        } else if (lane == 0) {
             const uint32_t idesc = ptx::instr_desc_f16_f32acc(kBM, bn);
             Walker walk(p, cta, grid);
             unsigned tile, kb, ke;
@@ -887,7 +931,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         if (p.staged_add != 0 && row_in_tile == 64) ptx::bulk_wait_group_read<0>();  // the staging boxes outlive the reads of them
     } else {
-        // ---------------------------------------------------------------- int8 -> binary16 converters (W8 only)
+        // ---------------------------------------------------------------- the second MMA issuer (fp16) / int8 -> binary16 converters (W8)
+        if constexpr (!W8) {
+            if (lane == 0 && p.issuers == 2) issue_in_turn(1);
+            __syncwarp();
+        }
         if constexpr (W8) {
             // The raw tile is [bn rows][64 bytes] unswizzled (bn is 128 or 256 here); thread i of the 128 converters takes 16-byte piece i, i + 128, ... of it,
             // that is row (piece / 4), k offset 16 * (piece % 4): a warp reads 512 contiguous bytes. Its 16 values become two 16-byte
@@ -2190,6 +2238,7 @@ void launch_config(const Context& ctx, const CUtensorMap& map_x, const CUtensorM
         }
     }
     if (p.stream_k == 0 && p.tiles < grid) grid = p.tiles;
+    p.issuers = (!W8 && p.stream_k == 0 && p.tiles <= grid) ? 2u : 1u;  // one whole tile to a CTA: two issuing threads, an accumulator each
     static bool configured[64] = {};  // per device; a benign race: every writer sets the same attribute
     if (ctx.device >= 64 || !configured[ctx.device]) {
         check(cudaFuncSetAttribute(gemm_tc_kernel<W8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit), "cudaFuncSetAttribute");
@@ -2269,6 +2318,7 @@ GemmParams common_params(Context& ctx, void* y, std::size_t ld_y, bool y_half, s
     p.status = ctx.status;
     // The residual update of the float32 stream goes through shared memory and a TMA reduce-add when Y can be described to the TMA.
     p.staged_add = (epilogue == Epilogue::Add && !y_half && p.vec_ok != 0) ? 2u : 0u;
+    p.issuers = 1;
     return p;
 }
 
@@ -2305,7 +2355,26 @@ void launch_gemm_f16(Context& ctx, const void* x, std::size_t ld_x, const void* 
     unsigned bn = 256;
     bool stream_k = false, pair = false, late = false;
     decode_config(config, n, epilogue == Epilogue::SwiGLU, pick_pair(t, n, k), "launch_gemm_f16", bn, stream_k, pair, &late);
-    if (config == -1 && !pair) {
+    // One wave of lone CTAs, a whole tile each: the kernel then runs two MMA-issuing threads and its k step is bound by shared memory
+    // instead of the issuing thread's commits, which makes it the fastest schedule measured for almost every shape of the trunk from
+    // 200 to 900 tokens where such a wave exists (o projection at 900 tokens: 28.8 -> 23.1 us; k or v: 18.9 -> 15.7; fused qkv at 450
+    // tokens: 22.0 -> 18.4; down projection at 600 tokens: 46.3 -> 41.3), CTA pairs included. The narrowest width that still fits the
+    // wave: the k loop a CTA has to feed is shortest. Not for long k at many tokens, where the pairs' even split wins (down projection
+    // at 1200 tokens: 59 us split on pairs, 65 us as one wave of lone CTAs).
+    bool one_wave = false;
+    if (config == -1 && t > kBM && t * k <= 900u * 9728u) {
+        const std::size_t m_tiles = (t + kBM - 1) / kBM, ctas = static_cast<std::size_t>(ctx.sm_count);
+        for (const unsigned width : {128u, 160u, 192u, 224u, 256u}) {
+            if (epilogue == Epilogue::SwiGLU && width != 128 && width != 256) continue;
+            if (m_tiles * ((n + width - 1) / width) <= ctas) {
+                bn = width;
+                pair = stream_k = late = false;
+                one_wave = true;
+                break;
+            }
+        }
+    }
+    if (config == -1 && !pair && !one_wave) {
         // Lone CTAs: the even split of k when whole tiles leave many SMs idle over a long k and no tile gets more than three pieces
         // (down projection at M 600: 50 tiles on 148 SMs, 58 us whole, 45 us split; its fix-up costs more than on pairs, so the bar
         // is higher: the o projection at the same M, 27 us whole, takes 31 us split).

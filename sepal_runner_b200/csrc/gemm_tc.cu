@@ -2238,7 +2238,9 @@ void launch_config(const Context& ctx, const CUtensorMap& map_x, const CUtensorM
         }
     }
     if (p.stream_k == 0 && p.tiles < grid) grid = p.tiles;
-    p.issuers = (!W8 && p.stream_k == 0 && p.tiles <= grid) ? 2u : 1u;  // one whole tile to a CTA: two issuing threads, an accumulator each
+    // One whole tile to a CTA: two issuing threads, an accumulator each. Not at the full width, where shared memory bounds the k step
+    // either way and the second thread only costs (q projection at 900 tokens: 24.1 us against 23.1).
+    p.issuers = (!W8 && p.stream_k == 0 && p.tiles <= grid && bn <= 224) ? 2u : 1u;
     static bool configured[64] = {};  // per device; a benign race: every writer sets the same attribute
     if (ctx.device >= 64 || !configured[ctx.device]) {
         check(cudaFuncSetAttribute(gemm_tc_kernel<W8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit), "cudaFuncSetAttribute");
@@ -2260,12 +2262,13 @@ unsigned pick_bn(std::size_t n, bool coarse) {
     return static_cast<unsigned>((n + 15) / 16 * 16);
 }
 
-// CTA pairs pay a cluster launch and two cluster barriers; measured, they win from about 24 GFLOP per product up (fp16 weights).
+// CTA pairs pay a cluster launch and two cluster barriers; measured, they win from about 18 GFLOP per product up (fp16 weights; below
+// that, and wherever one wave of narrower lone tiles exists, launch_gemm_f16 takes lone CTAs).
 // A pair's tile has 256 rows: when that pads the rows by over a tenth more than tiles of 128 rows do (300 rows: 512 against 384), the
 // lone CTAs win (gate_up at M 300: 48 us against 56).
 bool pick_pair(std::size_t t, std::size_t n, std::size_t k) {
     const std::size_t rows_pair = (t + 2 * kBM - 1) / (2 * kBM) * (2 * kBM), rows_lone = (t + kBM - 1) / kBM * kBM;
-    return t > kBM && 10 * rows_pair <= 11 * rows_lone && static_cast<double>(t) * static_cast<double>(n) * static_cast<double>(k) >= 1.2e10;
+    return t > kBM && 10 * rows_pair <= 11 * rows_lone && static_cast<double>(t) * static_cast<double>(n) * static_cast<double>(k) >= 0.9e10;
 }
 
 // config: -1 picks; 0..3 are the four fixed schedules of gemm.hpp; otherwise the tile width (a multiple of 16 in [16, 256]) plus 1
@@ -2360,12 +2363,13 @@ void launch_gemm_f16(Context& ctx, const void* x, std::size_t ld_x, const void* 
     // 200 to 900 tokens where such a wave exists (o projection at 900 tokens: 28.8 -> 23.1 us; k or v: 18.9 -> 15.7; fused qkv at 450
     // tokens: 22.0 -> 18.4; down projection at 600 tokens: 46.3 -> 41.3), CTA pairs included. The narrowest width that still fits the
     // wave: the k loop a CTA has to feed is shortest. Not for long k at many tokens, where the pairs' even split wins (down projection
-    // at 1200 tokens: 59 us split on pairs, 65 us as one wave of lone CTAs).
+    // at 1200 tokens: 59 us split on pairs, 65 us as one wave of lone CTAs), and not at the full width of 256, where the wave is as fast
+    // as the pairs only with its weights already in the L2 (q projection at 900 tokens, weights from DRAM: 25.6 us against 23.1).
     bool one_wave = false;
     if (config == -1 && t > kBM && t * k <= 900u * 9728u) {
         const std::size_t m_tiles = (t + kBM - 1) / kBM, ctas = static_cast<std::size_t>(ctx.sm_count);
-        for (const unsigned width : {128u, 160u, 192u, 224u, 256u}) {
-            if (epilogue == Epilogue::SwiGLU && width != 128 && width != 256) continue;
+        for (const unsigned width : {128u, 160u, 192u, 224u}) {
+            if (epilogue == Epilogue::SwiGLU && width != 128) continue;
             if (m_tiles * ((n + width - 1) / width) <= ctas) {
                 bn = width;
                 pair = stream_k = late = false;

@@ -181,13 +181,19 @@ def test_score_packs_requests_into_calls_and_matches_one_by_one(oracle):
         hidden, times = trunk.score(requests)
         assert hidden.shape == (len(requests), cfg.hidden) and np.isfinite(hidden).all()
         assert (times > 0).all() and (np.diff(times) >= 0).all()  # requests finish in the order of their calls
+        # A request alone and the same request inside a packed call go through launches of different row counts, for which the automatic
+        # schedule may differ (one wave of lone CTAs with two issuing threads sums the even and the odd k steps separately, the pair
+        # kernels sum k in order): last-bit differences of float32 sums, some of which cross a binary16 rounding boundary between
+        # layers and are then amplified by the mixers' recurrences. Measured: 2e-5 to 4.5e-4 after eight layers (largest for the 700-token
+        # request, whose DeltaNet states and attention keys carry over its cuts); the fp16 path's stated tolerance is 2e-3. Identical
+        # launches are bit-equal (next assertion), and inside one launch a row's result does not depend on the other rows.
         for i in (0, 1, 3, 6, 8, 9, 40, len(requests) - 1):
             alone, _, _ = trunk.run(requests[i])
-            assert rel_fro(hidden[i], alone) < 1e-5, i
+            assert rel_fro(hidden[i], alone) < 2e-3, i
         again, _ = trunk.score(requests)
         assert np.array_equal(again, hidden)
         one, _ = trunk.score(requests[6:7])
-        assert rel_fro(one[0], hidden[6]) < 1e-5
+        assert rel_fro(one[0], hidden[6]) < 2e-3
         with pytest.raises(sb.SepalB200Error, match="empty"):
             trunk.score([requests[0], np.zeros(0, np.uint32)])
         with pytest.raises(sb.SepalB200Error, match="outside the vocabulary"):

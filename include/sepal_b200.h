@@ -87,6 +87,16 @@ SEPAL_B200_API uint64_t sepal_b200_take_launch_count(void);
  * launches its kernels one after the other, runner/cuda/src/cuda_engine.cpp:1724-1952); off = plain stream order, for comparisons. */
 SEPAL_B200_API void sepal_b200_set_launch_overlap(int32_t on);
 
+/* The caller's promise for the multiplies it launches through `ctx` from now on (on != 0), or its withdrawal (0, the default): the
+ * weight matrix of a multiply (w, or q with its scales) is not written by the kernel that runs directly before the multiply in its
+ * stream. An inference engine's weights are uploaded once, so every multiply of the reference's engine qualifies
+ * (CudaEngine::Impl::gemm, runner/cuda/src/cuda_engine.cpp:1093-1154, reads device copies written at load time, as
+ * CudaGemm::upload_weights writes a provider's, runner/cuda/src/cuda_gemm.cpp:389-394). With the promise a kernel launched as a programmatic dependent (see above)
+ * requests its first weight tiles while the kernel before it is still finishing, and waits for that kernel only before it touches the
+ * activations and the result: a launch starts about a microsecond earlier. The provider and the trunk of this library, whose weights
+ * are uploaded through a synchronising call, set it for their own contexts. Results do not change. */
+SEPAL_B200_API int32_t sepal_b200_set_static_weights(sepal_b200_ctx* ctx, int32_t on);
+
 /* ---- launchers on device pointers ------------------------------------------------------------------------------------------ */
 
 /* binary16 x binary16 -> float32 accumulation on the tensor cores (tcgen05.mma), result binary16 (y_half != 0) or float32.
@@ -125,7 +135,10 @@ SEPAL_B200_API int32_t sepal_b200_gemm_f16_noalloc(const void* x, uint64_t ld_x,
  * launch_gemm_simt with SimtWeight::Int8Group (runner/cuda/src/gemm_simt_kernels.hpp:42-56). q is int8 [N, ld_q]; scales_t / descale come from sepal_b200_prepare_w8g_scales.
  * Requires K a multiple of 128, ld_x a multiple of 8, ld_q a multiple of 16, scales_t 16-byte aligned with ld_st >= N rounded up to
  * 256 (the padding zero). config as sepal_b200_gemm_f16, and 512 + w (w = 64, 96, ..., 192, 256 or 320) forces the kernel that takes the
- * weights as the tensor cores' first operand with w tokens to a tile, which -1 picks where it is the faster one. */
+ * weights as the tensor cores' first operand with w tokens to a tile, which -1 picks where it is the faster one; 512 + w + 1 (w up to
+ * 192, a float32 residual update into 16-byte aligned rows, fewer tiles than CTA pairs) forces its shared form, in which the CTA pairs
+ * that would idle take the first scale groups of every tile: Y becomes (Y + the first groups' product) + the other groups' product,
+ * two float32 additions in a fixed order instead of one (-1 takes this form where it is the faster one). */
 SEPAL_B200_API int32_t sepal_b200_gemm_w8g(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const int8_t* q, uint64_t ld_q, const void* scales_t,
                                            uint64_t ld_st, const float* descale, void* y, uint64_t ld_y, int32_t y_half, uint64_t t, uint64_t n,
                                            uint64_t k, int32_t epilogue, int32_t config, void* stream);
@@ -133,8 +146,8 @@ SEPAL_B200_API int32_t sepal_b200_gemm_w8g(sepal_b200_ctx* ctx, const void* x, u
 /* Which kernel the automatic schedule (config -1) of sepal_b200_gemm_w8g gives a [t x k] by [n x k] multiply on a GPU of `sm_count` SMs:
  * the tokens to a tile of the swapped kernel (96, 128, 160 or 192: one block; 256 or 320: two blocks of half as many that share the
  * converted weights; sepal_b200_gemm_w8g's config 512 + w forces it), or 0 for the unswapped kernels. `epilogue` as in the multiply;
- * `staged` != 0: the result goes into 16-byte aligned rows and is not a float32 SwiGLU (it then leaves through shared memory and the TMA,
- * which the estimate counts). Host arithmetic only: needs no GPU and no context. No counterpart in the reference. */
+ * `staged` != 0: the result goes into 16-byte aligned rows and is neither a float32 SwiGLU nor a binary16 residual update (it then
+ * leaves through shared memory and the TMA, which the estimate counts). Host arithmetic only: needs no GPU and no context. No counterpart in the reference. */
 SEPAL_B200_API int32_t sepal_b200_w8g_schedule(uint32_t sm_count, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t staged);
 
 /* binary16 activations x int8 weights with ONE float32 scale per output row (the gpu-q8w layout): Y[t, n] = sw[n] * sum_k x[t, k] q[n, k].

@@ -124,10 +124,17 @@ int32_t sepal_b200_debug_leave_status(sepal_b200_ctx* ctx, void* stream, int32_t
 uint64_t sepal_b200_take_launch_count(void) { return take_launch_count(); }
 
 int32_t sepal_b200_w8g_schedule(uint32_t sm_count, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t staged) {
-    return static_cast<int32_t>(w8g_swapped_tokens(sm_count, t, n, k, staged != 0, epilogue == static_cast<int32_t>(Epilogue::SwiGLU)));
+    return static_cast<int32_t>(w8g_swapped_tokens(sm_count, t, n, k, staged != 0, epilogue_of(epilogue)));
 }
 
 void sepal_b200_set_launch_overlap(int32_t on) { set_launch_overlap(on != 0); }
+
+int32_t sepal_b200_set_static_weights(sepal_b200_ctx* ctx, int32_t on) {
+    return guarded([&] {
+        require(ctx, "ctx");
+        ctx->ctx.static_weights = on != 0;
+    });
+}
 
 int32_t sepal_b200_gemm_f16(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const void* w, uint64_t ld_w, void* y, uint64_t ld_y, int32_t y_half,
                             uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t config, void* stream) {

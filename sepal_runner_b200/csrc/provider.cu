@@ -23,6 +23,7 @@ __global__ void scale_rows_kernel(float* y, std::size_t count, float beta) {
 }  // namespace
 
 B200Gemm::B200Gemm(int device, std::size_t arena_bytes) : ctx_(device, 0) {
+    ctx_.static_weights = true;  // upload_weights returns only after its stream has finished: no multiply follows a kernel that writes its weights
     arena_bytes_ = arena_bytes != 0 ? arena_bytes : (std::size_t{1} << 30);
     check(cudaSetDevice(device), "cudaSetDevice");
     check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");

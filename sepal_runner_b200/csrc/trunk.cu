@@ -220,6 +220,8 @@ void* Trunk::alloc(std::size_t bytes) {
 }
 
 Trunk::Trunk(int device, const TrunkConfig& config, const Checkpoint* checkpoint) : cfg_(config), ctx_(device, 0) {
+    ctx_.static_weights = true;  // the weights are in place (and the stream waited for) before the constructor returns
+
     TrunkConfig& c = cfg_;
     if (c.attn_o == 0) c.attn_o = c.attn_q;
     if (c.layers == 0 || c.hidden % 128 != 0 || c.intermediate % 128 != 0 || c.attn_q % 128 != 0 || c.attn_o % 128 != 0 || c.attn_kv % 8 != 0 ||

@@ -57,6 +57,7 @@ SIGNATURES = {
     "sepal_b200_trunk_open": (_i32, [_i32, _vp, C.POINTER(_vp)]),
     "sepal_b200_trunk_close": (None, [_vp]),
     "sepal_b200_set_launch_overlap": (None, [_i32]),
+    "sepal_b200_set_static_weights": (_i32, [_vp, _i32]),
     "sepal_b200_attention_prepare": (_i32, [_vp, _vp, _vp, _u64, _vp, _u64, _i32, _vp, _u64, _i32, _vp, _u64, _i32, _vp, _vp, _vp, _u64, _vp, _vp, _u64, _vp]),
     "sepal_b200_attention": (_i32, [_vp, _vp, _vp, _u64, _u64, _vp, _u64, _vp, _vp, _u64, _vp, _u64, _i32, _vp, _u64, _vp]),
     "sepal_b200_deltanet": (_i32, [_vp, _vp, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp, _u64, _vp]),
@@ -167,6 +168,11 @@ class Context:
         out = _i32()
         _check(self._lib.sepal_b200_status(self._h, _stream_ptr(stream), C.byref(out)))
         return out.value
+
+    def set_static_weights(self, on: bool = True) -> None:
+        """Promises (or withdraws the promise) that no kernel directly before a multiply of this context writes that multiply's weights
+        (sepal_b200_set_static_weights): the kernels then request their first weight tiles before they wait for the kernel before them."""
+        _check(self._lib.sepal_b200_set_static_weights(self._h, 1 if on else 0))
 
     def debug_leave_status(self, code: int, stale_counters: int = 0, stream=None) -> None:
         """Leaves the context as a kernel that gave up waiting would (sepal_b200_debug_leave_status): for tests of the recovery path."""

@@ -108,9 +108,12 @@ def test_int8_schedule_query_is_host_arithmetic(lib):
     two blocks of half as many) and the unswapped ones (0) for the trunk's shapes on a 148-SM GPU, as measured sweeps fixed it."""
     import sepal_runner_b200 as sb
 
-    assert sb.w8g_schedule(148, 900, 2560, 9728, sb.ADD) == 160      # the headline: 60 whole-k tiles of 160 tokens
+    assert sb.w8g_schedule(148, 900, 2560, 9728, sb.ADD) == 320      # the headline: 30 tiles of two blocks of 160 tokens, each shared by two pairs
+    assert sb.w8g_schedule(148, 900, 2560, 9728, sb.STORE) == 160    # stored, not added: 60 whole-k tiles of 160 tokens
     assert sb.w8g_schedule(148, 900, 2560, 4096, sb.ADD) == 160      # o + residual
-    assert sb.w8g_schedule(148, 300, 2560, 9728, sb.ADD) == 96       # few tokens: the narrowest tile
+    assert sb.w8g_schedule(148, 300, 2560, 9728, sb.STORE) == 96     # few tokens: the narrowest tile
+    assert sb.w8g_schedule(148, 300, 2560, 9728, sb.ADD) == 128      # a float32 residual update: 30 tiles, the other pairs take half of each
+    assert sb.w8g_schedule(148, 600, 2560, 9728, sb.ADD) == 160      # 40 tiles, 23 of the 76 groups of each go to the 34 spare pairs
     assert sb.w8g_schedule(148, 900, 9728, 2560, sb.STORE) == 320    # up: three tiles of two blocks of 160 by 38 tiles of weight rows
     assert sb.w8g_schedule(148, 4096, 2560, 9728, sb.ADD) == 320     # down at 4096 tokens
     assert sb.w8g_schedule(148, 4096, 19456, 2560, sb.SWIGLU) == 320

@@ -52,6 +52,9 @@ WORKLOADS = {
     # o-projection with the residual add fused (float32 stream updated in place)
     "f16_dn_out_m900": ("f16", 900, 2560, 2048, None, "add"),
     "f16_o_m900": ("f16", 900, 2560, 4096, None, "add"),
+    # the down projection as the trunk runs it, the residual add fused: fewer tiles than CTA pairs, so the pairs share the tiles
+    "w8g_down_add_m900": ("w8g", 900, 2560, 9728, None, "add"),
+    "f16_down_add_m900": ("f16", 900, 2560, 9728, None, "add"),
 }
 # Every named trunk GEMM (N x K) for the per-shape table: the projections of a layer at hidden 2560, MLP 9728.
 TRUNK_SHAPES = [("gate_up+swiglu", 19456, 2560, "swiglu"), ("up (config 0)", 9728, 2560, "store"), ("down+residual", 2560, 9728, "add"),

@@ -105,7 +105,10 @@ SEPAL_B200_API int32_t sepal_b200_set_static_weights(sepal_b200_ctx* ctx, int32_
  * Requires K, ld_x, ld_w multiples of 8, N and ld_y even, x and w 16-byte aligned (gemm_nt_supports, gemm_kernels.hpp:34-36);
  * SWIGLU needs N a multiple of 128. config: -1 picks the tile width and schedule from the shape; other values force one (tests and
  * tuning: 0..3, or a tile width that is a multiple of 16 up to 256, plus 1 for the even split of k, 2 for CTA pairs, 3 for both,
- * or 6 for pairs that run whole tiles first and split only the last waves). t == 0 is a no-op. */
+ * 6 for pairs that run whole tiles first and split only the last waves, and, for a float32 residual update (ADD, y_half == 0, 16-byte
+ * aligned rows) only, 7 for pairs that share every tile when there are fewer tiles than pairs, or 5 for pairs that share the tiles
+ * of the last, partial wave: the parts of a shared tile are added to Y one after the other in the order of their ranges of k, two
+ * or three float32 additions in a fixed order instead of one; -1 takes these forms where they are the faster ones). t == 0 is a no-op. */
 SEPAL_B200_API int32_t sepal_b200_gemm_f16(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const void* w, uint64_t ld_w, void* y, uint64_t ld_y,
                                            int32_t y_half, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t config, void* stream);
 

@@ -710,6 +710,48 @@ def test_late_split_with_swiglu(ctx, oracle):
 # ---- the automatic choice (config -1) on shapes that reach each of its branches ----------------------------------------------------------
 
 
+@pytest.mark.parametrize("t,n,k,width", [(4096, 2560, 2048, 256), (2100, 1280, 1544, 128), (4096, 2816, 1024, 256)])
+def test_pairs_share_the_tiles_of_the_last_wave(ctx, oracle, t, n, k, width):
+    """config width + 5: more tiles than CTA pairs and a float32 residual update. Whole tiles for the full waves; each tile of the last
+    wave in two or three parts (each a few k iterations longer than the one before) whose sums are added to Y in the order of their
+    ranges of k. Every element of Y is either Y + the whole product or ((Y + part 0) + part 1) + part 2, each as the pair kernel
+    computes it alone; the same bits on every launch; the tile counters end at zero."""
+    import torch
+
+    import sepal_runner_b200 as sb
+
+    pairs = ctx.info()["sm_count"] // 2
+    tiles = -(-t // 256) * -(-n // width)
+    rest = tiles % pairs
+    assert tiles > pairs and rest > 0
+    parts = min(pairs // rest, 3)
+    k_iters = -(-k // 64)
+    stagger = min(10, k_iters // (2 * parts))
+    first = (k_iters - stagger * (parts * (parts - 1) // 2)) // parts
+    assert parts >= 2 and first >= 4
+    cuts = [j * first + stagger * (j * (j - 1) // 2) for j in range(parts)] + [k_iters]
+    x, w = make(oracle, 9500 + t, t, n, k)
+    xd, wd = dev(x).half(), dev(w).half()
+    res = dev(np.random.default_rng(9501).standard_normal((t, n), dtype=np.float32))
+    in_parts = res.clone()
+    for j in range(parts):
+        xj = torch.zeros_like(xd)
+        xj[:, cuts[j] * 64:cuts[j + 1] * 64] = xd[:, cuts[j] * 64:cuts[j + 1] * 64]
+        in_parts = in_parts + ctx.gemm_f16(xj, wd, y_half=False, config=width + 2)
+    at_once = res + ctx.gemm_f16(xd, wd, y_half=False, config=width + 2)
+    split_before = ctx.gemm_f16(xd, wd, y_half=False, config=3)
+    for _ in range(20):
+        y = res.clone()
+        ctx.gemm_f16(xd, wd, y, epilogue=sb.ADD, config=width + 5)
+        ctx.check_status()
+        assert ((y == at_once) | (y == in_parts)).all()
+    shared = int((y != at_once).sum())
+    assert 0 < shared <= rest * 256 * width  # only the last wave's tiles are summed in parts
+    assert torch.equal(ctx.gemm_f16(xd, wd, y_half=False, config=3), split_before)
+    with pytest.raises(sb.SepalB200Error, match="width \\+ 5"):
+        ctx.gemm_f16(xd, wd, y_half=True, config=width + 5)
+
+
 @pytest.mark.parametrize("t,n,k,width", [(900, 2560, 2560, 256), (300, 640, 1024, 128), (600, 1040, 1000, 64), (900, 2560, 9728, 256), (900, 2560, 4096, 160)])
 def test_pairs_share_the_tiles_of_a_residual_update(ctx, oracle, t, n, k, width):
     """config width + 7: fewer tiles than CTA pairs and a float32 residual update. The spare pairs take the first k iterations of every

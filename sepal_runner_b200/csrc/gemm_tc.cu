@@ -2757,14 +2757,15 @@ void launch_gemm_f16(Context& ctx, const void* x, std::size_t ld_x, const void* 
     // at 4096 values of k (o projection) it gains nothing. Tiles of 256 columns, or, where those leave more than four tenths of the pairs without a tile
     // of their own, the narrowest width from 160 up that still gives every tile a spare pair.
     bool one_wave = false;
-    if (config == -1 && epilogue == Epilogue::Add && !y_half && t > kBM && k >= 6144 && reinterpret_cast<std::uintptr_t>(y) % 16 == 0 && ld_y % 4 == 0) {
+    if (config == -1 && epilogue == Epilogue::Add && !y_half && t > kBM && k >= 4096 && reinterpret_cast<std::uintptr_t>(y) % 16 == 0 && ld_y % 4 == 0) {
         const std::size_t m_pair_tiles = (t + 2 * kBM - 1) / (2 * kBM), pairs = static_cast<std::size_t>(ctx.sm_count / 2);
         const std::size_t tiles = m_pair_tiles * ((n + 255) / 256);
         if (tiles > pairs && pick_pair(t, n, k)) {
-            // more tiles than pairs: whole tiles for the full waves, the last wave's tiles in ordered parts (launch_pair's form 5)
+            // More tiles than pairs: whole tiles for the full waves, the last wave's tiles in ordered parts (launch_pair's form 5).
+            // From 4096 values of k (o projection at 4096 rows: 75.5 to 78 us -> 72.3 to 76; DeltaNet out projection, 2048 values: 43 -> 47).
             shared = pair = late = true;
             stream_k = false;
-        } else if (tiles < pairs && 6 * tiles <= 5 * pairs && tiles <= ctx.scratch.counter_count) {
+        } else if (k >= 6144 && tiles < pairs && 6 * tiles <= 5 * pairs && tiles <= ctx.scratch.counter_count) {
             shared = pair = true;
             stream_k = late = false;
             bn = 256;

@@ -138,10 +138,10 @@ SEPAL_B200_API int32_t sepal_b200_gemm_f16_noalloc(const void* x, uint64_t ld_x,
  * launch_gemm_simt with SimtWeight::Int8Group (runner/cuda/src/gemm_simt_kernels.hpp:42-56). q is int8 [N, ld_q]; scales_t / descale come from sepal_b200_prepare_w8g_scales.
  * Requires K a multiple of 128, ld_x a multiple of 8, ld_q a multiple of 16, scales_t 16-byte aligned with ld_st >= N rounded up to
  * 256 (the padding zero). config as sepal_b200_gemm_f16, and 512 + w (w = 64, 96, ..., 192, 256 or 320) forces the kernel that takes the
- * weights as the tensor cores' first operand with w tokens to a tile, which -1 picks where it is the faster one; 512 + w + 1 (w up to
- * 192, a float32 residual update into 16-byte aligned rows, fewer tiles than CTA pairs) forces its shared form, in which the CTA pairs
- * that would idle take the first scale groups of every tile: Y becomes (Y + the first groups' product) + the other groups' product,
- * two float32 additions in a fixed order instead of one (-1 takes this form where it is the faster one). */
+ * weights as the tensor cores' first operand with w tokens to a tile, which -1 picks where it is the faster one; 512 + w + 1 (a
+ * float32 result, stored or added, in 16-byte aligned rows; fewer tiles than CTA pairs) forces its shared form, in which the CTA pairs
+ * that would idle take the first scale groups of every tile: Y becomes (Y + the first groups' product) + the other groups' product
+ * (without the Y for a stored result), float32 additions in a fixed order (-1 takes this form where it is the faster one). */
 SEPAL_B200_API int32_t sepal_b200_gemm_w8g(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const int8_t* q, uint64_t ld_q, const void* scales_t,
                                            uint64_t ld_st, const float* descale, void* y, uint64_t ld_y, int32_t y_half, uint64_t t, uint64_t n,
                                            uint64_t k, int32_t epilogue, int32_t config, void* stream);

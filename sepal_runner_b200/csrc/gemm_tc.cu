@@ -1725,12 +1725,12 @@ constexpr int kW8tBarriers = 4 * kW8tMaxDepth + 2 * kW8tMaxA + 4;
 constexpr unsigned kW8tRawBytes = 128 * 128;                 // one raw box
 constexpr unsigned kW8tStagingBytes = 4 * 2 * 4096;          // four epilogue warps x two boxes of [32 x 32] float32
 
-// A pair's list of work in the swapped kernel: whole tiles round-robin, or, with fewer tiles than pairs and a float32 residual
-// update (p.stream_k != 0), the SHARED form that leaves no pair idle: pair t < tiles owns tile t and takes its scale groups from
+// A pair's list of work in the swapped kernel: whole tiles round-robin, or, with fewer tiles than pairs and a float32 result that
+// leaves through the TMA (p.stream_k != 0), the SHARED form that leaves no pair idle: pair t < tiles owns tile t and takes its scale groups from
 // p.split_base on; the first p.split_base groups of every tile go to the spare pairs (pair tiles + s takes them for tiles s, s + spares,
-// s + 2 spares, ...), which add their part to Y first and count it in the tile's counter; the owner adds its part once the counter
-// shows the spare pair's eight epilogue warps done (a spare pair's items end long before the owners do, all but its last). Y is then
-// (Y + the first groups' sum) + the other groups' sum, whatever the timing.
+// s + 2 spares, ...), which add their part to Y first (or store it, when the result is not a residual update) and count it in the
+// tile's counter; the owner adds its part once the counter shows the spare pair's eight epilogue warps done (a spare pair's items end
+// long before the owners do, all but its last). Y is then (Y + the first groups' sum) + the other groups' sum, whatever the timing.
 struct W8tItems {
     unsigned pair, pairs, tiles, groups, given, shared, step;
     __device__ W8tItems(const GemmParams& p, unsigned pair_, unsigned pairs_)
@@ -2086,8 +2086,9 @@ gemm_w8t_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        // the residual update adds the box to Y; a plain float32 result is stored over it
-                        if (p.epilogue == 1)
+                        // the residual update adds the box to Y; a plain float32 result is stored over it (the owner of a shared tile
+                        // adds its part to the part the spare pair has stored)
+                        if (p.epilogue == 1 || items.owner())
                             ptx::tma_reduce_add_2d(&map_y, my_boxes_addr + box * 4096, static_cast<int>(n_tile * 256 + rank * 128 + quarter * 32), static_cast<int>(t0 + c));
                         else if (n_tile * 256 + rank * 128 + quarter * 32 < p.n)
                             ptx::tma_store_2d(&map_y, my_boxes_addr + box * 4096, static_cast<int>(n_tile * 256 + rank * 128 + quarter * 32), static_cast<int>(t0 + c));
@@ -2445,17 +2446,18 @@ void launch_w8t_pair(const Context& ctx, const void* x, std::size_t ld_x, const 
     if (p.staged_store != 0)
         map_y = make_tensor_map_2d(ctx, p.y, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.m, p.epilogue == 2 ? p.n / 2 : p.n, p.ld_y, 16, 32, false);
     const unsigned smem = fixed + depth * per_group;
-    // Fewer tiles than pairs and a float32 residual update that leaves through the TMA's reduce-add: the idle pairs take the first
-    // `given` scale groups of every tile. (Results that are stored, not added, were tried through scratch memory, the owner adding the
+    // Fewer tiles than pairs and a float32 result that leaves through the TMA (a residual update: both parts are reduce-adds; a plain
+    // float32 result: the spare pair stores its part and the owner adds to it): the idle pairs take the first `given` scale groups of
+    // every tile. (Binary16 results were tried through scratch memory, the owner adding the
     // spare pair's float32 sums to its own before it finishes the tile: correct, and 5 to 20 us slower than whole tiles, because the
     // owner's epilogue then waits for an L2 round trip per chunk of 32 tokens. Taken out.)
     unsigned given = 0;
-    if (share != 0 && p.epilogue == 1 && p.staged_add != 0 && p.tiles <= ctx.scratch.counter_count && p.counters != nullptr &&
+    if (share != 0 && p.epilogue != 2 && p.staged_add != 0 && p.tiles <= ctx.scratch.counter_count && p.counters != nullptr &&
         (share > 0 || blocks == 1 || p.k_iters >= 48))  // (the automatic schedule's conditions are pick_w8t_tokens')
         given = w8t_given(pairs, p.tiles, p.k_iters, share > 0);
     if (share > 0 && given == 0)
-        throw std::invalid_argument("launch_gemm_w8g: the shared form (config 512 + w + 1) needs a float32 residual update into 16-byte aligned rows, "
-                                    "fewer tiles than CTA pairs and at least four scale groups");
+        throw std::invalid_argument("launch_gemm_w8g: the shared form (config 512 + w + 1) needs a float32 result (stored or added) in 16-byte aligned "
+                                    "rows, fewer tiles than CTA pairs and at least four scale groups");
     if (given != 0) {
         p.stream_k = 1;
         p.split_base = given;

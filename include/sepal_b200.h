@@ -108,7 +108,9 @@ SEPAL_B200_API int32_t sepal_b200_set_static_weights(sepal_b200_ctx* ctx, int32_
  * 6 for pairs that run whole tiles first and split only the last waves, and, for a float32 residual update (ADD, y_half == 0, 16-byte
  * aligned rows) only, 7 for pairs that share every tile when there are fewer tiles than pairs, or 5 for pairs that share the tiles
  * of the last, partial wave: the parts of a shared tile are added to Y one after the other in the order of their ranges of k, two
- * or three float32 additions in a fixed order instead of one; -1 takes these forms where they are the faster ones). t == 0 is a no-op. */
+ * or three float32 additions in a fixed order instead of one; -1 takes these forms where they are the faster ones); or 512 + w (w =
+ * 64, 96, ..., 192, 256 or 320) for the kernel that takes the weights as the tensor cores' first operand with w tokens to a tile,
+ * which -1 takes where its tiles make one well-filled wave. t == 0 is a no-op. */
 SEPAL_B200_API int32_t sepal_b200_gemm_f16(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const void* w, uint64_t ld_w, void* y, uint64_t ld_y,
                                            int32_t y_half, uint64_t t, uint64_t n, uint64_t k, int32_t epilogue, int32_t config, void* stream);
 

@@ -91,7 +91,8 @@ int32_t sepal_b200_info(sepal_b200_ctx* ctx, char* buffer, uint64_t capacity, ui
         const std::string json = std::string("{\"library\":\"sepal_b200\",\"api_version\":1,\"device\":") + std::to_string(c.device) +
                                  ",\"compute_capability\":\"" + std::to_string(c.compute_major) + "." + std::to_string(c.compute_minor) +
                                  "\",\"sm_count\":" + std::to_string(c.sm_count) + ",\"workspace_bytes\":" + std::to_string(c.scratch.partial_bytes) +
-                                 ",\"kernels\":[\"gemm_tc_kernel<BN,W8> (tcgen05.mma kind::f16, TMA, TMEM)\",\"quantize_group_s8_kernel\","
+                                 ",\"kernels\":[\"gemm_tc_kernel<W8> (tcgen05.mma kind::f16, TMA, TMEM)\",\"gemm_pair_kernel\",\"gemm_w8_pair_kernel\",\"gemm_w8t_pair_kernel\","
+                                 "\"gemm_f16t_pair_kernel\",\"quantize_group_s8_kernel\","
                                  "\"prepare_scales_kernel\",\"pack_gate_up_kernel\"],\"fallback\":\"none\"}";
         if (needed != nullptr) *needed = json.size() + 1;
         if (buffer == nullptr || capacity < json.size() + 1) throw std::length_error("buffer too small: " + std::to_string(json.size() + 1) + " bytes needed");

@@ -55,6 +55,8 @@ WORKLOADS = {
     # the down projection as the trunk runs it, the residual add fused: fewer tiles than CTA pairs, so the pairs share the tiles
     "w8g_down_add_m900": ("w8g", 900, 2560, 9728, None, "add"),
     "f16_down_add_m900": ("f16", 900, 2560, 9728, None, "add"),
+    # the attention layers' fused q, k, v projection: 72 swapped tiles of 320 tokens, one wave of the 74 CTA pairs
+    "f16_qkv_m900": ("f16", 900, 6144, 2560, None, "store"),
 }
 # Every named trunk GEMM (N x K) for the per-shape table: the projections of a layer at hidden 2560, MLP 9728.
 TRUNK_SHAPES = [("gate_up+swiglu", 19456, 2560, "swiglu"), ("up (config 0)", 9728, 2560, "store"), ("down+residual", 2560, 9728, "add"),

@@ -854,6 +854,11 @@ def test_automatic_choice_branches(ctx, oracle, t, n, k):
     y = ctx.gemm_f16(dev(x).half(), dev(w).half(), y_half=False)
     ctx.check_status()
     assert rel_fro(y.cpu().numpy(), want) < 1e-5
+    res = dev(np.random.default_rng(8001).standard_normal((t, n), dtype=np.float32))
+    yd = res.clone()
+    ctx.gemm_f16(dev(x).half(), dev(w).half(), yd, epilogue=__import__("sepal_runner_b200").ADD)  # (2048 rows: 70 swapped tiles of 320 tokens)
+    ctx.check_status()
+    assert rel_fro((yd - res).cpu().numpy(), want) < 1e-5
     if n > 2560:  # the swapped kernel's choice: the same bits as when it is asked for by name
         assert torch.equal(y, ctx.gemm_f16(dev(x).half(), dev(w).half(), y_half=False, config=512 + (320 if t == 900 else 160)))
         assert torch.equal(ctx.gemm_f16(dev(x).half(), dev(w).half(), y_half=True), y.half())

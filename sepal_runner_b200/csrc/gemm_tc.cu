@@ -2873,7 +2873,7 @@ void launch_gemm_f16(Context& ctx, const void* x, std::size_t ld_x, const void* 
             const unsigned tiles = static_cast<unsigned>((t + width - 1) / width) * n_tiles;
             if (tiles <= pairs && 10 * tiles >= 8 * pairs && tiles > best_tiles) best = width, best_tiles = tiles;  // the narrower tile on ties: less padding
         }
-        if (best != 0 && k <= 4096) {
+        if (best != 0 && k <= 4096 && 4 * n >= 3 * 256 * static_cast<std::size_t>(n_tiles)) {  // (and the tiles of 256 weight rows mostly real rows)
             const unsigned blocks = best > 192 ? 2u : 1u;
             launch_f16t_pair(ctx, x, ld_x, w, ld_w, common_params(ctx, y, ld_y, y_half, t, n, k, epilogue), best / blocks, blocks, stream);
             return;
@@ -2896,7 +2896,7 @@ void launch_gemm_f16(Context& ctx, const void* x, std::size_t ld_x, const void* 
     // at 4096 values of k (o projection) it gains nothing. Tiles of 256 columns, or, where those leave more than four tenths of the pairs without a tile
     // of their own, the narrowest width from 160 up that still gives every tile a spare pair.
     bool one_wave = false;
-    if (config == -1 && epilogue == Epilogue::Add && !y_half && t > kBM && k >= 4096 && reinterpret_cast<std::uintptr_t>(y) % 16 == 0 && ld_y % 4 == 0) {
+    if (config == -1 && epilogue == Epilogue::Add && aligned_f32 && t > kBM && k >= 4096 && n >= 512) {  // (narrow results keep their narrow tiles)
         const std::size_t m_pair_tiles = (t + 2 * kBM - 1) / (2 * kBM), pairs = static_cast<std::size_t>(ctx.sm_count / 2);
         const std::size_t tiles = m_pair_tiles * ((n + 255) / 256);
         if (tiles > pairs && pick_pair(t, n, k)) {

@@ -2873,6 +2873,14 @@ void launch_gemm_f16(Context& ctx, const void* x, std::size_t ld_x, const void* 
             const unsigned tiles = static_cast<unsigned>((t + width - 1) / width) * n_tiles;
             if (tiles <= pairs && 10 * tiles >= 8 * pairs && tiles > best_tiles) best = width, best_tiles = tiles;  // the narrower tile on ties: less padding
         }
+        // Two waves of swapped tiles where the pair kernel's 256-row tiles need a third (stored results only: the up projection at
+        // 900 tokens, 3 x 38 = 114 tiles of 320 tokens against 4 x 38 = 152 tiles on 74 pairs: 49.4 -> 46.4 us): the widest such tile.
+        if (best == 0 && epilogue == Epilogue::Store && static_cast<unsigned>((t + 2 * kBM - 1) / (2 * kBM)) * n_tiles > 2 * pairs) {
+            for (const unsigned width : {160u, 192u, 256u, 320u}) {
+                const unsigned tiles = static_cast<unsigned>((t + width - 1) / width) * n_tiles;
+                if (tiles > pairs && tiles <= 2 * pairs) best = width;
+            }
+        }
         if (best != 0 && k <= 4096 && 4 * n >= 3 * 256 * static_cast<std::size_t>(n_tiles)) {  // (and the tiles of 256 weight rows mostly real rows)
             const unsigned blocks = best > 192 ? 2u : 1u;
             launch_f16t_pair(ctx, x, ld_x, w, ld_w, common_params(ctx, y, ld_y, y_half, t, n, k, epilogue), best / blocks, blocks, stream);

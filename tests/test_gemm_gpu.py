@@ -759,6 +759,31 @@ def test_f16_swapped_kernel(ctx, oracle, t, n, k, tokens):
             assert rel_fro(got.float().cpu().numpy(), oracle.swiglu_packed(want.astype(np.float32), n // 2)) < (2e-3 if half else 1e-5)
 
 
+def test_f16_swapped_kernel_many_tiles_to_a_pair(ctx, oracle):
+    """3000 tokens by 2560 outputs: 320 tiles of 96 tokens on 74 pairs, so every pair walks four or five tiles and its ring of k steps
+    wraps around many times; two-block tiles likewise; every epilogue family once."""
+    import torch
+
+    import sepal_runner_b200 as sb
+
+    t, n, k = 3000, 2560, 520
+    x, w = make(oracle, 9700, t, n, k)
+    xd, wd = dev(x).half(), dev(w).half()
+    want = oracle.gemm(x, w)
+    res = dev(np.random.default_rng(9701).standard_normal((t, n), dtype=np.float32))
+    for config in (512 + 96, 512 + 192, 512 + 256, 512 + 320):
+        y = ctx.gemm_f16(xd, wd, y_half=False, config=config)
+        ctx.check_status()
+        assert rel_fro(y.cpu().numpy(), want) < 1e-5, config
+        assert torch.equal(ctx.gemm_f16(xd, wd, y_half=True, config=config), y.half())
+        yd = res.clone()
+        ctx.gemm_f16(xd, wd, yd, epilogue=sb.ADD, config=config)
+        assert torch.equal(yd, res + y)
+        got = ctx.gemm_f16(xd, wd, epilogue=sb.SWIGLU, y_half=True, config=config)
+        ctx.check_status()
+        assert rel_fro(got.float().cpu().numpy(), oracle.swiglu_packed(want.astype(np.float32), n // 2)) < 2e-3
+
+
 @pytest.mark.parametrize("t,n,k,width", [(4096, 2560, 2048, 256), (2100, 1280, 1544, 128), (4096, 2816, 1024, 256)])
 def test_pairs_share_the_tiles_of_the_last_wave(ctx, oracle, t, n, k, width):
     """config width + 5: more tiles than CTA pairs and a float32 residual update. Whole tiles for the full waves; each tile of the last

@@ -2497,7 +2497,8 @@ unsigned pick_w8t_tokens(unsigned pairs, unsigned m, unsigned n, unsigned k, boo
 }
 
 // The swapped int8 kernel (weights from tensor memory). `bt`: tokens per tile, a multiple of 32 from 64 to 192.
-// `share`: the shared form for fewer tiles than pairs (see W8tItems): 0 never, 1 wherever it can run, -1 where it is estimated to pay.
+// `share`: the shared form for a last wave with fewer tiles than pairs (see W8tItems): 0 never, 1 wherever it can run, -1 where it is
+// estimated to pay.
 void launch_w8t_pair(const Context& ctx, const void* x, std::size_t ld_x, const void* q, std::size_t ld_q, GemmParams p, unsigned bt, unsigned blocks,
                      int share, cudaStream_t stream) {
     p.bn = bt;
@@ -2542,7 +2543,7 @@ void launch_w8t_pair(const Context& ctx, const void* x, std::size_t ld_x, const 
     }
     if (share > 0 && given == 0)
         throw std::invalid_argument("launch_gemm_w8g: the shared form (config 512 + w + 1) needs a float32 result (stored or added) in 16-byte aligned "
-                                    "rows, fewer tiles than CTA pairs and at least four scale groups");
+                                    "rows, a last wave of fewer tiles than CTA pairs and at least four scale groups");
     if (given != 0) {
         p.stream_k = 1;
         p.split_base = given;

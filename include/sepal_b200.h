@@ -141,8 +141,8 @@ SEPAL_B200_API int32_t sepal_b200_gemm_f16_noalloc(const void* x, uint64_t ld_x,
  * Requires K a multiple of 128, ld_x a multiple of 8, ld_q a multiple of 16, scales_t 16-byte aligned with ld_st >= N rounded up to
  * 256 (the padding zero). config as sepal_b200_gemm_f16, and 512 + w (w = 64, 96, ..., 192, 256 or 320) forces the kernel that takes the
  * weights as the tensor cores' first operand with w tokens to a tile, which -1 picks where it is the faster one; 512 + w + 1 (a
- * float32 result, stored or added, in 16-byte aligned rows; fewer tiles than CTA pairs) forces its shared form, in which the CTA pairs
- * that would idle take the first scale groups of every tile: Y becomes (Y + the first groups' product) + the other groups' product
+ * float32 result, stored or added, in 16-byte aligned rows; a last wave of fewer tiles than CTA pairs) forces its shared form, in which
+ * the CTA pairs that would idle in that wave take the first scale groups of each of its tiles: Y becomes (Y + the first groups' product) + the other groups' product
  * (without the Y for a stored result), float32 additions in a fixed order (-1 takes this form where it is the faster one). */
 SEPAL_B200_API int32_t sepal_b200_gemm_w8g(sepal_b200_ctx* ctx, const void* x, uint64_t ld_x, const int8_t* q, uint64_t ld_q, const void* scales_t,
                                            uint64_t ld_st, const float* descale, void* y, uint64_t ld_y, int32_t y_half, uint64_t t, uint64_t n,
